@@ -1,0 +1,131 @@
+/*
+ * roller_b200 -- C ABI of the B200 (sm_100a) backend for the Roller rTile search -> fp32 GEMM path.
+ *
+ * The reference project compiles one `gemm_kernel(float* A, float* B, float* C)` per search hint
+ * through an MLIR/IREE pipeline and launches it through CuPy (src/roller.py:345-387 Compiler,
+ * src/roller.py:499-511 prepare_kernel, src/roller.py:525-607 run_eval / run_baseline). This
+ * library replaces that compile-and-launch layer: kernels are ahead-of-time compiled for
+ * sm_100a, one per buildable rTile, and a "plan" binds an rTile to a problem shape.
+ *
+ * Conventions
+ *   - every function returns 0 (ROLLER_OK) or a negative roller_status; nothing throws, aborts
+ *     or exits across this boundary;
+ *   - A is M x K, B is K x N, C is M x N, all row-major fp32 in device memory owned by the
+ *     caller; lda/ldb/ldc are row strides in elements;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream); *_run only
+ *     enqueues work;
+ *   - a plan is bound to the device that was current at create time and is not thread-safe.
+ */
+#ifndef ROLLER_B200_H_
+#define ROLLER_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum roller_status {
+  ROLLER_OK = 0,
+  ROLLER_ERR_INVALID = -1,     /* bad argument (null pointer, non-positive size, bad stride) */
+  ROLLER_ERR_UNSUPPORTED = -2, /* no compiled kernel for the requested rTile / mode */
+  ROLLER_ERR_CUDA = -3,        /* a CUDA runtime/driver call failed; see roller_b200_last_cuda_error */
+  ROLLER_ERR_DEVICE = -4,      /* the current device is not an sm_100 part */
+  ROLLER_ERR_TIMEOUT = -5,     /* a bounded device-side wait ran out; see roller_b200_last_status */
+  ROLLER_ERR_NOMEM = -6,       /* workspace allocation failed */
+  ROLLER_ERR_TOO_LARGE = -7    /* problem exceeds a fixed capacity of the entry point */
+} roller_status;
+
+/* Arithmetic modes of the tensor-core GEMM. */
+#define ROLLER_MODE_1XTF32 1 /* one TF32 product per fp32 product (10-bit mantissa inputs) */
+#define ROLLER_MODE_3XTF32 3 /* big/small split, three TF32 products: fp32-level accuracy */
+
+/* Flags for roller_b200_gemm_create. */
+#define ROLLER_FLAG_ACCUMULATE 1 /* C += A@B, the semantics of the reference's gemm_kernel, which
+                                    accumulates into a host-zeroed C (src/roller.py:62,534) */
+
+/* Device facts feeding the B200 device model of the search (reference: the constants hard-coded
+ * in arch.CUDA, src/arch.py:47-61). */
+typedef struct roller_dev_info {
+  int cc_major, cc_minor;
+  int sm_count;
+  int smem_per_block_optin; /* bytes a block may opt in to */
+  int smem_per_sm;          /* bytes */
+  int regs_per_sm;
+  int l2_bytes;
+  int sm_clock_khz;
+  int mem_clock_khz;
+  int mem_bus_bits;
+  int tmem_columns; /* 512 columns x 128 lanes x 32 bit per SM on sm_100 */
+  size_t total_mem;
+  char name[128];
+} roller_dev_info;
+
+/* One buildable rTile = one compiled kernel (reference: a TileDict hint, src/analyze.py:84-105,
+ * handed to Compiler, src/roller.py:345-356). */
+typedef struct roller_ktile {
+  int block_m;   /* output tile rows (128 per CTA, 256 for a CTA pair) */
+  int block_n;   /* output tile columns */
+  int rstep;     /* reduce step per pipeline stage, in elements */
+  int cta_group; /* 1, or 2 = two SMs cooperate on one tile (tcgen05 cta_group::2) */
+  int stages_1x; /* pipeline depth in 1xTF32 mode */
+  int stages_3x; /* pipeline depth in 3xTF32 mode */
+  int smem_1x;   /* dynamic shared memory per CTA, bytes */
+  int smem_3x;
+  int tmem_cols; /* TMEM columns allocated (double-buffered accumulator) */
+  int threads_1x;
+  int threads_3x;
+} roller_ktile;
+
+typedef struct roller_plan roller_plan;
+
+/* Replaces the constants of arch.CUDA (src/arch.py:47-61) with a query of device `dev`. */
+int roller_b200_device_info(int dev, roller_dev_info* out);
+
+/* Enumerate the compiled rTiles, so the search only emits hints that have a kernel (the
+ * reference can compile any hint at run time, src/roller.py:358-387). */
+int roller_b200_kernel_count(void);
+int roller_b200_kernel_desc(int idx, roller_ktile* out);
+
+/* Replaces Compiler(config, hint, ...).compile() (src/roller.py:345-387): bind an rTile to a
+ * problem. May allocate device workspace (only when lda/ldb are not multiples of 4 elements or
+ * A/B are not 16-byte aligned, in which case operands are staged through a padded copy). */
+int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int lda, int ldb,
+                            int ldc, int mode, int flags, roller_plan** out);
+
+/* Replaces cuda_func(grid, block, (A, B, C), shared_mem=...) (src/roller.py:545-550): enqueue one
+ * GEMM on `stream`. No allocation, no synchronisation. */
+int roller_b200_gemm_run(roller_plan* plan, const float* A, const float* B, float* C, void* stream);
+
+/* Replaces the timed loop of run_eval (src/roller.py:564-584): `warmup` untimed launches, then
+ * `iters` launches between two CUDA events on `stream`; *ms_per_iter is the mean. Blocks. */
+int roller_b200_gemm_time(roller_plan* plan, const float* A, const float* B, float* C, void* stream,
+                          int warmup, int iters, float* ms_per_iter);
+
+/* Host-buffer convenience used for end-to-end timing: copies A and B from host memory into
+ * plan-owned device buffers, runs the GEMM and copies C back, all on `stream`; blocks until C
+ * has arrived. The device buffers are allocated on the first call and kept. */
+int roller_b200_gemm_host(roller_plan* plan, const float* hA, const float* hB, float* hC,
+                          void* stream);
+
+/* Launch geometry the plan chose (the reference derives grid/block from the hint,
+ * src/roller.py:536-543). Any out pointer may be NULL. */
+int roller_b200_gemm_launch_info(const roller_plan* plan, int* grid, int* block, int* smem_bytes,
+                                 int* tiles_m, int* tiles_n);
+
+/* Reads back the device status word of the plan (0 = all bounded waits completed); returns
+ * ROLLER_ERR_TIMEOUT when it is non-zero. Synchronises the device. */
+int roller_b200_last_status(roller_plan* plan, uint32_t* device_status);
+
+int roller_b200_gemm_destroy(roller_plan* plan);
+
+const char* roller_b200_strerror(int status);
+/* Text of the last CUDA error seen by this library on the calling thread. */
+const char* roller_b200_last_cuda_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* ROLLER_B200_H_ */

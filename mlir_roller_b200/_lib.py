@@ -1,0 +1,213 @@
+"""ctypes binding of libroller_b200.so (declared in include/roller_b200.h).
+
+This is the only route from Python to the sm_100a kernels. There is no CPU fallback: when the
+shared library is missing or cannot be loaded, `load()` raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libroller_b200.so"
+
+MODE_1XTF32 = 1
+MODE_3XTF32 = 3
+FLAG_ACCUMULATE = 1
+
+OK = 0
+ERR_INVALID = -1
+ERR_UNSUPPORTED = -2
+ERR_CUDA = -3
+ERR_DEVICE = -4
+ERR_TIMEOUT = -5
+ERR_NOMEM = -6
+ERR_TOO_LARGE = -7
+
+
+class DevInfo(C.Structure):
+    _fields_ = [
+        ("cc_major", C.c_int), ("cc_minor", C.c_int),
+        ("sm_count", C.c_int),
+        ("smem_per_block_optin", C.c_int),
+        ("smem_per_sm", C.c_int),
+        ("regs_per_sm", C.c_int),
+        ("l2_bytes", C.c_int),
+        ("sm_clock_khz", C.c_int),
+        ("mem_clock_khz", C.c_int),
+        ("mem_bus_bits", C.c_int),
+        ("tmem_columns", C.c_int),
+        ("total_mem", C.c_size_t),
+        ("name", C.c_char * 128),
+    ]
+
+
+class KTile(C.Structure):
+    _fields_ = [
+        ("block_m", C.c_int), ("block_n", C.c_int), ("rstep", C.c_int), ("cta_group", C.c_int),
+        ("stages_1x", C.c_int), ("stages_3x", C.c_int),
+        ("smem_1x", C.c_int), ("smem_3x", C.c_int),
+        ("tmem_cols", C.c_int),
+        ("threads_1x", C.c_int), ("threads_3x", C.c_int),
+    ]
+
+    def as_dict(self) -> dict:
+        return {name: getattr(self, name) for name, _ in self._fields_}
+
+
+# name -> (restype, argtypes); every symbol include/roller_b200.h declares.
+SIGNATURES = {
+    "roller_b200_device_info": (C.c_int, [C.c_int, C.POINTER(DevInfo)]),
+    "roller_b200_kernel_count": (C.c_int, []),
+    "roller_b200_kernel_desc": (C.c_int, [C.c_int, C.POINTER(KTile)]),
+    "roller_b200_gemm_create": (C.c_int, [C.POINTER(KTile), C.c_int, C.c_int, C.c_int, C.c_int,
+                                          C.c_int, C.c_int, C.c_int, C.c_int,
+                                          C.POINTER(C.c_void_p)]),
+    "roller_b200_gemm_run": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "roller_b200_gemm_time": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                        C.c_int, C.c_int, C.POINTER(C.c_float)]),
+    "roller_b200_gemm_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "roller_b200_gemm_launch_info": (C.c_int, [C.c_void_p] + [C.POINTER(C.c_int)] * 5),
+    "roller_b200_last_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32)]),
+    "roller_b200_gemm_destroy": (C.c_int, [C.c_void_p]),
+    "roller_b200_strerror": (C.c_char_p, [C.c_int]),
+    "roller_b200_last_cuda_error": (C.c_char_p, []),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the shared library and type its entry points. Raises if it is not built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m mlir_roller_b200.build` "
+            "(there is no CPU fallback for the GEMM path)")
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here = header and library disagree
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+class RollerError(RuntimeError):
+    """Raised for a non-zero roller_status; `.status` holds the code."""
+
+    def __init__(self, status: int, where: str):
+        lib = load()
+        msg = lib.roller_b200_strerror(status).decode()
+        if status == ERR_CUDA:
+            msg += " (" + lib.roller_b200_last_cuda_error().decode() + ")"
+        super().__init__(f"{where}: {msg} [status {status}]")
+        self.status = status
+
+
+def check(status: int, where: str) -> None:
+    if status != OK:
+        raise RollerError(status, where)
+
+
+def device_info(dev: int = 0) -> DevInfo:
+    info = DevInfo()
+    check(load().roller_b200_device_info(dev, C.byref(info)), "roller_b200_device_info")
+    return info
+
+
+def kernel_tiles() -> list[KTile]:
+    """The rTiles that have a compiled kernel."""
+    lib = load()
+    out = []
+    for i in range(lib.roller_b200_kernel_count()):
+        kt = KTile()
+        check(lib.roller_b200_kernel_desc(i, C.byref(kt)), "roller_b200_kernel_desc")
+        out.append(kt)
+    return out
+
+
+def find_tile(block_m: int, block_n: int, cta_group: int | None = None) -> KTile:
+    for kt in kernel_tiles():
+        if kt.block_m == block_m and kt.block_n == block_n and \
+                (cta_group is None or kt.cta_group == cta_group):
+            return kt
+    raise RollerError(ERR_UNSUPPORTED, f"find_tile({block_m}, {block_n}, {cta_group})")
+
+
+def _stream_ptr(stream) -> C.c_void_p:
+    if stream is None:
+        import torch
+        stream = torch.cuda.current_stream()
+    return C.c_void_p(getattr(stream, "cuda_stream", stream))
+
+
+class GemmPlan:
+    """One rTile bound to one problem shape (owns the C-side plan)."""
+
+    def __init__(self, tile: KTile, M: int, N: int, K: int, *, lda: int | None = None,
+                 ldb: int | None = None, ldc: int | None = None, mode: int = MODE_3XTF32,
+                 flags: int = 0):
+        self._lib = load()
+        self._h = C.c_void_p()
+        self.tile = tile
+        self.M, self.N, self.K, self.mode = M, N, K, mode
+        self.lda = K if lda is None else lda
+        self.ldb = N if ldb is None else ldb
+        self.ldc = N if ldc is None else ldc
+        check(self._lib.roller_b200_gemm_create(C.byref(tile), M, N, K, self.lda, self.ldb,
+                                                self.ldc, mode, flags, C.byref(self._h)),
+              "roller_b200_gemm_create")
+
+    # -- raw-pointer interface (ints as returned by tensor.data_ptr())
+    def run_ptr(self, a_ptr: int, b_ptr: int, c_ptr: int, stream=None) -> None:
+        check(self._lib.roller_b200_gemm_run(self._h, a_ptr, b_ptr, c_ptr, _stream_ptr(stream)),
+              "roller_b200_gemm_run")
+
+    def run(self, A, B, Cout, stream=None) -> None:
+        self.run_ptr(A.data_ptr(), B.data_ptr(), Cout.data_ptr(), stream)
+
+    def time(self, A, B, Cout, warmup: int = 3, iters: int = 20, stream=None) -> float:
+        ms = C.c_float()
+        check(self._lib.roller_b200_gemm_time(self._h, A.data_ptr(), B.data_ptr(), Cout.data_ptr(),
+                                              _stream_ptr(stream), warmup, iters, C.byref(ms)),
+              "roller_b200_gemm_time")
+        return float(ms.value)
+
+    def run_host(self, hA, hB, hC, stream=None) -> None:
+        """hA/hB/hC: contiguous fp32 host arrays (numpy or pinned torch CPU tensors)."""
+        def ptr(x):
+            return x.ctypes.data if hasattr(x, "ctypes") else x.data_ptr()
+        check(self._lib.roller_b200_gemm_host(self._h, ptr(hA), ptr(hB), ptr(hC),
+                                              _stream_ptr(stream)), "roller_b200_gemm_host")
+
+    def launch_info(self) -> dict:
+        vals = [C.c_int() for _ in range(5)]
+        check(self._lib.roller_b200_gemm_launch_info(self._h, *[C.byref(v) for v in vals]),
+              "roller_b200_gemm_launch_info")
+        keys = ("grid", "block", "smem_bytes", "tiles_m", "tiles_n")
+        return {k: v.value for k, v in zip(keys, vals)}
+
+    def device_status(self) -> int:
+        st = C.c_uint32()
+        rc = self._lib.roller_b200_last_status(self._h, C.byref(st))
+        if rc not in (OK, ERR_TIMEOUT):
+            check(rc, "roller_b200_last_status")
+        return int(st.value)
+
+    def check_status(self) -> None:
+        st = self.device_status()
+        if st != 0:
+            raise RollerError(ERR_TIMEOUT, f"device status word = {st}")
+
+    def destroy(self) -> None:
+        if self._h:
+            self._lib.roller_b200_gemm_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass

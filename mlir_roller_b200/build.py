@@ -1,0 +1,65 @@
+"""Builds libroller_b200.so (the sm_100a kernels + C ABI) in-tree with nvcc.
+
+Run as `python -m mlir_roller_b200.build`; `build()` is also what the repository's build check
+calls. nvcc cross-compiles for sm_100a without a GPU.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+from pathlib import Path
+
+PKG_DIR = Path(__file__).resolve().parent
+CSRC = PKG_DIR / "csrc"
+LIB_PATH = PKG_DIR / "libroller_b200.so"
+
+SOURCES = ["gemm_variants.cu", "capi.cu"]
+HEADERS = ["ptx_sm100.cuh", "gemm_tf32_sm100.cuh", "gemm_launch.h"]
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC",
+    "--use_fast_math",
+]
+
+
+def _nvcc() -> str:
+    exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(exe):
+        raise RuntimeError("nvcc not found; libroller_b200.so cannot be built")
+    return exe
+
+
+def _stale() -> bool:
+    if not LIB_PATH.exists():
+        return True
+    built = LIB_PATH.stat().st_mtime
+    deps = [CSRC / f for f in SOURCES + HEADERS] + [PKG_DIR.parent / "include" / "roller_b200.h"]
+    return any(d.stat().st_mtime > built for d in deps)
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile every CUDA source for sm_100a and link the shared library."""
+    if not force and not _stale():
+        return LIB_PATH
+    nvcc = _nvcc()
+    objs = []
+    build_dir = PKG_DIR / "build"
+    build_dir.mkdir(exist_ok=True)
+    for src in SOURCES:
+        obj = build_dir / (src + ".o")
+        cmd = [nvcc, *NVCC_FLAGS, "-c", str(CSRC / src), "-o", str(obj)]
+        if verbose:
+            cmd[1:1] = ["-Xptxas", "-v"]
+        subprocess.run(cmd, check=True)
+        objs.append(str(obj))
+    subprocess.run([nvcc, "-shared", "-o", str(LIB_PATH), *objs, "-gencode",
+                    "arch=compute_100a,code=sm_100a"], check=True)
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    import sys
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -1,0 +1,374 @@
+// C ABI of libroller_b200: plans, tensor-map encoding, launch, timing. See include/roller_b200.h
+// for the contract of each entry point and the reference interface it stands in for.
+#include "../../include/roller_b200.h"
+
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "gemm_launch.h"
+
+namespace {
+
+using namespace rb200;
+
+thread_local char g_cuda_err[256] = "";
+
+int cuda_fail(cudaError_t e, const char* what) {
+  snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", what, cudaGetErrorString(e));
+  cudaGetLastError();  // clear the sticky-free error state
+  return ROLLER_ERR_CUDA;
+}
+
+#define RB_CUDA(call)                                   \
+  do {                                                  \
+    cudaError_t e_ = (call);                            \
+    if (e_ != cudaSuccess) return cuda_fail(e_, #call); \
+  } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up through the runtime, so the library has no link-time
+// dependency on libcuda.
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(p);
+  return fn;
+}
+
+// Row-major fp32 matrix `rows x cols` with row stride `ld` elements, loaded in boxes of
+// box_rows x box_cols; out-of-range elements read as zero.
+int encode_matrix(CUtensorMap* tm, const float* base, long long rows, long long cols, long long ld,
+                  int box_cols, int box_rows, CUtensorMapSwizzle swz) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled entry point not found");
+    return ROLLER_ERR_CUDA;
+  }
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * sizeof(float)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled failed with CUresult %d",
+             static_cast<int>(r));
+    return ROLLER_ERR_CUDA;
+  }
+  return ROLLER_OK;
+}
+
+// Copies a rows x cols matrix into a buffer whose row stride is a multiple of 4 elements, so
+// that TMA's 16-byte stride rule holds for operands with odd leading dimensions.
+__global__ void pad_rows_kernel(const float* __restrict__ src, long long ld_src,
+                                float* __restrict__ dst, long long ld_dst, int rows, int cols) {
+  const long long total = static_cast<long long>(rows) * cols;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / cols;
+    const long long c = i - r * cols;
+    dst[r * ld_dst + c] = src[r * ld_src + c];
+  }
+}
+
+long long round_up4(long long x) { return (x + 3) & ~3LL; }
+
+}  // namespace
+
+struct roller_plan {
+  const KernelVariant* kv;
+  int device;
+  int sm_count;
+  int M, N, K;
+  long long lda, ldb, ldc;
+  int mode, flags;
+  int tiles_m, tiles_n, grid;
+  bool stage_a, stage_b;  // operands go through a padded copy
+  float* ws_a;            // padded copies (device), owned
+  float* ws_b;
+  long long ws_lda, ws_ldb;
+  uint32_t* status;  // device status word, owned
+  // cached tensor maps for the last (A, B) pointers seen
+  const float* map_a_ptr;
+  const float* map_b_ptr;
+  CUtensorMap tmA, tmB;
+  // host-buffer path
+  float *hd_a, *hd_b, *hd_c;
+  cudaEvent_t ev0, ev1;
+};
+
+extern "C" {
+
+int roller_b200_device_info(int dev, roller_dev_info* out) {
+  if (!out) return ROLLER_ERR_INVALID;
+  cudaDeviceProp p;
+  RB_CUDA(cudaGetDeviceProperties(&p, dev));
+  memset(out, 0, sizeof(*out));
+  out->cc_major = p.major;
+  out->cc_minor = p.minor;
+  out->sm_count = p.multiProcessorCount;
+  out->smem_per_block_optin = static_cast<int>(p.sharedMemPerBlockOptin);
+  out->smem_per_sm = static_cast<int>(p.sharedMemPerMultiprocessor);
+  out->regs_per_sm = p.regsPerMultiprocessor;
+  out->l2_bytes = p.l2CacheSize;
+  int v = 0;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrClockRate, dev) == cudaSuccess) out->sm_clock_khz = v;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMemoryClockRate, dev) == cudaSuccess)
+    out->mem_clock_khz = v;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrGlobalMemoryBusWidth, dev) == cudaSuccess)
+    out->mem_bus_bits = v;
+  out->tmem_columns = (p.major == 10) ? 512 : 0;
+  out->total_mem = p.totalGlobalMem;
+  strncpy(out->name, p.name, sizeof(out->name) - 1);
+  return ROLLER_OK;
+}
+
+int roller_b200_kernel_count(void) {
+  // One entry per (block_n, cta_group): the table holds both modes of each tile.
+  return variant_count() / 2;
+}
+
+int roller_b200_kernel_desc(int idx, roller_ktile* out) {
+  if (!out || idx < 0 || idx >= roller_b200_kernel_count()) return ROLLER_ERR_INVALID;
+  const KernelVariant& v1 = variant_at(2 * idx);
+  const KernelVariant& v3 = variant_at(2 * idx + 1);
+  out->block_m = v1.block_m;
+  out->block_n = v1.block_n;
+  out->rstep = v1.rstep;
+  out->cta_group = v1.cta_group;
+  out->stages_1x = v1.stages;
+  out->stages_3x = v3.stages;
+  out->smem_1x = v1.smem_bytes;
+  out->smem_3x = v3.smem_bytes;
+  out->tmem_cols = v1.tmem_cols;
+  out->threads_1x = v1.threads;
+  out->threads_3x = v3.threads;
+  return ROLLER_OK;
+}
+
+int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int lda, int ldb, int ldc,
+                            int mode, int flags, roller_plan** out) {
+  if (!tile || !out) return ROLLER_ERR_INVALID;
+  *out = nullptr;
+  if (M <= 0 || N <= 0 || K <= 0 || lda < K || ldb < N || ldc < N) return ROLLER_ERR_INVALID;
+  if (mode != ROLLER_MODE_1XTF32 && mode != ROLLER_MODE_3XTF32) return ROLLER_ERR_INVALID;
+  if (flags & ~ROLLER_FLAG_ACCUMULATE) return ROLLER_ERR_INVALID;
+  const KernelVariant* kv =
+      find_variant(tile->block_m, tile->block_n, tile->rstep, tile->cta_group, mode);
+  if (!kv) return ROLLER_ERR_UNSUPPORTED;
+
+  int dev = 0;
+  RB_CUDA(cudaGetDevice(&dev));
+  cudaDeviceProp prop;
+  RB_CUDA(cudaGetDeviceProperties(&prop, dev));
+  if (prop.major != 10) return ROLLER_ERR_DEVICE;
+  if (static_cast<int>(prop.sharedMemPerBlockOptin) < kv->smem_bytes) return ROLLER_ERR_DEVICE;
+
+  roller_plan* p = new (std::nothrow) roller_plan();
+  if (!p) return ROLLER_ERR_NOMEM;
+  memset(p, 0, sizeof(*p));
+  p->kv = kv;
+  p->device = dev;
+  p->sm_count = prop.multiProcessorCount;
+  p->M = M; p->N = N; p->K = K;
+  p->lda = lda; p->ldb = ldb; p->ldc = ldc;
+  p->mode = mode;
+  p->flags = flags;
+  p->tiles_m = (M + kv->block_m - 1) / kv->block_m;
+  p->tiles_n = (N + kv->block_n - 1) / kv->block_n;
+  const long long tiles = static_cast<long long>(p->tiles_m) * p->tiles_n;
+  const int workers = p->sm_count / kv->cta_group;
+  p->grid = static_cast<int>(tiles < workers ? tiles : workers) * kv->cta_group;
+  p->stage_a = (lda % 4) != 0;
+  p->stage_b = (ldb % 4) != 0;
+
+  cudaError_t e = cudaFuncSetAttribute(kv->func, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kv->smem_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&p->status, sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMemset(p->status, 0, sizeof(uint32_t));
+  if (e == cudaSuccess && p->stage_a) {
+    p->ws_lda = round_up4(K);
+    e = cudaMalloc(&p->ws_a, sizeof(float) * p->ws_lda * M);
+  }
+  if (e == cudaSuccess && p->stage_b) {
+    p->ws_ldb = round_up4(N);
+    e = cudaMalloc(&p->ws_b, sizeof(float) * p->ws_ldb * K);
+  }
+  if (e == cudaSuccess) e = cudaEventCreate(&p->ev0);
+  if (e == cudaSuccess) e = cudaEventCreate(&p->ev1);
+  if (e != cudaSuccess) {
+    int rc = (e == cudaErrorMemoryAllocation) ? ROLLER_ERR_NOMEM : cuda_fail(e, "plan setup");
+    cudaGetLastError();
+    roller_b200_gemm_destroy(p);
+    return rc;
+  }
+  *out = p;
+  return ROLLER_OK;
+}
+
+int roller_b200_gemm_run(roller_plan* p, const float* A, const float* B, float* C, void* stream) {
+  if (!p || !A || !B || !C) return ROLLER_ERR_INVALID;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const KernelVariant* kv = p->kv;
+
+  // Operands that break TMA's rules (row stride or base not a multiple of 16 bytes) are staged
+  // through a padded copy; the base-alignment case needs a workspace made on demand at create
+  // time, so an unaligned base with an aligned stride is rejected here.
+  const float* a_src = A;
+  const float* b_src = B;
+  long long lda = p->lda, ldb = p->ldb;
+  if (p->stage_a) {
+    pad_rows_kernel<<<p->sm_count * 8, 256, 0, st>>>(A, p->lda, p->ws_a, p->ws_lda, p->M, p->K);
+    a_src = p->ws_a;
+    lda = p->ws_lda;
+  } else if (reinterpret_cast<uintptr_t>(A) & 15) {
+    return ROLLER_ERR_INVALID;
+  }
+  if (p->stage_b) {
+    pad_rows_kernel<<<p->sm_count * 8, 256, 0, st>>>(B, p->ldb, p->ws_b, p->ws_ldb, p->K, p->N);
+    b_src = p->ws_b;
+    ldb = p->ws_ldb;
+  } else if (reinterpret_cast<uintptr_t>(B) & 15) {
+    return ROLLER_ERR_INVALID;
+  }
+
+  if (a_src != p->map_a_ptr) {
+    int rc = encode_matrix(&p->tmA, a_src, p->M, p->K, lda, 32, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != ROLLER_OK) return rc;
+    p->map_a_ptr = a_src;
+  }
+  if (b_src != p->map_b_ptr) {
+    int rc = encode_matrix(&p->tmB, b_src, p->K, p->N, ldb, 32, 32,
+                           CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+    if (rc != ROLLER_OK) return rc;
+    p->map_b_ptr = b_src;
+  }
+
+  GemmArgs args;
+  args.tmA = p->tmA;
+  args.tmB = p->tmB;
+  args.C = C;
+  args.M = p->M; args.N = p->N; args.K = p->K;
+  args.ldc = p->ldc;
+  args.tiles_m = p->tiles_m;
+  args.tiles_n = p->tiles_n;
+  args.flags = (p->flags & ROLLER_FLAG_ACCUMULATE) ? kFlagAccumulate : 0;
+  if ((p->ldc % 4) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) args.flags |= kFlagVecStore;
+  args.status = p->status;
+  RB_CUDA(kv->launch(args, p->grid, st));
+  return ROLLER_OK;
+}
+
+int roller_b200_gemm_time(roller_plan* p, const float* A, const float* B, float* C, void* stream,
+                          int warmup, int iters, float* ms_per_iter) {
+  if (!p || !ms_per_iter || iters <= 0 || warmup < 0) return ROLLER_ERR_INVALID;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  for (int i = 0; i < warmup; ++i) {
+    int rc = roller_b200_gemm_run(p, A, B, C, stream);
+    if (rc != ROLLER_OK) return rc;
+  }
+  RB_CUDA(cudaStreamSynchronize(st));
+  RB_CUDA(cudaEventRecord(p->ev0, st));
+  for (int i = 0; i < iters; ++i) {
+    int rc = roller_b200_gemm_run(p, A, B, C, stream);
+    if (rc != ROLLER_OK) return rc;
+  }
+  RB_CUDA(cudaEventRecord(p->ev1, st));
+  RB_CUDA(cudaEventSynchronize(p->ev1));
+  float ms = 0.f;
+  RB_CUDA(cudaEventElapsedTime(&ms, p->ev0, p->ev1));
+  *ms_per_iter = ms / static_cast<float>(iters);
+  return ROLLER_OK;
+}
+
+int roller_b200_gemm_host(roller_plan* p, const float* hA, const float* hB, float* hC, void* stream) {
+  if (!p || !hA || !hB || !hC) return ROLLER_ERR_INVALID;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t a_bytes = sizeof(float) * static_cast<size_t>(p->lda) * p->M;
+  const size_t b_bytes = sizeof(float) * static_cast<size_t>(p->ldb) * p->K;
+  const size_t c_bytes = sizeof(float) * static_cast<size_t>(p->ldc) * p->M;
+  if (!p->hd_a) {
+    cudaError_t e = cudaMalloc(&p->hd_a, a_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&p->hd_b, b_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&p->hd_c, c_bytes);
+    if (e != cudaSuccess) {
+      cudaFree(p->hd_a); cudaFree(p->hd_b); cudaFree(p->hd_c);
+      p->hd_a = p->hd_b = p->hd_c = nullptr;
+      cudaGetLastError();
+      return ROLLER_ERR_NOMEM;
+    }
+  }
+  RB_CUDA(cudaMemcpyAsync(p->hd_a, hA, a_bytes, cudaMemcpyHostToDevice, st));
+  RB_CUDA(cudaMemcpyAsync(p->hd_b, hB, b_bytes, cudaMemcpyHostToDevice, st));
+  if (p->flags & ROLLER_FLAG_ACCUMULATE)
+    RB_CUDA(cudaMemcpyAsync(p->hd_c, hC, c_bytes, cudaMemcpyHostToDevice, st));
+  int rc = roller_b200_gemm_run(p, p->hd_a, p->hd_b, p->hd_c, stream);
+  if (rc != ROLLER_OK) return rc;
+  RB_CUDA(cudaMemcpyAsync(hC, p->hd_c, c_bytes, cudaMemcpyDeviceToHost, st));
+  RB_CUDA(cudaStreamSynchronize(st));
+  return ROLLER_OK;
+}
+
+int roller_b200_gemm_launch_info(const roller_plan* p, int* grid, int* block, int* smem_bytes,
+                                 int* tiles_m, int* tiles_n) {
+  if (!p) return ROLLER_ERR_INVALID;
+  if (grid) *grid = p->grid;
+  if (block) *block = p->kv->threads;
+  if (smem_bytes) *smem_bytes = p->kv->smem_bytes;
+  if (tiles_m) *tiles_m = p->tiles_m;
+  if (tiles_n) *tiles_n = p->tiles_n;
+  return ROLLER_OK;
+}
+
+int roller_b200_last_status(roller_plan* p, uint32_t* device_status) {
+  if (!p) return ROLLER_ERR_INVALID;
+  uint32_t h = 0;
+  RB_CUDA(cudaDeviceSynchronize());
+  RB_CUDA(cudaMemcpy(&h, p->status, sizeof(h), cudaMemcpyDeviceToHost));
+  if (device_status) *device_status = h;
+  return h == 0 ? ROLLER_OK : ROLLER_ERR_TIMEOUT;
+}
+
+int roller_b200_gemm_destroy(roller_plan* p) {
+  if (!p) return ROLLER_OK;
+  cudaFree(p->ws_a);
+  cudaFree(p->ws_b);
+  cudaFree(p->status);
+  cudaFree(p->hd_a);
+  cudaFree(p->hd_b);
+  cudaFree(p->hd_c);
+  if (p->ev0) cudaEventDestroy(p->ev0);
+  if (p->ev1) cudaEventDestroy(p->ev1);
+  cudaGetLastError();
+  delete p;
+  return ROLLER_OK;
+}
+
+const char* roller_b200_strerror(int status) {
+  switch (status) {
+    case ROLLER_OK: return "ok";
+    case ROLLER_ERR_INVALID: return "invalid argument";
+    case ROLLER_ERR_UNSUPPORTED: return "no compiled kernel for this rTile and mode";
+    case ROLLER_ERR_CUDA: return "CUDA call failed";
+    case ROLLER_ERR_DEVICE: return "current device is not an sm_100 GPU with enough shared memory";
+    case ROLLER_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+    case ROLLER_ERR_NOMEM: return "device memory allocation failed";
+    case ROLLER_ERR_TOO_LARGE: return "problem exceeds the capacity of this entry point";
+    default: return "unknown status";
+  }
+}
+
+const char* roller_b200_last_cuda_error(void) { return g_cuda_err; }
+
+}  // extern "C"

@@ -1,0 +1,44 @@
+// Host-side table of the compiled GEMM kernels (one per rTile x mode) and their launcher.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace rb200 {
+
+// Kernel flag bits (GemmArgs::flags).
+constexpr int kFlagAccumulate = 1;  // C += A@B instead of C = A@B
+constexpr int kFlagVecStore = 2;    // C rows are 16-byte aligned: use 128-bit stores
+
+struct GemmArgs {
+  CUtensorMap tmA;
+  CUtensorMap tmB;
+  float* C;
+  int M, N, K;
+  long long ldc;
+  int tiles_m, tiles_n;
+  int flags;
+  uint32_t* status;
+};
+
+struct KernelVariant {
+  int block_m;    // tile rows (128 * cta_group)
+  int block_n;    // tile columns
+  int rstep;      // k per stage
+  int cta_group;  // 1 or 2
+  int mode;       // 1 or 3
+  int stages;
+  int smem_bytes;
+  int tmem_cols;
+  int threads;
+  const void* func;  // kernel symbol, for cudaFuncSetAttribute / occupancy queries
+  cudaError_t (*launch)(const GemmArgs& args, int grid, cudaStream_t stream);
+};
+
+int variant_count();
+const KernelVariant& variant_at(int idx);
+// Returns nullptr when no kernel was compiled for the combination.
+const KernelVariant* find_variant(int block_m, int block_n, int rstep, int cta_group, int mode);
+
+}  // namespace rb200

@@ -1,0 +1,323 @@
+// fp32 GEMM C[M,N] = A[M,K] @ B[K,N] (all row-major) on the sm_100a tensor cores.
+//
+// This kernel family replaces the per-hint generated `gemm_kernel` of the reference
+// (schedule: src/roller.py:93-342, payload linalg.matmul: src/roller.py:47-68). One
+// instantiation exists per rTile the search may emit: block tile (128*CG) x BN, reduce step 32.
+//
+// Arithmetic: tcgen05.mma kind::tf32 with fp32 accumulation in TMEM.
+//   MODE 1 ("1xTF32"): one MMA per k-step on the raw fp32 words; the tensor core reads the top
+//          19 bits of each word.
+//   MODE 3 ("3xTF32"): each operand x is used as big(x) = the raw word (its low 13 bits are not
+//          read) and small(x) = x - trunc19(x), computed exactly in fp32 by the split warps and
+//          rounded to 19 bits; per k-step three MMAs small*big + big*small + big*big go into
+//          the same accumulator, which recovers fp32-level accuracy.
+//
+// Pipeline (one persistent CTA, or CTA pair when CG == 2, per SM):
+//   warp 0      TMA producer: A box 128x32 (K-major, 128B swizzle), B boxes 32x32
+//               (N contiguous, 128B swizzle on 32-byte chunks) into a STAGES-deep ring
+//   warps 6..   split warps (MODE 3) write the small parts next to the raw tiles; with a CTA
+//               pair they also forward "stage ready" to the leader CTA's barrier
+//   warp 1      MMA issuer (one thread, leader CTA only) + TMEM allocation
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator and store C with tail predicates
+// The accumulator is double-buffered in TMEM so the epilogue of tile i overlaps the main loop
+// of tile i+1. Ragged M/N/K need no special main loop: TMA zero-fills out-of-range elements.
+#pragma once
+
+#include "gemm_launch.h"
+#include "ptx_sm100.cuh"
+
+namespace rb200 {
+
+template <int BN_, int MODE_, int CG_>
+struct GemmCfg {
+  static constexpr int BN = BN_;      // tile columns (of the CTA pair when CG == 2)
+  static constexpr int MODE = MODE_;  // 1 or 3 tensor-core products per fp32 product
+  static constexpr int CG = CG_;      // CTAs cooperating on one tile (tcgen05 cta_group)
+  static constexpr int BM = 128;      // tile rows held by one CTA
+  static constexpr int BK = 32;       // reduce step: 32 fp32 = one 128-byte swizzle row
+  static constexpr int BNL = BN / CG; // B columns staged by one CTA
+  static constexpr int A_BYTES = BM * BK * 4;
+  static constexpr int B_BOX_BYTES = 32 * BK * 4;
+  static constexpr int B_BOXES = BNL / 32;
+  static constexpr int B_BYTES = B_BOXES * B_BOX_BYTES;
+  static constexpr int RAW_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGE_BYTES = (MODE == 3 ? 2 : 1) * RAW_BYTES;
+  static constexpr int CTRL_BYTES = 256;
+  static constexpr int SMEM_LIMIT = 232448;  // 227 KiB opt-in maximum per CTA
+  static constexpr int STAGES_FIT = (SMEM_LIMIT - 1024 - CTRL_BYTES) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + CTRL_BYTES + 1024;
+  static constexpr int ACC_STAGES = 2;
+  static constexpr int TMEM_COLS = ACC_STAGES * BN;
+  static constexpr bool HAS_XFORM = (MODE == 3) || (CG == 2);
+  static constexpr int XFORM_WARPS = (MODE == 3) ? 4 : 1;
+  static constexpr int FIRST_XFORM_WARP = 6;
+  static constexpr int THREADS = (FIRST_XFORM_WARP + (HAS_XFORM ? XFORM_WARPS : 0)) * 32;
+  static constexpr int MMA_M = BM * CG;
+  static constexpr int TILE_M = BM * CG;
+
+  static_assert(BN % (32 * CG) == 0, "each CTA stages whole 32-column boxes of B");
+  static_assert(TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "power of two");
+  static_assert(STAGES >= 2, "need at least a double buffer");
+  static_assert(RAW_BYTES % 1024 == 0, "swizzle atoms must stay 1024-byte aligned");
+};
+
+// Tile order: walk the output in panels of 8 tile-rows so that concurrently running CTAs
+// share A row panels and B column panels in L2 (the reference swizzles thread blocks with
+// panel width 8 for the same reason, src/roller.py:334-339).
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& mb, int& nb) {
+  constexpr int kPanel = 8;
+  const int per_panel = kPanel * tiles_n;
+  const int panel = t / per_panel;
+  const int first_m = panel * kPanel;
+  const int rows = min(tiles_m - first_m, kPanel);
+  const int r = t - panel * per_panel;
+  mb = first_m + r % rows;
+  nb = r / rows;
+}
+
+// small(x) = x - trunc19(x), then rounded to nearest on the 19-bit grid the tensor core reads.
+__device__ __forceinline__ uint32_t split_small(uint32_t xb) {
+  const float x = __uint_as_float(xb);
+  const float big = __uint_as_float(xb & 0xFFFFE000u);
+  float s = x - big;
+  if ((xb & 0x7F800000u) == 0x7F800000u) s = 0.0f;  // inf/nan stay in the big part only
+  return __float_as_uint(s) + 0x1000u;
+}
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
+gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 float* __restrict__ C, int M, int N, int K, long long ldc, int tiles_m,
+                 int tiles_n, int flags, uint32_t* status) {
+  constexpr int BN = Cfg::BN, BK = Cfg::BK, CG = Cfg::CG, STAGES = Cfg::STAGES;
+
+  extern __shared__ uint8_t smem_dyn[];
+  const uint32_t smem_dyn_addr = smem_addr(smem_dyn);
+  const uint32_t smem_base = (smem_dyn_addr + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_dyn + (smem_base - smem_dyn_addr);
+
+  const uint32_t ctrl = smem_base + STAGES * Cfg::STAGE_BYTES;
+  auto full_bar = [&](int s) { return ctrl + 8u * s; };         // TMA bytes landed (per CTA)
+  auto ready_bar = [&](int s) { return ctrl + 64u + 8u * s; };  // stage usable by MMA (leader)
+  auto empty_bar = [&](int s) { return ctrl + 128u + 8u * s; }; // MMAs done reading (per CTA)
+  auto tmem_full_bar = [&](int a) { return ctrl + 192u + 8u * a; };
+  auto tmem_empty_bar = [&](int a) { return ctrl + 208u + 8u * a; };
+  const uint32_t tmem_slot = ctrl + 224u;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
+  const bool is_leader = (cta_rank == 0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(ready_bar(s), CG * Cfg::XFORM_WARPS);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < Cfg::ACC_STAGES; ++a) {
+      mbar_init(tmem_full_bar(a), 1);
+      mbar_init(tmem_empty_bar(a), CG * 4);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) tmem_alloc<CG>(tmem_slot, Cfg::TMEM_COLS);
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  tcgen05_fence_before_sync();
+  if constexpr (CG == 2) cluster_sync(); else __syncthreads();
+  tcgen05_fence_after_sync();
+
+  uint32_t tmem_base;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_workers = gridDim.x / CG;
+  const int worker = blockIdx.x / CG;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = worker; t < num_tiles && ok; t += num_workers) {
+        int mb, nb;
+        tile_coords(t, tiles_m, tiles_n, mb, nb);
+        const int m0 = (mb * CG + static_cast<int>(cta_rank)) * Cfg::BM;
+        const int n0 = nb * BN + static_cast<int>(cta_rank) * Cfg::BNL;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, status, kDevTimeoutEmpty)) { ok = false; break; }
+          mbar_expect_tx(full_bar(s), Cfg::RAW_BYTES);
+          const uint32_t a_dst = smem_base + s * Cfg::STAGE_BYTES;
+          const uint32_t b_dst = a_dst + Cfg::A_BYTES;
+          tma_load_2d(a_dst, &tmA, full_bar(s), kb * BK, m0);
+#pragma unroll
+          for (int j = 0; j < Cfg::B_BOXES; ++j)
+            tma_load_2d(b_dst + j * Cfg::B_BOX_BYTES, &tmB, full_bar(s), n0 + j * 32, kb * BK);
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+      }
+      // Tail: the MMA issuer's last releases must land in this CTA before it may exit.
+      for (int i = 0; i < STAGES && ok; ++i) {
+        ok = mbar_wait(empty_bar(s), ph ^ 1u, status, kDevTimeoutTail);
+        if (++s == STAGES) { s = 0; ph ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0 && is_leader) {
+      constexpr uint32_t idesc = make_idesc_tf32(Cfg::MMA_M, BN);
+      int s = 0;
+      uint32_t ph = 0;
+      int acc = 0;
+      uint32_t acc_ph = 0;
+      bool ok = true;
+      for (int t = worker; t < num_tiles && ok; t += num_workers) {
+        if (!mbar_wait<CG == 2>(tmem_empty_bar(acc), acc_ph ^ 1u, status, kDevTimeoutTmemEmpty)) break;
+        tcgen05_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          const uint32_t wait_bar = Cfg::HAS_XFORM ? ready_bar(s) : full_bar(s);
+          if (!mbar_wait<CG == 2>(wait_bar, ph, status, kDevTimeoutReady)) { ok = false; break; }
+          tcgen05_fence_after_sync();
+          const uint32_t stage = smem_base + s * Cfg::STAGE_BYTES;
+          // A: rows of 128 B, 8-row swizzle atoms 1024 B apart.
+          const uint64_t a_raw = make_smem_desc(stage, 16, 1024, kLayoutSw128);
+          // B: rows (one k each) of 128 B = 32 columns; 4-row swizzle atoms 512 B apart along K,
+          // next 32 columns one whole box further.
+          const uint64_t b_raw =
+              make_smem_desc(stage + Cfg::A_BYTES, Cfg::B_BOX_BYTES, 512, kLayoutSw128Base32);
+          const uint64_t a_sml = make_smem_desc(stage + Cfg::RAW_BYTES, 16, 1024, kLayoutSw128);
+          const uint64_t b_sml = make_smem_desc(stage + Cfg::RAW_BYTES + Cfg::A_BYTES,
+                                                Cfg::B_BOX_BYTES, 512, kLayoutSw128Base32);
+#pragma unroll
+          for (int kk = 0; kk < BK / 8; ++kk) {
+            // One MMA consumes 8 k: 32 bytes along an A row, 8 rows (1024 bytes) of a B box.
+            const uint64_t a_off = static_cast<uint64_t>(kk * 2);
+            const uint64_t b_off = static_cast<uint64_t>(kk * 64);
+            const uint32_t first = (kb | kk) != 0 ? 1u : 0u;
+            if constexpr (Cfg::MODE == 3) {
+              umma_tf32<CG>(d_tmem, a_sml + a_off, b_raw + b_off, idesc, first);
+              umma_tf32<CG>(d_tmem, a_raw + a_off, b_sml + b_off, idesc, 1u);
+              umma_tf32<CG>(d_tmem, a_raw + a_off, b_raw + b_off, idesc, 1u);
+            } else {
+              umma_tf32<CG>(d_tmem, a_raw + a_off, b_raw + b_off, idesc, first);
+            }
+          }
+          umma_commit<CG>(empty_bar(s));
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+        if (ok) umma_commit<CG>(tmem_full_bar(acc));
+        acc ^= 1;
+        if (acc == 0) acc_ph ^= 1u;
+      }
+    }
+  } else if (warp < Cfg::FIRST_XFORM_WARP) {
+    // ------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;  // TMEM lanes a warp may read: 32 * (warp id mod 4)
+    const bool accumulate = (flags & kFlagAccumulate) != 0;
+    const bool vec_store = (flags & kFlagVecStore) != 0;
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    for (int t = worker; t < num_tiles; t += num_workers) {
+      int mb, nb;
+      tile_coords(t, tiles_m, tiles_n, mb, nb);
+      const int row = (mb * CG + static_cast<int>(cta_rank)) * Cfg::BM + quarter * 32 + lane;
+      const int n0 = nb * BN;
+      if (!mbar_wait(tmem_full_bar(acc), acc_ph, status, kDevTimeoutTmemFull)) break;
+      tcgen05_fence_after_sync();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                             static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < M && col0 < N) {
+          float* dst = C + static_cast<size_t>(row) * static_cast<size_t>(ldc) + col0;
+          if (vec_store && col0 + 32 <= N) {
+            float4* dst4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 o = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                     __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+              if (accumulate) {
+                const float4 old = dst4[j];
+                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              }
+              dst4[j] = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col0 + j < N) {
+                float o = __uint_as_float(v[j]);
+                if (accumulate) o += dst[j];
+                dst[j] = o;
+              }
+            }
+          }
+        }
+      }
+      tcgen05_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (CG == 2) mbar_arrive_cluster(tmem_empty_bar(acc), 0);
+        else mbar_arrive(tmem_empty_bar(acc));
+      }
+      acc ^= 1;
+      if (acc == 0) acc_ph ^= 1u;
+    }
+  } else if constexpr (Cfg::HAS_XFORM) {
+    // ------------------------------------------------------------ split / relay warps
+    constexpr int XT = Cfg::XFORM_WARPS * 32;
+    const int xt = threadIdx.x - Cfg::FIRST_XFORM_WARP * 32;
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int t = worker; t < num_tiles && ok; t += num_workers) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(full_bar(s), ph, status, kDevTimeoutFull)) { ok = false; break; }
+        if constexpr (Cfg::MODE == 3) {
+          // Element-wise, so the swizzled placement of the raw tile carries over unchanged.
+          const uint4* src = reinterpret_cast<const uint4*>(smem_gen + s * Cfg::STAGE_BYTES);
+          uint4* dst = reinterpret_cast<uint4*>(smem_gen + s * Cfg::STAGE_BYTES + Cfg::RAW_BYTES);
+          constexpr int kVecs = Cfg::RAW_BYTES / 16;
+          static_assert(kVecs % XT == 0, "whole passes");
+#pragma unroll 8
+          for (int i = 0; i < kVecs / XT; ++i) {
+            const uint4 x = src[i * XT + xt];
+            uint4 y;
+            y.x = split_small(x.x); y.y = split_small(x.y);
+            y.z = split_small(x.z); y.w = split_small(x.w);
+            dst[i * XT + xt] = y;
+          }
+          fence_proxy_async_smem();
+        }
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (CG == 2) mbar_arrive_cluster(ready_bar(s), 0);
+          else mbar_arrive(ready_bar(s));
+        }
+        if (++s == STAGES) { s = 0; ph ^= 1u; }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  __syncwarp();
+  tcgen05_fence_before_sync();
+  if constexpr (CG == 2) cluster_sync(); else __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after_sync();
+    tmem_dealloc<CG>(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+}  // namespace rb200
