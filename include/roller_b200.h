@@ -112,7 +112,17 @@ int roller_b200_gemm_host(roller_plan* plan, const float* hA, const float* hB, f
 /* Launch geometry the plan chose (the reference derives grid/block from the hint,
  * src/roller.py:536-543). Any out pointer may be NULL. */
 int roller_b200_gemm_launch_info(const roller_plan* plan, int* grid, int* block, int* smem_bytes,
-                                 int* tiles_m, int* tiles_n);
+                                 int* tiles_m, int* tiles_n, int* max_clusters);
+
+/* Accumulation chunk of the 3xTF32 mode: the TMEM accumulator is drained into fp32 registers
+ * every `k_elems` elements of the reduction (rounded up to whole 32-element steps; 0 = never,
+ * one chunk spans K). Shorter chunks cost more drains and give a smaller rounding error. The
+ * reference's kernels accumulate in fp32 registers throughout (src/roller.py:280-282). */
+int roller_b200_gemm_set_chunk(roller_plan* plan, int k_elems);
+
+/* Overrides the number of persistent CTAs (a multiple of cta_group, at most the SM count and
+ * at most one per tile). The reference derives its grid from the hint (src/roller.py:536). */
+int roller_b200_gemm_set_grid(roller_plan* plan, int ctas);
 
 /* Reads back the device status word of the plan (0 = all bounded waits completed); returns
  * ROLLER_ERR_TIMEOUT when it is non-zero. Synchronises the device. */

@@ -66,7 +66,9 @@ SIGNATURES = {
     "roller_b200_gemm_time": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                         C.c_int, C.c_int, C.POINTER(C.c_float)]),
     "roller_b200_gemm_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
-    "roller_b200_gemm_launch_info": (C.c_int, [C.c_void_p] + [C.POINTER(C.c_int)] * 5),
+    "roller_b200_gemm_launch_info": (C.c_int, [C.c_void_p] + [C.POINTER(C.c_int)] * 6),
+    "roller_b200_gemm_set_chunk": (C.c_int, [C.c_void_p, C.c_int]),
+    "roller_b200_gemm_set_grid": (C.c_int, [C.c_void_p, C.c_int]),
     "roller_b200_last_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32)]),
     "roller_b200_gemm_destroy": (C.c_int, [C.c_void_p]),
     "roller_b200_strerror": (C.c_char_p, [C.c_int]),
@@ -182,11 +184,17 @@ class GemmPlan:
         check(self._lib.roller_b200_gemm_host(self._h, ptr(hA), ptr(hB), ptr(hC),
                                               _stream_ptr(stream)), "roller_b200_gemm_host")
 
+    def set_chunk(self, k_elems: int) -> None:
+        check(self._lib.roller_b200_gemm_set_chunk(self._h, k_elems), "roller_b200_gemm_set_chunk")
+
+    def set_grid(self, ctas: int) -> None:
+        check(self._lib.roller_b200_gemm_set_grid(self._h, ctas), "roller_b200_gemm_set_grid")
+
     def launch_info(self) -> dict:
-        vals = [C.c_int() for _ in range(5)]
+        vals = [C.c_int() for _ in range(6)]
         check(self._lib.roller_b200_gemm_launch_info(self._h, *[C.byref(v) for v in vals]),
               "roller_b200_gemm_launch_info")
-        keys = ("grid", "block", "smem_bytes", "tiles_m", "tiles_n")
+        keys = ("grid", "block", "smem_bytes", "tiles_m", "tiles_n", "max_clusters")
         return {k: v.value for k, v in zip(keys, vals)}
 
     def device_status(self) -> int:

@@ -94,6 +94,8 @@ struct roller_plan {
   long long lda, ldb, ldc;
   int mode, flags;
   int tiles_m, tiles_n, grid;
+  int chunk_kb;           // accumulation chunk, in 32-element k-blocks
+  int max_clusters;       // co-resident CTA pairs the device reports (cta_group 2 only)
   bool stage_a, stage_b;  // operands go through a padded copy
   float* ws_a;            // padded copies (device), owned
   float* ws_b;
@@ -190,11 +192,35 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
   const long long tiles = static_cast<long long>(p->tiles_m) * p->tiles_n;
   const int workers = p->sm_count / kv->cta_group;
   p->grid = static_cast<int>(tiles < workers ? tiles : workers) * kv->cta_group;
+  // 3xTF32 drains the TMEM accumulator every 128 k (see the kernel header); 1xTF32 is
+  // dominated by the 10-bit input mantissa, so one chunk spans the whole reduction.
+  const int num_kb = (K + kv->rstep - 1) / kv->rstep;
+  p->chunk_kb = (mode == ROLLER_MODE_3XTF32) ? 4 : num_kb;
   p->stage_a = (lda % 4) != 0;
   p->stage_b = (ldb % 4) != 0;
 
   cudaError_t e = cudaFuncSetAttribute(kv->func, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kv->smem_bytes);
+  if (e == cudaSuccess && kv->cta_group == 2) {
+    // A persistent grid must be co-resident: ask how many CTA pairs the device can hold.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(p->sm_count), 1, 1);
+    cfg.blockDim = dim3(static_cast<unsigned>(kv->threads), 1, 1);
+    cfg.dynamicSmemBytes = static_cast<size_t>(kv->smem_bytes);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, kv->func, &cfg);
+    if (e == cudaSuccess) {
+      p->max_clusters = n;
+      if (n > 0 && p->grid > 2 * n) p->grid = 2 * n;
+    }
+  }
   if (e == cudaSuccess) e = cudaMalloc(&p->status, sizeof(uint32_t));
   if (e == cudaSuccess) e = cudaMemset(p->status, 0, sizeof(uint32_t));
   if (e == cudaSuccess && p->stage_a) {
@@ -263,6 +289,7 @@ int roller_b200_gemm_run(roller_plan* p, const float* A, const float* B, float* 
   args.ldc = p->ldc;
   args.tiles_m = p->tiles_m;
   args.tiles_n = p->tiles_n;
+  args.chunk_kb = p->chunk_kb;
   args.flags = (p->flags & ROLLER_FLAG_ACCUMULATE) ? kFlagAccumulate : 0;
   if ((p->ldc % 4) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) args.flags |= kFlagVecStore;
   args.status = p->status;
@@ -321,13 +348,32 @@ int roller_b200_gemm_host(roller_plan* p, const float* hA, const float* hB, floa
 }
 
 int roller_b200_gemm_launch_info(const roller_plan* p, int* grid, int* block, int* smem_bytes,
-                                 int* tiles_m, int* tiles_n) {
+                                 int* tiles_m, int* tiles_n, int* max_clusters) {
   if (!p) return ROLLER_ERR_INVALID;
   if (grid) *grid = p->grid;
   if (block) *block = p->kv->threads;
   if (smem_bytes) *smem_bytes = p->kv->smem_bytes;
   if (tiles_m) *tiles_m = p->tiles_m;
   if (tiles_n) *tiles_n = p->tiles_n;
+  if (max_clusters) *max_clusters = p->max_clusters;
+  return ROLLER_OK;
+}
+
+int roller_b200_gemm_set_chunk(roller_plan* p, int k_elems) {
+  if (!p || k_elems < 0) return ROLLER_ERR_INVALID;
+  const int num_kb = (p->K + p->kv->rstep - 1) / p->kv->rstep;
+  int kb = (k_elems == 0) ? num_kb : (k_elems + p->kv->rstep - 1) / p->kv->rstep;
+  if (kb < 1) kb = 1;
+  if (kb > num_kb) kb = num_kb;
+  p->chunk_kb = kb;
+  return ROLLER_OK;
+}
+
+int roller_b200_gemm_set_grid(roller_plan* p, int ctas) {
+  if (!p || ctas <= 0 || ctas % p->kv->cta_group != 0) return ROLLER_ERR_INVALID;
+  const long long tiles = static_cast<long long>(p->tiles_m) * p->tiles_n;
+  if (ctas > p->sm_count || ctas / p->kv->cta_group > tiles) return ROLLER_ERR_INVALID;
+  p->grid = ctas;
   return ROLLER_OK;
 }
 

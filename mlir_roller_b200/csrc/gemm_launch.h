@@ -18,6 +18,7 @@ struct GemmArgs {
   int M, N, K;
   long long ldc;
   int tiles_m, tiles_n;
+  int chunk_kb;  // k-blocks accumulated in TMEM before a drain into registers
   int flags;
   uint32_t* status;
 };

@@ -6,21 +6,27 @@
 //
 // Arithmetic: tcgen05.mma kind::tf32 with fp32 accumulation in TMEM.
 //   MODE 1 ("1xTF32"): one MMA per k-step on the raw fp32 words; the tensor core reads the top
-//          19 bits of each word.
+//          19 bits of each word (truncation, measured on B200).
 //   MODE 3 ("3xTF32"): each operand x is used as big(x) = the raw word (its low 13 bits are not
 //          read) and small(x) = x - trunc19(x), computed exactly in fp32 by the split warps and
 //          rounded to 19 bits; per k-step three MMAs small*big + big*small + big*big go into
-//          the same accumulator, which recovers fp32-level accuracy.
+//          the same accumulator.
+// The TMEM accumulator rounds toward zero on every MMA, which on B200 shows up as an error that
+// grows linearly with the number of MMAs chained into one accumulator (1.7e-5 of max|C| at
+// K = 2048 in 3xTF32). The reduction is therefore cut into chunks of `chunk_kb` k-blocks: each
+// chunk is accumulated in TMEM from zero, then drained by the epilogue warps into fp32
+// registers with round-to-nearest adds while the next chunk runs in the other TMEM buffer.
 //
-// Pipeline (one persistent CTA, or CTA pair when CG == 2, per SM):
-//   warp 0      TMA producer: A box 128x32 (K-major, 128B swizzle), B boxes 32x32
-//               (N contiguous, 128B swizzle on 32-byte chunks) into a STAGES-deep ring
-//   warps 6..   split warps (MODE 3) write the small parts next to the raw tiles; with a CTA
-//               pair they also forward "stage ready" to the leader CTA's barrier
-//   warp 1      MMA issuer (one thread, leader CTA only) + TMEM allocation
-//   warps 2..5  epilogue: tcgen05.ld the finished accumulator and store C with tail predicates
-// The accumulator is double-buffered in TMEM so the epilogue of tile i overlaps the main loop
-// of tile i+1. Ragged M/N/K need no special main loop: TMA zero-fills out-of-range elements.
+// Pipeline (one persistent CTA, or CTA pair when CG == 2, per SM; 16 warps):
+//   warp 0        TMA producer: A box 128x32 (K-major, 128B swizzle), B boxes 32x32
+//                 (N contiguous, 128B swizzle on 32-byte chunks) into a STAGES-deep ring
+//   warp 1        MMA issuer (one thread, leader CTA only) + TMEM allocation
+//   warps 4..11   accumulate/epilogue: warp w owns TMEM lanes 32*(w%4).. and one half of the
+//                 tile's columns; sums chunk results in registers, stores C with tail predicates
+//   warps 12..15  split warps (MODE 3) write the small parts next to the raw tiles and tell the
+//                 leader CTA's barrier that the stage is ready
+// With a CTA pair in MODE 1 both CTAs' TMA loads report straight to the leader's barrier.
+// Ragged M/N/K need no special main loop: TMA zero-fills out-of-range elements.
 #pragma once
 
 #include "gemm_launch.h"
@@ -49,17 +55,27 @@ struct GemmCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + CTRL_BYTES + 1024;
   static constexpr int ACC_STAGES = 2;
   static constexpr int TMEM_COLS = ACC_STAGES * BN;
-  static constexpr bool HAS_XFORM = (MODE == 3) || (CG == 2);
-  static constexpr int XFORM_WARPS = (MODE == 3) ? 4 : 1;
-  static constexpr int FIRST_XFORM_WARP = 6;
-  static constexpr int THREADS = (FIRST_XFORM_WARP + (HAS_XFORM ? XFORM_WARPS : 0)) * 32;
+  static constexpr bool HAS_XFORM = (MODE == 3);
+  static constexpr int XFORM_WARPS = 4;
+  static constexpr int FIRST_EPI_WARP = 4;
+  static constexpr int EPI_WARPS = 8;
+  static constexpr int FIRST_XFORM_WARP = 12;
+  static constexpr int THREADS = 512;
+  static constexpr int EPI_COLS = BN / 2;  // accumulator columns one epilogue thread owns
   static constexpr int MMA_M = BM * CG;
   static constexpr int TILE_M = BM * CG;
+  // Register rebalancing between warpgroups (only the widest tile needs it): 512 threads get
+  // 128 registers each at launch; the control and split warpgroups give some back so that the
+  // two accumulate warpgroups can hold 128 accumulators per thread.
+  static constexpr bool REBALANCE = (EPI_COLS > 64);
+  static constexpr int REGS_CTRL = 64, REGS_XFORM = 80, REGS_EPI = 184;
 
   static_assert(BN % (32 * CG) == 0, "each CTA stages whole 32-column boxes of B");
+  static_assert(EPI_COLS % 32 == 0, "epilogue threads read whole 32-column slabs");
   static_assert(TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "power of two");
   static_assert(STAGES >= 2, "need at least a double buffer");
   static_assert(RAW_BYTES % 1024 == 0, "swizzle atoms must stay 1024-byte aligned");
+  static_assert(4 * (REGS_CTRL + REGS_XFORM + 2 * REGS_EPI) * 32 <= 65536, "register file");
 };
 
 // Tile order: walk the output in panels of 8 tile-rows so that concurrently running CTAs
@@ -85,11 +101,20 @@ __device__ __forceinline__ uint32_t split_small(uint32_t xb) {
   return __float_as_uint(s) + 0x1000u;
 }
 
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  float* __restrict__ C, int M, int N, int K, long long ldc, int tiles_m,
-                 int tiles_n, int flags, uint32_t* status) {
+                 int tiles_n, int chunk_kb, int flags, uint32_t* status) {
   constexpr int BN = Cfg::BN, BK = Cfg::BK, CG = Cfg::CG, STAGES = Cfg::STAGES;
 
   extern __shared__ uint8_t smem_dyn[];
@@ -118,7 +143,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int a = 0; a < Cfg::ACC_STAGES; ++a) {
       mbar_init(tmem_full_bar(a), 1);
-      mbar_init(tmem_empty_bar(a), CG * 4);
+      mbar_init(tmem_empty_bar(a), CG * Cfg::EPI_WARPS);
     }
     fence_barrier_init();
   }
@@ -139,9 +164,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int worker = blockIdx.x / CG;
   const int num_kb = (K + BK - 1) / BK;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+  if (warp < Cfg::FIRST_EPI_WARP) {
+    if constexpr (Cfg::REBALANCE) setmaxnreg_dec<Cfg::REGS_CTRL>();
+    if (warp == 0 && lane == 0) {
+      // ---------------------------------------------------------- TMA producer
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -152,13 +178,23 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int n0 = nb * BN + static_cast<int>(cta_rank) * Cfg::BNL;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(s), ph ^ 1u, status, kDevTimeoutEmpty)) { ok = false; break; }
-          mbar_expect_tx(full_bar(s), Cfg::RAW_BYTES);
           const uint32_t a_dst = smem_base + s * Cfg::STAGE_BYTES;
           const uint32_t b_dst = a_dst + Cfg::A_BYTES;
-          tma_load_2d(a_dst, &tmA, full_bar(s), kb * BK, m0);
+          if constexpr (CG == 2 && !Cfg::HAS_XFORM) {
+            // The leader's barrier counts the bytes of both CTAs; only the leader arms it.
+            if (is_leader) mbar_expect_tx(full_bar(s), 2 * Cfg::RAW_BYTES);
+            const uint32_t bar = map_to_cta(full_bar(s), 0);
+            tma_load_2d_pair(a_dst, &tmA, bar, kb * BK, m0);
 #pragma unroll
-          for (int j = 0; j < Cfg::B_BOXES; ++j)
-            tma_load_2d(b_dst + j * Cfg::B_BOX_BYTES, &tmB, full_bar(s), n0 + j * 32, kb * BK);
+            for (int j = 0; j < Cfg::B_BOXES; ++j)
+              tma_load_2d_pair(b_dst + j * Cfg::B_BOX_BYTES, &tmB, bar, n0 + j * 32, kb * BK);
+          } else {
+            mbar_expect_tx(full_bar(s), Cfg::RAW_BYTES);
+            tma_load_2d(a_dst, &tmA, full_bar(s), kb * BK, m0);
+#pragma unroll
+            for (int j = 0; j < Cfg::B_BOXES; ++j)
+              tma_load_2d(b_dst + j * Cfg::B_BOX_BYTES, &tmB, full_bar(s), n0 + j * 32, kb * BK);
+          }
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
       }
@@ -167,10 +203,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         ok = mbar_wait(empty_bar(s), ph ^ 1u, status, kDevTimeoutTail);
         if (++s == STAGES) { s = 0; ph ^= 1u; }
       }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0 && is_leader) {
+    } else if (warp == 1 && lane == 0 && is_leader) {
+      // ---------------------------------------------------------- MMA issuer
       constexpr uint32_t idesc = make_idesc_tf32(Cfg::MMA_M, BN);
       int s = 0;
       uint32_t ph = 0;
@@ -178,75 +212,115 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t acc_ph = 0;
       bool ok = true;
       for (int t = worker; t < num_tiles && ok; t += num_workers) {
-        if (!mbar_wait<CG == 2>(tmem_empty_bar(acc), acc_ph ^ 1u, status, kDevTimeoutTmemEmpty)) break;
-        tcgen05_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-        for (int kb = 0; kb < num_kb; ++kb) {
-          const uint32_t wait_bar = Cfg::HAS_XFORM ? ready_bar(s) : full_bar(s);
-          if (!mbar_wait<CG == 2>(wait_bar, ph, status, kDevTimeoutReady)) { ok = false; break; }
-          tcgen05_fence_after_sync();
-          const uint32_t stage = smem_base + s * Cfg::STAGE_BYTES;
-          // A: rows of 128 B, 8-row swizzle atoms 1024 B apart.
-          const uint64_t a_raw = make_smem_desc(stage, 16, 1024, kLayoutSw128);
-          // B: rows (one k each) of 128 B = 32 columns; 4-row swizzle atoms 512 B apart along K,
-          // next 32 columns one whole box further.
-          const uint64_t b_raw =
-              make_smem_desc(stage + Cfg::A_BYTES, Cfg::B_BOX_BYTES, 512, kLayoutSw128Base32);
-          const uint64_t a_sml = make_smem_desc(stage + Cfg::RAW_BYTES, 16, 1024, kLayoutSw128);
-          const uint64_t b_sml = make_smem_desc(stage + Cfg::RAW_BYTES + Cfg::A_BYTES,
-                                                Cfg::B_BOX_BYTES, 512, kLayoutSw128Base32);
-#pragma unroll
-          for (int kk = 0; kk < BK / 8; ++kk) {
-            // One MMA consumes 8 k: 32 bytes along an A row, 8 rows (1024 bytes) of a B box.
-            const uint64_t a_off = static_cast<uint64_t>(kk * 2);
-            const uint64_t b_off = static_cast<uint64_t>(kk * 64);
-            const uint32_t first = (kb | kk) != 0 ? 1u : 0u;
-            if constexpr (Cfg::MODE == 3) {
-              umma_tf32<CG>(d_tmem, a_sml + a_off, b_raw + b_off, idesc, first);
-              umma_tf32<CG>(d_tmem, a_raw + a_off, b_sml + b_off, idesc, 1u);
-              umma_tf32<CG>(d_tmem, a_raw + a_off, b_raw + b_off, idesc, 1u);
-            } else {
-              umma_tf32<CG>(d_tmem, a_raw + a_off, b_raw + b_off, idesc, first);
-            }
+        for (int kb0 = 0; kb0 < num_kb && ok; kb0 += chunk_kb) {
+          const int kb1 = min(kb0 + chunk_kb, num_kb);
+          if (!mbar_wait(tmem_empty_bar(acc), acc_ph ^ 1u, status, kDevTimeoutTmemEmpty)) {
+            ok = false;
+            break;
           }
-          umma_commit<CG>(empty_bar(s));
-          if (++s == STAGES) { s = 0; ph ^= 1u; }
+          tcgen05_fence_after_sync();
+          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+          for (int kb = kb0; kb < kb1; ++kb) {
+            const uint32_t wait_bar = Cfg::HAS_XFORM ? ready_bar(s) : full_bar(s);
+            if (!mbar_wait(wait_bar, ph, status, kDevTimeoutReady)) { ok = false; break; }
+            tcgen05_fence_after_sync();
+            const uint32_t stage = smem_base + s * Cfg::STAGE_BYTES;
+            // A: rows of 128 B, 8-row swizzle atoms 1024 B apart.
+            const uint64_t a_raw = make_smem_desc(stage, 16, 1024, kLayoutSw128);
+            // B: rows (one k each) of 128 B = 32 columns; 4-row swizzle atoms 512 B apart along
+            // K, the next 32 columns one whole box further.
+            const uint64_t b_raw =
+                make_smem_desc(stage + Cfg::A_BYTES, Cfg::B_BOX_BYTES, 512, kLayoutSw128Base32);
+            // One MMA consumes 8 k: 32 bytes along an A row, 8 rows (1024 bytes) of a B box.
+            if constexpr (Cfg::MODE == 3) {
+              const uint64_t a_sml = make_smem_desc(stage + Cfg::RAW_BYTES, 16, 1024, kLayoutSw128);
+              const uint64_t b_sml = make_smem_desc(stage + Cfg::RAW_BYTES + Cfg::A_BYTES,
+                                                    Cfg::B_BOX_BYTES, 512, kLayoutSw128Base32);
+              // Correction terms first: they are 2^-11 of the main term, so adding them while
+              // the accumulator is still small costs the least rounding.
+#pragma unroll
+              for (int kk = 0; kk < BK / 8; ++kk) {
+                const uint64_t a_off = static_cast<uint64_t>(kk * 2);
+                const uint64_t b_off = static_cast<uint64_t>(kk * 64);
+                umma_tf32<CG>(d_tmem, a_sml + a_off, b_raw + b_off, idesc,
+                              (kb != kb0 || kk != 0) ? 1u : 0u);
+                umma_tf32<CG>(d_tmem, a_raw + a_off, b_sml + b_off, idesc, 1u);
+              }
+#pragma unroll
+              for (int kk = 0; kk < BK / 8; ++kk)
+                umma_tf32<CG>(d_tmem, a_raw + static_cast<uint64_t>(kk * 2),
+                              b_raw + static_cast<uint64_t>(kk * 64), idesc, 1u);
+            } else {
+#pragma unroll
+              for (int kk = 0; kk < BK / 8; ++kk)
+                umma_tf32<CG>(d_tmem, a_raw + static_cast<uint64_t>(kk * 2),
+                              b_raw + static_cast<uint64_t>(kk * 64), idesc,
+                              (kb != kb0 || kk != 0) ? 1u : 0u);
+            }
+            umma_commit<CG>(empty_bar(s));
+            if (++s == STAGES) { s = 0; ph ^= 1u; }
+          }
+          if (ok) umma_commit<CG>(tmem_full_bar(acc));
+          acc ^= 1;
+          if (acc == 0) acc_ph ^= 1u;
         }
-        if (ok) umma_commit<CG>(tmem_full_bar(acc));
-        acc ^= 1;
-        if (acc == 0) acc_ph ^= 1u;
       }
     }
   } else if (warp < Cfg::FIRST_XFORM_WARP) {
-    // ------------------------------------------------------------ epilogue
+    // ------------------------------------------------------------ accumulate + epilogue
+    if constexpr (Cfg::REBALANCE) setmaxnreg_inc<Cfg::REGS_EPI>();
+    constexpr int COLS = Cfg::EPI_COLS;
     const int quarter = warp & 3;  // TMEM lanes a warp may read: 32 * (warp id mod 4)
+    const int half = (warp - Cfg::FIRST_EPI_WARP) >> 2;
     const bool accumulate = (flags & kFlagAccumulate) != 0;
     const bool vec_store = (flags & kFlagVecStore) != 0;
     int acc = 0;
     uint32_t acc_ph = 0;
-    for (int t = worker; t < num_tiles; t += num_workers) {
+    bool ok = true;
+    float sum[COLS];
+    for (int t = worker; t < num_tiles && ok; t += num_workers) {
       int mb, nb;
       tile_coords(t, tiles_m, tiles_n, mb, nb);
       const int row = (mb * CG + static_cast<int>(cta_rank)) * Cfg::BM + quarter * 32 + lane;
-      const int n0 = nb * BN;
-      if (!mbar_wait(tmem_full_bar(acc), acc_ph, status, kDevTimeoutTmemFull)) break;
-      tcgen05_fence_after_sync();
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                             static_cast<uint32_t>(acc * BN);
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_row + static_cast<uint32_t>(c * 32), v);
-        tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        if (row < M && col0 < N) {
-          float* dst = C + static_cast<size_t>(row) * static_cast<size_t>(ldc) + col0;
+      const int n0 = nb * BN + half * COLS;
+#pragma unroll
+      for (int j = 0; j < COLS; ++j) sum[j] = 0.0f;
+      for (int kb0 = 0; kb0 < num_kb; kb0 += chunk_kb) {
+        if (!mbar_wait(tmem_full_bar(acc), acc_ph, status, kDevTimeoutTmemFull)) { ok = false; break; }
+        tcgen05_fence_after_sync();
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                               static_cast<uint32_t>(acc * BN + half * COLS);
+#pragma unroll
+        for (int c = 0; c < COLS / 16; ++c) {
+          uint32_t v[16];
+          tmem_ld_32x16(t_row + static_cast<uint32_t>(c * 16), v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) sum[c * 16 + j] += __uint_as_float(v[j]);
+        }
+        tcgen05_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (CG == 2) mbar_arrive_cluster(tmem_empty_bar(acc), 0);
+          else mbar_arrive(tmem_empty_bar(acc));
+        }
+        acc ^= 1;
+        if (acc == 0) acc_ph ^= 1u;
+      }
+      if (!ok) break;
+      if (row < M) {
+        float* crow = C + static_cast<size_t>(row) * static_cast<size_t>(ldc);
+#pragma unroll
+        for (int c = 0; c < COLS / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= N) break;
+          float* dst = crow + col0;
           if (vec_store && col0 + 32 <= N) {
             float4* dst4 = reinterpret_cast<float4*>(dst);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              float4 o = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                     __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+              float4 o = make_float4(sum[c * 32 + 4 * j], sum[c * 32 + 4 * j + 1],
+                                     sum[c * 32 + 4 * j + 2], sum[c * 32 + 4 * j + 3]);
               if (accumulate) {
                 const float4 old = dst4[j];
                 o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
@@ -257,7 +331,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               if (col0 + j < N) {
-                float o = __uint_as_float(v[j]);
+                float o = sum[c * 32 + j];
                 if (accumulate) o += dst[j];
                 dst[j] = o;
               }
@@ -265,47 +339,45 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
       }
-      tcgen05_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        if constexpr (CG == 2) mbar_arrive_cluster(tmem_empty_bar(acc), 0);
-        else mbar_arrive(tmem_empty_bar(acc));
-      }
-      acc ^= 1;
-      if (acc == 0) acc_ph ^= 1u;
     }
-  } else if constexpr (Cfg::HAS_XFORM) {
+  } else {
     // ------------------------------------------------------------ split / relay warps
-    constexpr int XT = Cfg::XFORM_WARPS * 32;
-    const int xt = threadIdx.x - Cfg::FIRST_XFORM_WARP * 32;
-    int s = 0;
-    uint32_t ph = 0;
-    bool ok = true;
-    for (int t = worker; t < num_tiles && ok; t += num_workers) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        if (!mbar_wait(full_bar(s), ph, status, kDevTimeoutFull)) { ok = false; break; }
-        if constexpr (Cfg::MODE == 3) {
-          // Element-wise, so the swizzled placement of the raw tile carries over unchanged.
-          const uint4* src = reinterpret_cast<const uint4*>(smem_gen + s * Cfg::STAGE_BYTES);
-          uint4* dst = reinterpret_cast<uint4*>(smem_gen + s * Cfg::STAGE_BYTES + Cfg::RAW_BYTES);
-          constexpr int kVecs = Cfg::RAW_BYTES / 16;
-          static_assert(kVecs % XT == 0, "whole passes");
+    if constexpr (Cfg::REBALANCE) setmaxnreg_dec<Cfg::REGS_XFORM>();
+    if constexpr (Cfg::HAS_XFORM) {
+      if (warp < Cfg::FIRST_XFORM_WARP + Cfg::XFORM_WARPS) {
+        constexpr int XT = Cfg::XFORM_WARPS * 32;
+        const int xt = threadIdx.x - Cfg::FIRST_XFORM_WARP * 32;
+        int s = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        for (int t = worker; t < num_tiles && ok; t += num_workers) {
+          for (int kb = 0; kb < num_kb; ++kb) {
+            if (!mbar_wait(full_bar(s), ph, status, kDevTimeoutFull)) { ok = false; break; }
+            if constexpr (Cfg::MODE == 3) {
+              // Element-wise, so the swizzled placement of the raw tile carries over unchanged.
+              const uint4* src = reinterpret_cast<const uint4*>(smem_gen + s * Cfg::STAGE_BYTES);
+              uint4* dst =
+                  reinterpret_cast<uint4*>(smem_gen + s * Cfg::STAGE_BYTES + Cfg::RAW_BYTES);
+              constexpr int kVecs = Cfg::RAW_BYTES / 16;
+              static_assert(kVecs % XT == 0, "whole passes");
 #pragma unroll 8
-          for (int i = 0; i < kVecs / XT; ++i) {
-            const uint4 x = src[i * XT + xt];
-            uint4 y;
-            y.x = split_small(x.x); y.y = split_small(x.y);
-            y.z = split_small(x.z); y.w = split_small(x.w);
-            dst[i * XT + xt] = y;
+              for (int i = 0; i < kVecs / XT; ++i) {
+                const uint4 x = src[i * XT + xt];
+                uint4 y;
+                y.x = split_small(x.x); y.y = split_small(x.y);
+                y.z = split_small(x.z); y.w = split_small(x.w);
+                dst[i * XT + xt] = y;
+              }
+              fence_proxy_async_smem();
+            }
+            __syncwarp();
+            if (lane == 0) {
+              if constexpr (CG == 2) mbar_arrive_cluster(ready_bar(s), 0);
+              else mbar_arrive(ready_bar(s));
+            }
+            if (++s == STAGES) { s = 0; ph ^= 1u; }
           }
-          fence_proxy_async_smem();
         }
-        __syncwarp();
-        if (lane == 0) {
-          if constexpr (CG == 2) mbar_arrive_cluster(ready_bar(s), 0);
-          else mbar_arrive(ready_bar(s));
-        }
-        if (++s == STAGES) { s = 0; ph ^= 1u; }
       }
     }
   }
