@@ -103,7 +103,8 @@ int roller_b200_gemm_run(roller_plan* plan, const float* A, const float* B, floa
 int roller_b200_gemm_time(roller_plan* plan, const float* A, const float* B, float* C, void* stream,
                           int warmup, int iters, float* ms_per_iter);
 
-/* Host-buffer convenience used for end-to-end timing: copies A and B from host memory into
+/* Host-buffer form of the whole run_eval data path -- allocate/upload operands, launch, read C
+ * back (src/roller.py:532-550) -- used for end-to-end timing: copies A and B from host memory into
  * plan-owned device buffers, runs the GEMM and copies C back, all on `stream`; blocks until C
  * has arrived. The device buffers are allocated on the first call and kept. */
 int roller_b200_gemm_host(roller_plan* plan, const float* hA, const float* hB, float* hC,
@@ -124,14 +125,21 @@ int roller_b200_gemm_set_chunk(roller_plan* plan, int k_elems);
  * at most one per tile). The reference derives its grid from the hint (src/roller.py:536). */
 int roller_b200_gemm_set_grid(roller_plan* plan, int ctas);
 
-/* Reads back the device status word of the plan (0 = all bounded waits completed); returns
+/* Stands in for the per-hint try/except of the sweep (src/benchmark.py:43-58): a kernel whose
+ * pipeline stalls ends by itself and reports here instead of hanging.
+ * Reads back the device status word of the plan (0 = all bounded waits completed); returns
  * ROLLER_ERR_TIMEOUT when it is non-zero. Synchronises the device. */
 int roller_b200_last_status(roller_plan* plan, uint32_t* device_status);
 
+/* Releases what roller_b200_gemm_create allocated (the reference leaves its module to the
+ * garbage collector, src/roller.py:504-505). */
 int roller_b200_gemm_destroy(roller_plan* plan);
 
+/* Text for a roller_status; the Python layer raises it as the exception message that the
+ * sweep prints per failed hint (src/benchmark.py:55-58). */
 const char* roller_b200_strerror(int status);
-/* Text of the last CUDA error seen by this library on the calling thread. */
+/* Text of the last CUDA error seen by this library on the calling thread (the reference
+ * surfaces CuPy's exception text the same way, src/benchmark.py:55-58). */
 const char* roller_b200_last_cuda_error(void);
 
 #ifdef __cplusplus

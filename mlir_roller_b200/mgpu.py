@@ -1,0 +1,172 @@
+"""Output-stationary sharding of one GEMM across the GPUs of a node.
+
+The reference is single-GPU (it pins one device, .env:5-6); this driver is what the B200 build
+adds on top of its hot path. One process per GPU (`torch.distributed`, NCCL over NVLink): rank r
+owns one block of C and computes it from its rows of A and its columns of B with the full
+reduction, so the compute phase needs no exchange at all. Operands are replicated (or placed)
+in every GPU's own memory before the timed region. A collective is used only to bring the C
+blocks to one rank when the caller wants the whole matrix there.
+
+Layouts
+  * 1-D row sharding (grid = (n, 1)): rank r holds A[rows_r, :], all of B, and C[rows_r, :].
+  * 2-D sharding (grid = (gm, gn)): rank r = i * gn + j holds A[rows_i, :], reads the column
+    block B[:, cols_j] as a strided view of the replicated B (ldb stays N; TMA handles the
+    stride, nothing is repacked), and owns C[rows_i, cols_j].
+The rTile search runs per shard shape, so every rank picks the kernel that suits its block.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+
+@dataclass(frozen=True)
+class Block:
+    """Half-open row/column ranges of C owned by one rank."""
+    rank: int
+    row0: int
+    row1: int
+    col0: int
+    col1: int
+
+    @property
+    def rows(self) -> int:
+        return self.row1 - self.row0
+
+    @property
+    def cols(self) -> int:
+        return self.col1 - self.col0
+
+
+def _split(extent: int, parts: int, align: int) -> List[Tuple[int, int]]:
+    """Cut [0, extent) into `parts` contiguous ranges whose boundaries are multiples of
+    `align` (except the end); earlier ranges take the remainder units. Ranges may be empty
+    when there are fewer units than parts."""
+    units = -(-extent // align)
+    base, extra = divmod(units, parts)
+    out, start = [], 0
+    for p in range(parts):
+        n = (base + (1 if p < extra else 0)) * align
+        stop = min(start + n, extent)
+        out.append((start, stop))
+        start = stop
+    return out
+
+
+def partition(M: int, N: int, grid_m: int, grid_n: int, align_m: int = 128,
+              align_n: int = 32) -> List[Block]:
+    """Blocks of C for a grid_m x grid_n process grid, rank = i * grid_n + j.
+
+    Row boundaries fall on multiples of `align_m` (one CTA's tile rows) and column boundaries
+    on multiples of `align_n` (one TMA box of B, which also keeps the B view 16-byte aligned).
+    """
+    if grid_m < 1 or grid_n < 1:
+        raise ValueError("grid dimensions must be positive")
+    rows = _split(M, grid_m, align_m)
+    cols = _split(N, grid_n, align_n)
+    return [Block(i * grid_n + j, r0, r1, c0, c1)
+            for i, (r0, r1) in enumerate(rows) for j, (c0, c1) in enumerate(cols)]
+
+
+def default_grid(world_size: int, M: int, N: int) -> Tuple[int, int]:
+    """Row sharding while blocks stay at least 1024 rows tall, else the most square grid
+    (8 ranks on a square problem -> 4 x 2)."""
+    if M // world_size >= 1024 or world_size == 1:
+        return world_size, 1
+    best = (world_size, 1)
+    for gn in range(1, world_size + 1):
+        if world_size % gn == 0:
+            gm = world_size // gn
+            if abs(M / gm - N / gn) < abs(M / best[0] - N / best[1]):
+                best = (gm, gn)
+    return best
+
+
+def gather_blocks(local, blocks: Sequence[Block], M: int, N: int, rank: int, root: int = 0,
+                  group=None, out=None):
+    """Assemble C on `root` from every rank's block. `local` is this rank's (rows x cols) block,
+    contiguous. Returns the full matrix on root (written into `out` when given), None elsewhere.
+
+    Uses point-to-point sends into `root` (NCCL send/recv on GPUs, gloo on CPU): blocks differ
+    in shape, and only one rank needs the result, so an all-gather would move 7/8 of the data
+    for nothing on an 8-GPU node.
+    """
+    import torch
+    import torch.distributed as dist
+
+    mine = blocks[rank]
+    if tuple(local.shape) != (mine.rows, mine.cols):
+        raise ValueError(f"rank {rank}: block is {tuple(local.shape)}, expected {(mine.rows, mine.cols)}")
+    if rank != root:
+        if mine.rows * mine.cols > 0:
+            dist.send(local.contiguous(), dst=root, group=group)
+        return None
+    full = out if out is not None else torch.empty((M, N), dtype=local.dtype, device=local.device)
+    full[mine.row0:mine.row1, mine.col0:mine.col1].copy_(local)
+    for b in blocks:
+        if b.rank == root or b.rows * b.cols == 0:
+            continue
+        if b.col0 == 0 and b.col1 == N:
+            # a band of whole rows is contiguous in C: receive in place
+            dist.recv(full[b.row0:b.row1], src=b.rank, group=group)
+        else:
+            tmp = torch.empty((b.rows, b.cols), dtype=local.dtype, device=local.device)
+            dist.recv(tmp, src=b.rank, group=group)
+            full[b.row0:b.row1, b.col0:b.col1].copy_(tmp)
+    return full
+
+
+class ShardedGemm:
+    """This rank's part of C = A @ B on a grid_m x grid_n process grid.
+
+    Usage, one process per GPU with the process group already initialised:
+
+        sg = ShardedGemm(M, N, K, rank, world_size)            # searches the shard's rTile
+        sg.run(A_rows, B_full, C_block)                         # local kernel, no communication
+        C = sg.gather(C_block)                                  # whole C on rank 0, None elsewhere
+    """
+
+    def __init__(self, M: int, N: int, K: int, rank: int, world_size: int,
+                 grid: Optional[Tuple[int, int]] = None, mode: int = 3, arch=None,
+                 measure: bool = False):
+        from . import _lib, roller
+        from .analyze import MatmulConfig
+        self.M, self.N, self.K = M, N, K
+        self.rank, self.world_size = rank, world_size
+        self.grid = grid if grid is not None else default_grid(world_size, M, N)
+        if self.grid[0] * self.grid[1] != world_size:
+            raise ValueError(f"grid {self.grid} does not match world size {world_size}")
+        self.blocks = partition(M, N, self.grid[0], self.grid[1])
+        self.block = self.blocks[rank]
+        self.mode = mode
+        self.plan = None
+        self.hint = None
+        if self.block.rows > 0 and self.block.cols > 0:
+            cfg = MatmulConfig(self.block.rows, self.block.cols, K, 32)
+            hint, _fn, _ms = roller.best_hint(cfg, arch, mode=mode, measure=measure)
+            self.hint = hint
+            tile = roller.kernel_tile_for(hint)
+            # B is addressed inside the replicated K x N matrix, C is this rank's own block
+            self.plan = _lib.GemmPlan(tile, self.block.rows, self.block.cols, K, lda=K, ldb=N,
+                                      ldc=self.block.cols, mode=mode)
+
+    def local_operands(self, A_full, B_full):
+        """Views of the replicated operands this rank reads: its rows of A, its columns of B."""
+        b = self.block
+        return A_full[b.row0:b.row1], B_full[:, b.col0:b.col1]
+
+    def run(self, A_rows, B_full, C_block, stream=None) -> None:
+        """Enqueue the local GEMM. `A_rows` = A[rows_r, :] (contiguous), `B_full` = the whole
+        replicated B (K x N, contiguous), `C_block` = this rank's rows x cols output."""
+        if self.plan is None:
+            return
+        b = self.block
+        elem = B_full.element_size()
+        self.plan.run_ptr(A_rows.data_ptr(), B_full.data_ptr() + b.col0 * elem,
+                          C_block.data_ptr(), stream)
+
+    def gather(self, C_block, root: int = 0, group=None, out=None):
+        return gather_blocks(C_block, self.blocks, self.M, self.N, self.rank, root, group, out)
+
+    def flops(self) -> int:
+        return 2 * self.block.rows * self.block.cols * self.K

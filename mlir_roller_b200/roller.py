@@ -1,0 +1,233 @@
+"""Compile / launch / time layer of the Roller hot path on B200.
+
+Same surface as the reference's src/roller.py -- `Compiler(config, hint, pipeline_depth,
+dump_path).compile()`, `run_eval`, `run_baseline`, `time_cuda` -- but where the reference emits
+MLIR, lowers it through an IREE fork to sm_80 PTX and loads that with CuPy
+(src/roller.py:345-511), `compile()` here binds the hint to the ahead-of-time compiled sm_100a
+kernel for its rTile through the C ABI (include/roller_b200.h). Device arrays are torch CUDA
+tensors; kernels get raw device pointers exactly as the reference passes `dA.data.ptr`.
+
+Differences a caller can observe, all deliberate:
+  * the kernel writes C = A @ B; the reference's generated kernel accumulates into a C the host
+    zeroed (src/roller.py:62,534). `Compiler(..., accumulate=True)` gives that behaviour;
+  * a hint whose block tile has no compiled kernel raises (the reference can compile any hint);
+    the sweep's per-hint try/except (src/benchmark.py:43-58) skips it the same way it skips a
+    hint that fails to compile there;
+  * there is no CPU fallback: without the shared library or without an sm_100 GPU, `compile()`
+    raises.
+"""
+from __future__ import annotations
+
+from contextlib import contextmanager
+from pathlib import Path
+from typing import Optional
+
+from . import _lib
+from .analyze import MODE_1XTF32, MODE_3XTF32, MatmulConfig, TileDict, get_roller_hints
+from .arch import B200, CUDA  # noqa: F401  (same names importable as from the reference module)
+from .utils import get_block_dims  # noqa: F401
+
+
+def _torch():
+    import torch
+    if not torch.cuda.is_available():
+        raise RuntimeError("roller_b200 needs a CUDA device (sm_100); there is no CPU fallback")
+    return torch
+
+
+class CompiledGemm:
+    """What `Compiler.compile()` returns: callable like a CuPy kernel,
+    `f(grid_dims, block_dims, (ptrA, ptrB, ptrC), shared_mem=bytes)` (src/roller.py:545-550).
+
+    The launch geometry belongs to the compiled kernel (persistent grid, fixed block, its own
+    shared-memory size), so `grid_dims`, `block_dims` and `shared_mem` are checked for shape and
+    otherwise ignored; `launch_info()` reports what is really used.
+    """
+
+    def __init__(self, plan: _lib.GemmPlan, hint: TileDict):
+        self.plan = plan
+        self.hint = hint
+
+    def __call__(self, grid_dims, block_dims, args, shared_mem: int = 0, stream=None) -> None:
+        if len(args) != 3:
+            raise ValueError("expected (ptrA, ptrB, ptrC)")
+        for dims in (grid_dims, block_dims):
+            if not all(isinstance(d, int) and d > 0 for d in dims):
+                raise ValueError(f"launch dimensions must be positive integers, got {dims}")
+        if shared_mem < 0:
+            raise ValueError("shared_mem must be non-negative")
+        self.plan.run_ptr(int(args[0]), int(args[1]), int(args[2]), stream)
+
+    def launch_info(self) -> dict:
+        return self.plan.launch_info()
+
+    def time(self, A, B, C, warmup: int = 3, iters: int = 20) -> float:
+        return self.plan.time(A, B, C, warmup, iters)
+
+
+def kernel_tile_for(hint: TileDict) -> _lib.KTile:
+    """The compiled rTile that implements `hint`: same block tile, and the same CTA grouping
+    when the hint names one. Raises RollerError(UNSUPPORTED) when there is none."""
+    bm, bn = hint.block_tile[0], hint.block_tile[1]
+    cta_group = getattr(hint, "cta_group", None)
+    return _lib.find_tile(bm, bn, cta_group)
+
+
+class Compiler:
+    """Binds (problem, hint) to a launchable kernel (src/roller.py:345-387).
+
+    `pipeline_depth` and `dump_path` are accepted for call compatibility: the pipeline depth is
+    fixed per compiled kernel (reported in `launch_info`), and there is no IR to dump.
+    `mode` selects 3xTF32 (default, fp32-level accuracy) or 1xTF32.
+    """
+
+    def __init__(self, config: MatmulConfig, hint: TileDict, pipeline_depth: int = 2,
+                 dump_path: Optional[Path] = None, mode: Optional[int] = None,
+                 accumulate: bool = False):
+        self.config = config
+        self.hint = hint
+        self.pipeline_depth = pipeline_depth
+        self.dump_path = dump_path
+        self.mode = mode if mode is not None else (getattr(hint, "mode", None) or MODE_3XTF32)
+        self.accumulate = accumulate
+
+    def compile(self) -> CompiledGemm:
+        _torch()
+        if self.config.el_bits != 32:
+            raise _lib.RollerError(_lib.ERR_UNSUPPORTED, "only fp32 (el_bits=32) kernels exist")
+        tile = kernel_tile_for(self.hint)
+        plan = _lib.GemmPlan(tile, self.config.M, self.config.N, self.config.K, mode=self.mode,
+                             flags=_lib.FLAG_ACCUMULATE if self.accumulate else 0)
+        return CompiledGemm(plan, self.hint)
+
+
+@contextmanager
+def time_cuda():
+    """Two CUDA events around the body on the current stream; the second is synchronised on
+    exit (src/roller.py:514-522). Read the time with `start.elapsed_time(end)` (ms)."""
+    torch = _torch()
+    start = torch.cuda.Event(enable_timing=True)
+    end = torch.cuda.Event(enable_timing=True)
+    start.record()
+    yield start, end
+    end.record()
+    end.synchronize()
+
+
+def _strict_fp32_matmul(torch, a, b, out=None):
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        return torch.matmul(a, b, out=out) if out is not None else torch.matmul(a, b)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
+def run_eval(cuda_func, pipeline_depth, hint: TileDict, repeat_times: int = 20):
+    """Launch, check once against the library fp32 product, warm up 10x, time `repeat_times`
+    launches; returns (ms per launch, GFLOPS) (src/roller.py:525-586)."""
+    torch = _torch()
+    cfg = hint.matmul_config
+    M, N, K = cfg.M, cfg.N, cfg.K
+    dA = torch.rand(M, K, dtype=torch.float32, device="cuda")
+    dB = torch.rand(K, N, dtype=torch.float32, device="cuda")
+    dC = torch.zeros(M, N, dtype=torch.float32, device="cuda")
+
+    grid_dims = (max(N // hint.block_tile[1], 1), max(M // hint.block_tile[0], 1))
+    block_dims = (max(hint.block_tile[1] // max(hint.thread_tile[1], 1), 1),
+                  max(hint.block_tile[0] // max(hint.thread_tile[0], 1), 1))
+    shared_memory_usage = hint.smem_cost * pipeline_depth
+    args = (dA.data_ptr(), dB.data_ptr(), dC.data_ptr())
+
+    cuda_func(grid_dims, block_dims, args, shared_mem=shared_memory_usage)
+    ref = _strict_fp32_matmul(torch, dA, dB)
+    if not torch.allclose(dC, ref, rtol=1e-5, atol=1e-8):
+        worst = float((dC - ref).abs().max() / ref.abs().max())
+        print(f"result differs from the fp32 library product: max |diff| / max |ref| = {worst:.3e}")
+
+    for _ in range(10):
+        cuda_func(grid_dims, block_dims, args, shared_mem=shared_memory_usage)
+    with time_cuda() as (start_gpu, end_gpu):
+        for _ in range(repeat_times):
+            cuda_func(grid_dims, block_dims, args, shared_mem=shared_memory_usage)
+    t_gpu = start_gpu.elapsed_time(end_gpu)
+
+    print(f"t={t_gpu / repeat_times:.6f} ms", end=" ")
+    flops = 2 * M * N * K
+    gflops = repeat_times * flops * 1e-9 / (t_gpu / 1000)
+    print(f"GFLOPS={gflops:.6f}")
+    return t_gpu / repeat_times, gflops
+
+
+def run_baseline(config: MatmulConfig, repeat_times: int = 50, allow_tf32: bool = False):
+    """Library GEMM baseline (cuBLAS through torch; the reference uses cuBLAS through CuPy,
+    src/roller.py:589-607): 10 warm-ups, `repeat_times` timed; returns (ms, GFLOPS)."""
+    torch = _torch()
+    M, N, K = config.M, config.N, config.K
+    dA = torch.rand(M, K, dtype=torch.float32, device="cuda")
+    dB = torch.rand(K, N, dtype=torch.float32, device="cuda")
+    dC = torch.zeros(M, N, dtype=torch.float32, device="cuda")
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = allow_tf32
+    try:
+        for _ in range(10):
+            torch.matmul(dA, dB, out=dC)
+        with time_cuda() as (start_gpu, end_gpu):
+            for _ in range(repeat_times):
+                torch.matmul(dA, dB, out=dC)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    t_gpu = start_gpu.elapsed_time(end_gpu)
+
+    print(f"t={t_gpu / repeat_times:.6f} ms", end=" ")
+    flops = 2 * M * N * K
+    gflops = repeat_times * flops * 1e-9 / (t_gpu / 1000)
+    print(f"GFLOPS={gflops:.6f}")
+    return t_gpu / repeat_times, gflops
+
+
+def best_hint(config: MatmulConfig, arch=None, topk: int = 20, mode: int = MODE_3XTF32,
+              measure: bool = True):
+    """Search, then (like the reference's drivers, src/roller.py:617-633) time every hint and
+    keep the fastest. Returns (hint, compiled kernel, ms). With `measure=False` the top-ranked
+    hint is taken as is."""
+    torch = _torch()
+    arch = B200() if arch is None else arch
+    hints = get_roller_hints(config, arch, topk=topk, mode=mode) if isinstance(arch, B200) \
+        else get_roller_hints(config, arch, topk=topk)
+    if not measure:
+        hint = hints[0]
+        return hint, Compiler(config, hint, mode=mode).compile(), None
+    dA = torch.rand(config.M, config.K, dtype=torch.float32, device="cuda")
+    dB = torch.rand(config.K, config.N, dtype=torch.float32, device="cuda")
+    dC = torch.empty(config.M, config.N, dtype=torch.float32, device="cuda")
+    best = None
+    for hint in hints:
+        try:
+            fn = Compiler(config, hint, mode=mode).compile()
+            ms = fn.time(dA, dB, dC, warmup=2, iters=5)
+        except _lib.RollerError:
+            continue
+        if best is None or ms < best[2]:
+            best = (hint, fn, ms)
+    if best is None:
+        raise _lib.RollerError(_lib.ERR_UNSUPPORTED, "no hint could be bound to a kernel")
+    return best
+
+
+if __name__ == "__main__":
+    S = 4096
+    config = MatmulConfig(M=S, N=S, K=S, el_bits=32)
+    pipeline_depth = 2
+    hints = get_roller_hints(config, B200(), topk=20)
+    run_baseline(config)
+    result_dict = {}
+    for hint in hints:
+        cuda_func = Compiler(config, hint, pipeline_depth, dump_path=Path("log")).compile()
+        print(hint)
+        t, gflops = run_eval(cuda_func, pipeline_depth, hint)
+        print("---\n")
+        result_dict[hint] = (t, gflops)
+    if result_dict:
+        best = min(result_dict, key=lambda h: result_dict[h][0])
+        print(f"Best hint: {best}, time: {result_dict[best][0]}, GFLOPS: {result_dict[best][1]}")

@@ -1,0 +1,65 @@
+/*
+ * TEST INFRASTRUCTURE -- plain-C restatement of the GEMM on the Roller hot path.
+ * Built by oracle/gemm_oracle.py (gcc) and used only by tests, the smoke check and the CPU
+ * baseline; the product never links or loads it.
+ *
+ * oracle_sgemm_accumulate: what the reference's generated `gemm_kernel` computes -- the
+ *   linalg.matmul payload C += A @ B on fp32 (src/roller.py:47-68, C zeroed by the host at
+ *   src/roller.py:534), lowered to fp32 outer products / FMAs (src/roller.py:280-282) with the
+ *   reduction walked in blocks of the hint's `rstep` (src/roller.py:93-342).
+ * oracle_gemm_3xtf32: the arithmetic of the B200 3xTF32 kernels with an ideal per-chunk
+ *   accumulator, to predict their error band on the CPU.
+ * Parity unpinned: the reference has no golden outputs for its kernel; both functions are
+ *   checked against the fp64 product in tests/.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <string.h>
+
+static float bits_to_float(uint32_t b) { float f; memcpy(&f, &b, 4); return f; }
+static uint32_t float_to_bits(float f) { uint32_t b; memcpy(&b, &f, 4); return b; }
+
+/* the 19 bits of an fp32 word the tensor core reads */
+static float trunc19(float x) { return bits_to_float(float_to_bits(x) & 0xFFFFE000u); }
+
+/* x - trunc19(x), rounded to nearest on the 19-bit grid; 0 for inf/nan */
+float oracle_split_small(float x) {
+  uint32_t xb = float_to_bits(x);
+  float s = x - trunc19(x);
+  if ((xb & 0x7F800000u) == 0x7F800000u) s = 0.0f;
+  return bits_to_float((float_to_bits(s) + 0x1000u) & 0xFFFFE000u);
+}
+
+void oracle_sgemm_accumulate(const float* A, const float* B, float* C, int M, int N, int K,
+                             int rstep) {
+  if (rstep < 1) rstep = 1;
+  for (int k0 = 0; k0 < K; k0 += rstep) {
+    int k1 = k0 + rstep < K ? k0 + rstep : K;
+    for (int i = 0; i < M; ++i)
+      for (int j = 0; j < N; ++j) {
+        float acc = C[(size_t)i * N + j];
+        for (int k = k0; k < k1; ++k) acc = fmaf(A[(size_t)i * K + k], B[(size_t)k * N + j], acc);
+        C[(size_t)i * N + j] = acc;
+      }
+  }
+}
+
+void oracle_gemm_3xtf32(const float* A, const float* B, float* C, int M, int N, int K, int chunk) {
+  if (chunk < 1) chunk = K;
+  for (int i = 0; i < M; ++i)
+    for (int j = 0; j < N; ++j) {
+      float sum = 0.0f;
+      for (int k0 = 0; k0 < K; k0 += chunk) {
+        int k1 = k0 + chunk < K ? k0 + chunk : K;
+        double part = 0.0;
+        for (int k = k0; k < k1; ++k) {
+          float a = A[(size_t)i * K + k], b = B[(size_t)k * N + j];
+          double ab = trunc19(a), bb = trunc19(b);
+          double as = oracle_split_small(a), bs = oracle_split_small(b);
+          part += as * bb + ab * bs + ab * bb;
+        }
+        sum += (float)part;
+      }
+      C[(size_t)i * N + j] = sum;
+    }
+}

@@ -1,0 +1,75 @@
+"""The Blackwell device model and policy: every emitted rTile is buildable and sane."""
+import ctypes
+
+import pytest
+from hypothesis import given, settings, strategies as st
+
+from mlir_roller_b200 import analyze, arch
+from mlir_roller_b200.analyze import MODE_1XTF32, MODE_3XTF32, MatmulConfig, get_roller_hints
+
+TILES = {(t[0], t[1], t[2]) for t in arch.B200_KERNEL_TILES}
+
+
+def check_hint(h, M, N, K, mode):
+    dev = arch.B200()
+    assert (h.block_tile[0], h.block_tile[1], h.cta_group) in TILES
+    assert h.rstep == 32 and h.mode == mode
+    assert h.tmem_cols == 2 * h.block_tile[1] <= dev.tmem_columns
+    assert h.smem_cost * h.stages + 2048 <= dev.smem_cap == 227 * 1024
+    assert h.block_tile[0] == 128 * h.cta_group
+    assert h.grid_size == -(-M // h.block_tile[0]) * -(-N // h.block_tile[1])
+    assert h.num_wave == -(-h.grid_size // (dev.compute_max_core // h.cta_group))
+    assert h.est_us > 0 and h.valid
+
+
+@pytest.mark.parametrize("mode", [MODE_1XTF32, MODE_3XTF32])
+def test_readme_and_config_shapes(mode):
+    shapes = [(2048, 2048, 2048), (8192, 4096, 4096), (4097, 2049, 8193), (16, 8192, 8192),
+              (16384, 16384, 16384), (1024, 4096, 4096), (4096, 8192, 16384), (1, 1, 1)]
+    for M, N, K in shapes:
+        hints = get_roller_hints(MatmulConfig(M, N, K, 32), arch.B200(), topk=20, mode=mode)
+        assert 1 <= len(hints) <= len(TILES)
+        assert len({(h.block_tile[0], h.block_tile[1], h.cta_group) for h in hints}) == len(hints)
+        est = [h.est_us for h in hints]
+        assert est == sorted(est)
+        for h in hints:
+            check_hint(h, M, N, K, mode)
+
+
+def test_large_square_prefers_the_cta_pair_tile():
+    for mode in (MODE_1XTF32, MODE_3XTF32):
+        top = get_roller_hints(MatmulConfig(8192, 8192, 8192, 32), arch.B200(), topk=1, mode=mode)[0]
+        assert (top.block_tile, top.cta_group) == ([256, 256], 2)
+
+
+def test_topk_and_dispatch():
+    cfg = MatmulConfig(4096, 4096, 4096, 32)
+    assert len(get_roller_hints(cfg, arch.B200(), topk=2)) == 2
+    # the generic policy is still what a non-B200 device model gets
+    assert get_roller_hints(cfg, arch.CUDA(), topk=1)[0].block_tile == [128, 128]
+    with pytest.raises(ValueError):
+        get_roller_hints(MatmulConfig(64, 64, 64, 16), arch.B200())
+    with pytest.raises(ValueError):
+        analyze.BlackwellPolicy(cfg, arch.B200(), mode=2)
+
+
+@settings(max_examples=150, deadline=None)
+@given(st.integers(1, 20000), st.integers(1, 20000), st.integers(1, 20000),
+       st.sampled_from([MODE_1XTF32, MODE_3XTF32]))
+def test_any_ragged_shape_gets_valid_hints(M, N, K, mode):
+    hints = get_roller_hints(MatmulConfig(M, N, K, 32), arch.B200(), topk=3, mode=mode)
+    assert hints
+    for h in hints:
+        check_hint(h, M, N, K, mode)
+
+
+def test_tile_table_matches_the_library():
+    """The table the search ranks is exactly what libroller_b200 was compiled with."""
+    from mlir_roller_b200 import _lib
+    lib_tiles = [(k.block_m, k.block_n, k.cta_group, k.stages_1x, k.stages_3x)
+                 for k in _lib.kernel_tiles()]
+    assert sorted(lib_tiles) == sorted(arch.B200_KERNEL_TILES)
+    for k in _lib.kernel_tiles():
+        assert k.rstep == 32 and k.tmem_cols == 2 * k.block_n
+        assert max(k.smem_1x, k.smem_3x) <= 227 * 1024
+        assert isinstance(k, ctypes.Structure)

@@ -1,0 +1,107 @@
+"""Host-side logic of the multi-GPU driver: partitioning and the gather, the latter over a
+world_size-2 gloo group on CPU (blocks produced by the oracle stand in for the kernel output)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+from hypothesis import given, settings, strategies as st
+
+from mlir_roller_b200 import mgpu
+
+
+def test_row_partition_of_m13():
+    blocks = mgpu.partition(8192, 4096, 8, 1)
+    assert [(b.row0, b.row1, b.col0, b.col1) for b in blocks] == \
+        [(i * 1024, (i + 1) * 1024, 0, 4096) for i in range(8)]
+    assert [b.rank for b in blocks] == list(range(8))
+
+
+def test_2d_partition_of_16384():
+    blocks = mgpu.partition(16384, 16384, 4, 2)
+    assert len(blocks) == 8
+    b = blocks[5]  # i = 2, j = 1
+    assert (b.row0, b.row1, b.col0, b.col1) == (8192, 12288, 8192, 16384)
+    assert all(b.rows == 4096 and b.cols == 8192 for b in blocks)
+
+
+def test_default_grid():
+    assert mgpu.default_grid(8, 8192, 4096) == (8, 1)
+    assert mgpu.default_grid(8, 16384, 16384) == (8, 1)
+    assert mgpu.default_grid(8, 2048, 2048) == (4, 2)
+    assert mgpu.default_grid(1, 100, 100) == (1, 1)
+
+
+@settings(max_examples=200, deadline=None)
+@given(st.integers(1, 5000), st.integers(1, 5000), st.integers(1, 8), st.integers(1, 4))
+def test_partition_tiles_c_exactly(M, N, gm, gn):
+    blocks = mgpu.partition(M, N, gm, gn)
+    assert len(blocks) == gm * gn
+    cover = np.zeros((M, N), dtype=np.int8)
+    for b in blocks:
+        assert 0 <= b.row0 <= b.row1 <= M and 0 <= b.col0 <= b.col1 <= N
+        if b.rows and b.cols:
+            assert b.row0 % 128 == 0 and b.col0 % 32 == 0
+        cover[b.row0:b.row1, b.col0:b.col1] += 1
+    assert (cover == 1).all()
+
+
+def test_partition_rejects_bad_grid():
+    with pytest.raises(ValueError):
+        mgpu.partition(10, 10, 0, 1)
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _gather_worker(rank, world, port, grid, M, N, K, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import gemm_oracle
+        A, B = gemm_oracle.make_inputs(M, N, K, "uniform", seed=3)
+        blocks = mgpu.partition(M, N, grid[0], grid[1], align_m=8, align_n=4)
+        b = blocks[rank]
+        local = torch.from_numpy(gemm_oracle.matmul_fp32(A[b.row0:b.row1], B[:, b.col0:b.col1]))
+        sentinel = torch.full((M, N), float("nan"))
+        full = mgpu.gather_blocks(local, blocks, M, N, rank, root=0, out=sentinel)
+        if rank == 0:
+            want = np.empty((M, N), np.float32)
+            for bb in blocks:
+                want[bb.row0:bb.row1, bb.col0:bb.col1] = gemm_oracle.matmul_fp32(
+                    A[bb.row0:bb.row1], B[:, bb.col0:bb.col1])
+            q.put(bool(np.array_equal(full.numpy(), want)) and full is sentinel)
+        else:
+            q.put(full is None)
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("grid", [(2, 1), (1, 2)])
+def test_gather_two_ranks_gloo(grid):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gather_worker, args=(r, 2, port, grid, 40, 24, 16, q))
+             for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(results)
+
+
+def test_gather_checks_block_shape():
+    blocks = mgpu.partition(16, 16, 1, 1, align_m=8, align_n=4)
+    with pytest.raises(ValueError):
+        mgpu.gather_blocks(torch.zeros(3, 3), blocks, 16, 16, rank=0)

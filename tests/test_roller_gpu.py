@@ -1,0 +1,89 @@
+"""The drop-in Python surface (Compiler / run_eval / run_baseline / benchmark / mgpu) on a GPU."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from mlir_roller_b200 import B200, CUDA, MatmulConfig, _lib, get_roller_hints, mgpu, roller  # noqa: E402
+from mlir_roller_b200 import benchmark as bm  # noqa: E402
+from oracle import gemm_oracle as g  # noqa: E402
+
+
+def test_compile_and_call_like_the_reference():
+    cfg = MatmulConfig(512, 384, 256, 32)
+    hint = get_roller_hints(cfg, B200(), topk=1)[0]
+    fn = roller.Compiler(cfg, hint, pipeline_depth=2, dump_path=None).compile()
+    A, B = g.make_inputs(512, 384, 256, "uniform", 0)
+    dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    dC = torch.zeros(512, 384, device="cuda")
+    grid = (384 // hint.block_tile[1] or 1, 512 // hint.block_tile[0] or 1)
+    fn(grid, (8, 16), (dA.data_ptr(), dB.data_ptr(), dC.data_ptr()), shared_mem=hint.smem_cost * 2)
+    torch.cuda.synchronize()
+    assert g.err_norm(dC.cpu().numpy(), g.matmul_fp64(A, B)) <= 1e-5
+    info = fn.launch_info()
+    assert info["block"] == 512 and info["smem_bytes"] <= 227 * 1024
+    with pytest.raises(ValueError):
+        fn((0, 1), (1, 1), (dA.data_ptr(), dB.data_ptr(), dC.data_ptr()))
+
+
+def test_reference_policy_hints_bind_when_a_kernel_exists():
+    cfg = MatmulConfig(1024, 1024, 512, 32)
+    hints = get_roller_hints(cfg, CUDA(), topk=20)
+    bound, skipped = 0, 0
+    for h in hints:
+        try:
+            roller.Compiler(cfg, h).compile()
+            bound += 1
+        except _lib.RollerError as e:
+            assert e.status == _lib.ERR_UNSUPPORTED
+            skipped += 1
+    assert bound >= 1 and skipped >= 1  # [128,128] binds; e.g. [64,64] has no sm_100a kernel
+
+
+def test_run_eval_and_baseline(capsys):
+    cfg = MatmulConfig(1024, 1024, 1024, 32)
+    hint = get_roller_hints(cfg, B200(), topk=1)[0]
+    fn = roller.Compiler(cfg, hint).compile()
+    ms, gflops = roller.run_eval(fn, 2, hint, repeat_times=5)
+    assert ms > 0 and abs(gflops - 2 * 1024 ** 3 * 1e-9 / (ms / 1e3)) / gflops < 1e-6
+    bms, bg = roller.run_baseline(cfg, repeat_times=5)
+    assert bms > 0 and bg > 0
+    out = capsys.readouterr().out
+    assert "GFLOPS=" in out and "differs" not in out  # passes the reference's allclose check
+
+
+def test_best_hint_measures():
+    cfg = MatmulConfig(1024, 2048, 512, 32)
+    hint, fn, ms = roller.best_hint(cfg, B200(), topk=3)
+    assert ms > 0 and hint.block_tile[0] in (128, 256)
+
+
+def test_benchmark_sweep_writes_csv(tmp_path):
+    csv = tmp_path / "benchmark_results.csv"
+    df = bm.benchmark([(512, 512, 512), (300, 200, 100)], topk=2, csv_path=str(csv))
+    assert csv.exists() and len(df) == 2
+    for col in ["M", "N", "K", "CuPy Time (ms)", "CuPy GFLOPS", "Roller Time (ms)", "Roller GFLOPS",
+                "Speedup vs CuPy", "Best Hint"]:
+        assert col in df.columns
+    assert (df["max_rel_err"] <= 1e-5).all()
+
+
+def test_sharded_gemm_on_one_gpu_emulating_ranks():
+    # ranks are emulated one after another on this GPU; the gather itself is covered by the
+    # gloo test on CPU
+    M, N, K = 1024, 768, 640
+    A, B = g.make_inputs(M, N, K, "uniform", seed=13)
+    dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    C64 = g.matmul_fp64(A, B)
+    for world, grid in ((2, (2, 1)), (4, (2, 2)), (8, (4, 2))):
+        full = torch.full((M, N), float("nan"), device="cuda")
+        for rank in range(world):
+            sg = mgpu.ShardedGemm(M, N, K, rank, world, grid=grid)
+            b = sg.block
+            a_rows, _ = sg.local_operands(dA, dB)
+            c_blk = torch.empty(b.rows, b.cols, device="cuda")
+            sg.run(a_rows.contiguous(), dB, c_blk)
+            full[b.row0:b.row1, b.col0:b.col1] = c_blk
+        torch.cuda.synchronize()
+        assert g.err_norm(full.cpu().numpy(), C64) <= 1e-5, grid
