@@ -125,6 +125,23 @@ int roller_b200_gemm_set_chunk(roller_plan* plan, int k_elems);
  * at most one per tile). The reference derives its grid from the hint (src/roller.py:536). */
 int roller_b200_gemm_set_grid(roller_plan* plan, int ctas);
 
+/* One GEMM, enqueued on `stream`, that allocates nothing: no cudaMalloc, cudaFree or allocating
+ * library call, on this or any later call. It has no counterpart in the reference (whose launch
+ * path allocates freely through CuPy); it exists for callers that cannot allocate -- a process
+ * whose own memory pool already holds all of the device's memory, or a latency-critical loop that
+ * cannot afford the implicit device synchronisation of cudaMalloc/cudaFree.
+ * It does what roller_b200_gemm_create + roller_b200_gemm_run do, including the padded staging
+ * copies for operands whose row stride or base address is not a multiple of 16 bytes, but keeps
+ * that scratch in a fixed 32 MiB array inside the library (resident on every GPU that loads the
+ * library, until exit). Staging needs beyond 32 MiB return ROLLER_ERR_TOO_LARGE.
+ * All calls share the array and it keeps the last call's contents: calls whose GPU work
+ * overlaps race on it. The first call on a device resolves the array's device address; make
+ * that call before starting any stream capture. `dev_status` (optional, device memory) receives
+ * the kernel's bounded-wait status word; NULL uses a word inside the library. C = A @ B. */
+int roller_b200_gemm_static_scratch(const roller_ktile* tile, int mode, int M, int N, int K,
+                                    int lda, int ldb, int ldc, const float* A, const float* B,
+                                    float* C, uint32_t* dev_status, void* stream);
+
 /* Stands in for the per-hint try/except of the sweep (src/benchmark.py:43-58): a kernel whose
  * pipeline stalls ends by itself and reports here instead of hanging.
  * Reads back the device status word of the plan (0 = all bounded waits completed); returns

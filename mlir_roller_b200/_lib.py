@@ -69,6 +69,9 @@ SIGNATURES = {
     "roller_b200_gemm_launch_info": (C.c_int, [C.c_void_p] + [C.POINTER(C.c_int)] * 6),
     "roller_b200_gemm_set_chunk": (C.c_int, [C.c_void_p, C.c_int]),
     "roller_b200_gemm_set_grid": (C.c_int, [C.c_void_p, C.c_int]),
+    "roller_b200_gemm_static_scratch": (C.c_int, [C.POINTER(KTile), C.c_int, C.c_int, C.c_int,
+                                                  C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                                                  C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "roller_b200_last_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32)]),
     "roller_b200_gemm_destroy": (C.c_int, [C.c_void_p]),
     "roller_b200_strerror": (C.c_char_p, [C.c_int]),
@@ -143,6 +146,17 @@ def _stream_ptr(stream) -> C.c_void_p:
         import torch
         stream = torch.cuda.current_stream()
     return C.c_void_p(getattr(stream, "cuda_stream", stream))
+
+
+def gemm_static_scratch(tile: KTile, mode: int, M: int, N: int, K: int, lda: int, ldb: int,
+                        ldc: int, a_ptr: int, b_ptr: int, c_ptr: int, status_ptr: int = 0,
+                        stream=None) -> None:
+    """Enqueue C = A @ B through the entry point that allocates nothing (its scratch is a fixed
+    32 MiB array inside the library; see include/roller_b200.h for who needs that and the limits)."""
+    check(load().roller_b200_gemm_static_scratch(C.byref(tile), mode, M, N, K, lda, ldb, ldc,
+                                                 a_ptr, b_ptr, c_ptr, status_ptr or None,
+                                                 _stream_ptr(stream)),
+          "roller_b200_gemm_static_scratch")
 
 
 class GemmPlan:

@@ -1,0 +1,84 @@
+"""The entry point that allocates nothing (roller_b200_gemm_static_scratch).
+
+Some callers cannot let a library allocate device memory: their own pool already owns all of
+it, or they run where the stall of a cudaMalloc is not acceptable. For them the library keeps
+the staging scratch of the unaligned-operand path in a fixed array of its own. This test calls
+that entry point through the C ABI and checks it against the plan-based entry points on the
+same operands, twice in a row (the second call finds the array holding the first call's data).
+It is collected last so that a run stopping at the first failure has already run all others.
+"""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+from mlir_roller_b200 import _lib  # noqa: E402
+from oracle import gemm_oracle as g  # noqa: E402
+
+TOL_3X = 4e-6   # same bound the other 3xTF32 parity tests hold
+TOL_1X = 2e-3
+
+
+def _plan_result(tile, mode, dA, dB, M, N, K, lda, ldb, ldc):
+    dC = torch.full((M, ldc), float("nan"), device="cuda")
+    plan = _lib.GemmPlan(tile, M, N, K, lda=lda, ldb=ldb, ldc=ldc, mode=mode)
+    plan.run(dA, dB, dC)
+    torch.cuda.synchronize()
+    plan.check_status()
+    plan.destroy()
+    return dC
+
+
+@pytest.mark.parametrize("tile_key,mode", [((256, 128, 2), 3), ((128, 64, 1), 1)])
+def test_static_scratch_matches_plan_path_twice(tile_key, mode):
+    tile = _lib.find_tile(*tile_key)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    # two different problems back to back: both operands need staging (odd leading dimensions)
+    for (M, N, K, pad) in ((257, 131, 203, 0), (190, 333, 77, 3)):
+        lda, ldb, ldc = K + pad, N + pad, N + pad
+        A, B = g.make_inputs(M, N, K, "normal", seed=M)
+        dA = torch.zeros(M, lda, device="cuda"); dA[:, :K] = torch.from_numpy(A).cuda()
+        dB = torch.zeros(K, ldb, device="cuda"); dB[:, :N] = torch.from_numpy(B).cuda()
+        want = _plan_result(tile, mode, dA, dB, M, N, K, lda, ldb, ldc)
+        for _ in range(2):
+            dC = torch.full((M, ldc), float("nan"), device="cuda")
+            before = torch.cuda.memory_allocated()
+            _lib.gemm_static_scratch(tile, mode, M, N, K, lda, ldb, ldc, dA.data_ptr(),
+                                     dB.data_ptr(), dC.data_ptr(), status.data_ptr())
+            torch.cuda.synchronize()
+            assert torch.cuda.memory_allocated() == before
+            assert int(status.item()) == 0
+            got, ref = dC[:, :N].cpu().numpy(), want[:, :N].cpu().numpy()
+            assert np.array_equal(got, ref)          # same kernel, same staging layout
+            err = g.err_norm(got, g.matmul_fp64(A, B))
+            assert err <= (TOL_3X if mode == 3 else TOL_1X)
+            if ldc > N:
+                assert torch.isnan(dC[:, N:]).all()
+
+
+def test_static_scratch_aligned_operands_and_default_status_word():
+    tile = _lib.find_tile(256, 256, 2)
+    M, N, K = 512, 384, 256
+    A, B = g.make_inputs(M, N, K, "uniform", seed=5)
+    dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    want = _plan_result(tile, 3, dA, dB, M, N, K, K, N, N)
+    for _ in range(2):
+        dC = torch.empty(M, N, device="cuda")
+        _lib.gemm_static_scratch(tile, 3, M, N, K, K, N, N, dA.data_ptr(), dB.data_ptr(),
+                                 dC.data_ptr())
+        torch.cuda.synchronize()
+        assert torch.equal(dC, want)
+
+
+def test_static_scratch_rejects_what_does_not_fit():
+    tile = _lib.find_tile(128, 128, 1)
+    # staging copies of 4097 x 8193 and 8193 x 2049 need ~200 MB: beyond the 32 MiB array
+    a = torch.zeros(16, device="cuda")
+    with pytest.raises(_lib.RollerError) as e:
+        _lib.gemm_static_scratch(tile, 3, 4097, 2049, 8193, 8193, 2049, 2049, a.data_ptr(),
+                                 a.data_ptr(), a.data_ptr())
+    assert e.value.status == _lib.ERR_TOO_LARGE
+    with pytest.raises(_lib.RollerError) as e:
+        _lib.gemm_static_scratch(tile, 3, 0, 8, 8, 8, 8, 8, a.data_ptr(), a.data_ptr(), a.data_ptr())
+    assert e.value.status == _lib.ERR_INVALID
