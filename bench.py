@@ -196,7 +196,7 @@ def measure_tf32_library_peak(torch, seconds: float = 1.0):
 class ShapeCase:
     """One README shape bound to its selected kernel, with resident seeded operands."""
 
-    def __init__(self, torch, idx, shape, mode, arch):
+    def __init__(self, torch, idx, shape, mode, arch, measure=True):
         from mlir_roller_b200 import roller
         from mlir_roller_b200.analyze import MatmulConfig
         self.idx, self.shape, self.mode = idx, shape, mode
@@ -208,7 +208,8 @@ class ShapeCase:
         self.C = torch.empty(m, n, device="cuda")
         cfg = MatmulConfig(m, n, k, 32)
         t0 = time.perf_counter()
-        self.hint, self.fn, self.pick_ms = roller.best_hint(cfg, arch, topk=6, mode=mode)
+        self.hint, self.fn, self.pick_ms = roller.best_hint(cfg, arch, topk=6, mode=mode,
+                                                            measure=measure)
         self.select_ms = (time.perf_counter() - t0) * 1e3
         self.plan = self.fn.plan
         self.ptrs = (self.A.data_ptr(), self.B.data_ptr(), self.C.data_ptr())
@@ -341,7 +342,8 @@ def run_gpu_arm(args) -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     arch = B200.from_device(local_rank)
 
-    cases = [ShapeCase(torch, i, s, MODE_3XTF32, arch) for i, s in enumerate(README_SHAPES)]
+    measure = args.select == "measure"
+    cases = [ShapeCase(torch, i, s, MODE_3XTF32, arch, measure) for i, s in enumerate(README_SHAPES)]
     errs = [c.error(torch) for c in cases]
     for c in cases:
         c.plan.check_status()
@@ -360,7 +362,7 @@ def run_gpu_arm(args) -> None:
     value = sweep_flops() * world / step_ms / 1e9
 
     # 1xTF32 for the per-shape report (not part of `value`)
-    cases1 = [ShapeCase(torch, i, s, MODE_1XTF32, arch) for i, s in enumerate(README_SHAPES)]
+    cases1 = [ShapeCase(torch, i, s, MODE_1XTF32, arch, measure) for i, s in enumerate(README_SHAPES)]
     errs1 = [c.error(torch) for c in cases1]
     _, per_shape_ms1 = timed_sweep(torch, cases1, max(args.steps // 2, 1), 1, None)
     del cases1
@@ -468,6 +470,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--select", default="measure", choices=["measure", "model"],
+                    help="rTile per shape: time the top hints (default) or trust the cost model")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":

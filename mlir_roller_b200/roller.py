@@ -215,19 +215,35 @@ def best_hint(config: MatmulConfig, arch=None, topk: int = 20, mode: int = MODE_
     return best
 
 
-if __name__ == "__main__":
-    S = 4096
-    config = MatmulConfig(M=S, N=S, K=S, el_bits=32)
+def _main(argv=None) -> None:
+    """Single-problem driver (the reference's `python src/roller.py`, src/roller.py:610-633):
+    baseline, search, then compile + run_eval each hint and report the fastest."""
+    import argparse
+    ap = argparse.ArgumentParser(description="Roller rTile search -> fp32 GEMM on B200, one shape")
+    ap.add_argument("--shape", type=int, nargs=3, default=[4096, 4096, 4096], metavar=("M", "N", "K"))
+    ap.add_argument("--mode", type=int, default=MODE_3XTF32, choices=[MODE_1XTF32, MODE_3XTF32])
+    ap.add_argument("--topk", type=int, default=20)
+    ap.add_argument("--repeat", type=int, default=20)
+    ap.add_argument("--no-baseline", action="store_true")
+    args = ap.parse_args(argv)
+    M, N, K = args.shape
+    config = MatmulConfig(M=M, N=N, K=K, el_bits=32)
     pipeline_depth = 2
-    hints = get_roller_hints(config, B200(), topk=20)
-    run_baseline(config)
+    hints = get_roller_hints(config, B200(), topk=args.topk, mode=args.mode)
+    if not args.no_baseline:
+        run_baseline(config)
     result_dict = {}
     for hint in hints:
-        cuda_func = Compiler(config, hint, pipeline_depth, dump_path=Path("log")).compile()
+        cuda_func = Compiler(config, hint, pipeline_depth, dump_path=Path("log"),
+                             mode=args.mode).compile()
         print(hint)
-        t, gflops = run_eval(cuda_func, pipeline_depth, hint)
+        t, gflops = run_eval(cuda_func, pipeline_depth, hint, repeat_times=args.repeat)
         print("---\n")
         result_dict[hint] = (t, gflops)
     if result_dict:
         best = min(result_dict, key=lambda h: result_dict[h][0])
         print(f"Best hint: {best}, time: {result_dict[best][0]}, GFLOPS: {result_dict[best][1]}")
+
+
+if __name__ == "__main__":
+    _main()
