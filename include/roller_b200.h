@@ -125,6 +125,13 @@ int roller_b200_gemm_set_chunk(roller_plan* plan, int k_elems);
  * at most one per tile). The reference derives its grid from the hint (src/roller.py:536). */
 int roller_b200_gemm_set_grid(roller_plan* plan, int ctas);
 
+/* Stream-K scheduling of the leftover tiles (those that do not fill a last wave of the persistent
+ * grid): -1 = use it when it shortens the schedule by 3 % or more (default), 0 = never (every
+ * tile is reduced by one worker; results are then bit-identical for every rTile and every
+ * sharding), 1 = whenever there are leftover tiles. May allocate the scratch area for the
+ * partial tiles. The reference's grid is always one block per tile (src/roller.py:536). */
+int roller_b200_gemm_set_stream_k(roller_plan* plan, int mode);
+
 /* One GEMM, enqueued on `stream`, that allocates nothing: no cudaMalloc, cudaFree or allocating
  * library call, on this or any later call. It has no counterpart in the reference (whose launch
  * path allocates freely through CuPy); it exists for callers that cannot allocate -- a process

@@ -69,6 +69,7 @@ SIGNATURES = {
     "roller_b200_gemm_launch_info": (C.c_int, [C.c_void_p] + [C.POINTER(C.c_int)] * 6),
     "roller_b200_gemm_set_chunk": (C.c_int, [C.c_void_p, C.c_int]),
     "roller_b200_gemm_set_grid": (C.c_int, [C.c_void_p, C.c_int]),
+    "roller_b200_gemm_set_stream_k": (C.c_int, [C.c_void_p, C.c_int]),
     "roller_b200_gemm_static_scratch": (C.c_int, [C.POINTER(KTile), C.c_int, C.c_int, C.c_int,
                                                   C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                                   C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
@@ -203,6 +204,11 @@ class GemmPlan:
 
     def set_grid(self, ctas: int) -> None:
         check(self._lib.roller_b200_gemm_set_grid(self._h, ctas), "roller_b200_gemm_set_grid")
+
+    def set_stream_k(self, mode: int) -> None:
+        """-1 automatic, 0 off (bit-identical results across tiles and shardings), 1 on."""
+        check(self._lib.roller_b200_gemm_set_stream_k(self._h, mode),
+              "roller_b200_gemm_set_stream_k")
 
     def launch_info(self) -> dict:
         vals = [C.c_int() for _ in range(6)]

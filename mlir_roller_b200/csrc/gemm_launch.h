@@ -21,6 +21,10 @@ struct GemmArgs {
   int chunk_kb;  // k-blocks accumulated in TMEM before a drain into registers
   int flags;
   uint32_t* status;
+  int sk_tiles;         // tiles dealt out in k-chunks (stream-K); 0 = whole tiles only
+  float* sk_ws;         // one 128 x block_n slot per CTA for partial tiles
+  uint32_t* sk_flags;   // one flag per CTA, set to `epoch` when its slot is valid
+  uint32_t epoch;       // distinguishes this launch's flags from earlier launches'
 };
 
 struct KernelVariant {

@@ -27,6 +27,16 @@
 //                 leader CTA's barrier that the stage is ready
 // With a CTA pair in MODE 1 both CTAs' TMA loads report straight to the leader's barrier.
 // Ragged M/N/K need no special main loop: TMA zero-fills out-of-range elements.
+//
+// Work distribution. Tiles are handed to the persistent workers (CTAs or CTA pairs) round-robin.
+// When the tile count does not divide by the worker count, the last, partly filled wave would
+// leave SMs idle, so the first `sk_tiles` tiles are instead cut along K into chunk-sized units
+// that are dealt evenly to all workers ("stream-K"). A worker that computes only part of a
+// tile's reduction writes its partial sums to its slot of a global scratch area and raises a
+// flag; the worker that holds the end of the tile's reduction adds the slots of the others and
+// stores C. Every worker runs its stream-K units first (the piece it must publish before the
+// piece it must complete), then its whole tiles, so these waits are short; they are bounded
+// like every other wait in the kernel.
 #pragma once
 
 #include "gemm_launch.h"
@@ -110,11 +120,74 @@ __device__ __forceinline__ void setmaxnreg_inc() {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
 }
 
+// One unit of work for all roles of a worker: k-blocks [kb0, kb1) of tile `tile`.
+struct Segment {
+  int tile;
+  int kb0, kb1;
+  bool final;  // holds the end of the tile's reduction: adds the other workers' partials, stores C
+};
+
+// Static schedule shared by the producer, split, MMA and epilogue roles (each walks its own copy).
+struct Schedule {
+  int num_tiles, workers, worker, num_kb, chunk_kb, cpt, sk_tiles;
+  long long u_begin, u_end;  // this worker's stream-K units (chunks), consumed from the end
+  int dp_next;               // next whole tile
+
+  __device__ Schedule(int num_tiles_, int workers_, int worker_, int num_kb_, int chunk_kb_,
+                      int sk_tiles_)
+      : num_tiles(num_tiles_), workers(workers_), worker(worker_), num_kb(num_kb_),
+        chunk_kb(chunk_kb_), sk_tiles(sk_tiles_) {
+    cpt = (num_kb + chunk_kb - 1) / chunk_kb;
+    u_begin = unit_begin(worker);
+    u_end = unit_begin(worker + 1);
+    dp_next = sk_tiles + worker;
+  }
+  __device__ long long unit_begin(int w) const {
+    return static_cast<long long>(sk_tiles) * cpt * w / workers;
+  }
+  __device__ bool next(Segment& s) {
+    if (u_end > u_begin) {
+      const int tile = static_cast<int>((u_end - 1) / cpt);
+      const long long t0 = static_cast<long long>(tile) * cpt;
+      const long long sb = u_begin > t0 ? u_begin : t0;
+      s.tile = tile;
+      s.kb0 = static_cast<int>(sb - t0) * chunk_kb;
+      s.kb1 = min(static_cast<int>(u_end - t0) * chunk_kb, num_kb);
+      s.final = (u_end - t0 == cpt);
+      u_end = sb;
+      return true;
+    }
+    if (dp_next < num_tiles) {
+      s.tile = dp_next;
+      s.kb0 = 0;
+      s.kb1 = num_kb;
+      s.final = true;
+      dp_next += workers;
+      return true;
+    }
+    return false;
+  }
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Barrier among the 256 accumulate/epilogue threads only (hardware barrier 1).
+__device__ __forceinline__ void epi_bar_sync() {
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+}
+
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  float* __restrict__ C, int M, int N, int K, long long ldc, int tiles_m,
-                 int tiles_n, int chunk_kb, int flags, uint32_t* status) {
+                 int tiles_n, int chunk_kb, int flags, uint32_t* status, int sk_tiles,
+                 float* sk_ws, uint32_t* sk_flags, uint32_t epoch) {
   constexpr int BN = Cfg::BN, BK = Cfg::BK, CG = Cfg::CG, STAGES = Cfg::STAGES;
 
   extern __shared__ uint8_t smem_dyn[];
@@ -129,6 +202,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   auto tmem_full_bar = [&](int a) { return ctrl + 192u + 8u * a; };
   auto tmem_empty_bar = [&](int a) { return ctrl + 208u + 8u * a; };
   const uint32_t tmem_slot = ctrl + 224u;
+  volatile uint32_t* epi_abort =
+      reinterpret_cast<volatile uint32_t*>(smem_gen + STAGES * Cfg::STAGE_BYTES + 232);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -145,6 +220,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(tmem_full_bar(a), 1);
       mbar_init(tmem_empty_bar(a), CG * Cfg::EPI_WARPS);
     }
+    *epi_abort = 0;
     fence_barrier_init();
   }
   if (warp == 1) tmem_alloc<CG>(tmem_slot, Cfg::TMEM_COLS);
@@ -159,10 +235,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
-  const int num_tiles = tiles_m * tiles_n;
-  const int num_workers = gridDim.x / CG;
-  const int worker = blockIdx.x / CG;
   const int num_kb = (K + BK - 1) / BK;
+  Schedule sched(tiles_m * tiles_n, static_cast<int>(gridDim.x) / CG,
+                 static_cast<int>(blockIdx.x) / CG, num_kb, chunk_kb, sk_tiles);
+  Segment sg;
 
   if (warp < Cfg::FIRST_EPI_WARP) {
     if constexpr (Cfg::REBALANCE) setmaxnreg_dec<Cfg::REGS_CTRL>();
@@ -171,12 +247,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int t = worker; t < num_tiles && ok; t += num_workers) {
+      while (ok && sched.next(sg)) {
         int mb, nb;
-        tile_coords(t, tiles_m, tiles_n, mb, nb);
+        tile_coords(sg.tile, tiles_m, tiles_n, mb, nb);
         const int m0 = (mb * CG + static_cast<int>(cta_rank)) * Cfg::BM;
         const int n0 = nb * BN + static_cast<int>(cta_rank) * Cfg::BNL;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!mbar_wait(empty_bar(s), ph ^ 1u, status, kDevTimeoutEmpty)) { ok = false; break; }
           const uint32_t a_dst = smem_base + s * Cfg::STAGE_BYTES;
           const uint32_t b_dst = a_dst + Cfg::A_BYTES;
@@ -211,9 +287,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int acc = 0;
       uint32_t acc_ph = 0;
       bool ok = true;
-      for (int t = worker; t < num_tiles && ok; t += num_workers) {
-        for (int kb0 = 0; kb0 < num_kb && ok; kb0 += chunk_kb) {
-          const int kb1 = min(kb0 + chunk_kb, num_kb);
+      while (ok && sched.next(sg)) {
+        for (int kb0 = sg.kb0; kb0 < sg.kb1 && ok; kb0 += chunk_kb) {
+          const int kb1 = min(kb0 + chunk_kb, sg.kb1);
           if (!mbar_wait(tmem_empty_bar(acc), acc_ph ^ 1u, status, kDevTimeoutTmemEmpty)) {
             ok = false;
             break;
@@ -272,20 +348,23 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     constexpr int COLS = Cfg::EPI_COLS;
     const int quarter = warp & 3;  // TMEM lanes a warp may read: 32 * (warp id mod 4)
     const int half = (warp - Cfg::FIRST_EPI_WARP) >> 2;
+    const int et = static_cast<int>(threadIdx.x) - Cfg::FIRST_EPI_WARP * 32;  // 0..255
     const bool accumulate = (flags & kFlagAccumulate) != 0;
     const bool vec_store = (flags & kFlagVecStore) != 0;
+    // Stream-K scratch: one slot of 128 x BN floats per CTA; thread `et` owns every 256th float4.
+    constexpr size_t kSlotFloats = static_cast<size_t>(Cfg::BM) * BN;
     int acc = 0;
     uint32_t acc_ph = 0;
     bool ok = true;
     float sum[COLS];
-    for (int t = worker; t < num_tiles && ok; t += num_workers) {
+    while (ok && sched.next(sg)) {
       int mb, nb;
-      tile_coords(t, tiles_m, tiles_n, mb, nb);
+      tile_coords(sg.tile, tiles_m, tiles_n, mb, nb);
       const int row = (mb * CG + static_cast<int>(cta_rank)) * Cfg::BM + quarter * 32 + lane;
       const int n0 = nb * BN + half * COLS;
 #pragma unroll
       for (int j = 0; j < COLS; ++j) sum[j] = 0.0f;
-      for (int kb0 = 0; kb0 < num_kb; kb0 += chunk_kb) {
+      for (int kb0 = sg.kb0; kb0 < sg.kb1; kb0 += chunk_kb) {
         if (!mbar_wait(tmem_full_bar(acc), acc_ph, status, kDevTimeoutTmemFull)) { ok = false; break; }
         tcgen05_fence_after_sync();
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
@@ -308,6 +387,53 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (acc == 0) acc_ph ^= 1u;
       }
       if (!ok) break;
+
+      if (!sg.final) {
+        // Publish this worker's partial sums of the tile, then raise its flag.
+        float4* slot = reinterpret_cast<float4*>(
+            sk_ws + (static_cast<size_t>(sched.worker) * CG + cta_rank) * kSlotFloats);
+#pragma unroll
+        for (int j = 0; j < COLS / 4; ++j)
+          slot[j * 256 + et] = make_float4(sum[4 * j], sum[4 * j + 1], sum[4 * j + 2], sum[4 * j + 3]);
+        __threadfence();
+        epi_bar_sync();
+        if (et == 0) st_release_gpu(sk_flags + sched.worker * CG + cta_rank, epoch);
+        continue;
+      }
+      if (sg.kb0 > 0) {
+        // Add the partial sums of the workers that computed the earlier parts of this tile.
+        const long long tile_u0 = static_cast<long long>(sg.tile) * sched.cpt;
+        for (int p = sched.worker - 1; p >= 0; --p) {
+          // A worker with no stream-K units (more workers than units) publishes nothing.
+          if (sched.unit_begin(p + 1) == sched.unit_begin(p)) continue;
+          if (et == 0) {
+            const uint32_t* flag = sk_flags + p * CG + cta_rank;
+            const long long t0 = clock64();
+            uint32_t spins = 0;
+            while (ld_acquire_gpu(flag) != epoch) {
+              if ((++spins & 63u) == 0) {
+                if (*reinterpret_cast<volatile uint32_t*>(status) != kDevOk) { *epi_abort = 1; break; }
+                if (clock64() - t0 > kSpinLimitCycles) {
+                  atomicCAS(status, kDevOk, kDevTimeoutFixup);
+                  *epi_abort = 1;
+                  break;
+                }
+              }
+            }
+          }
+          epi_bar_sync();
+          if (*epi_abort != 0) { ok = false; break; }
+          const float4* slot = reinterpret_cast<const float4*>(
+              sk_ws + (static_cast<size_t>(p) * CG + cta_rank) * kSlotFloats);
+#pragma unroll
+          for (int j = 0; j < COLS / 4; ++j) {
+            const float4 q = __ldcg(slot + j * 256 + et);
+            sum[4 * j] += q.x; sum[4 * j + 1] += q.y; sum[4 * j + 2] += q.z; sum[4 * j + 3] += q.w;
+          }
+          if (sched.unit_begin(p) <= tile_u0) break;  // worker p started the tile
+        }
+        if (!ok) break;
+      }
       if (row < M) {
         float* crow = C + static_cast<size_t>(row) * static_cast<size_t>(ldc);
 #pragma unroll
@@ -341,7 +467,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
   } else {
-    // ------------------------------------------------------------ split / relay warps
+    // ------------------------------------------------------------ split warps
     if constexpr (Cfg::REBALANCE) setmaxnreg_dec<Cfg::REGS_XFORM>();
     if constexpr (Cfg::HAS_XFORM) {
       if (warp < Cfg::FIRST_XFORM_WARP + Cfg::XFORM_WARPS) {
@@ -350,26 +476,24 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int s = 0;
         uint32_t ph = 0;
         bool ok = true;
-        for (int t = worker; t < num_tiles && ok; t += num_workers) {
-          for (int kb = 0; kb < num_kb; ++kb) {
+        while (ok && sched.next(sg)) {
+          for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
             if (!mbar_wait(full_bar(s), ph, status, kDevTimeoutFull)) { ok = false; break; }
-            if constexpr (Cfg::MODE == 3) {
-              // Element-wise, so the swizzled placement of the raw tile carries over unchanged.
-              const uint4* src = reinterpret_cast<const uint4*>(smem_gen + s * Cfg::STAGE_BYTES);
-              uint4* dst =
-                  reinterpret_cast<uint4*>(smem_gen + s * Cfg::STAGE_BYTES + Cfg::RAW_BYTES);
-              constexpr int kVecs = Cfg::RAW_BYTES / 16;
-              static_assert(kVecs % XT == 0, "whole passes");
+            // Element-wise, so the swizzled placement of the raw tile carries over unchanged.
+            const uint4* src = reinterpret_cast<const uint4*>(smem_gen + s * Cfg::STAGE_BYTES);
+            uint4* dst =
+                reinterpret_cast<uint4*>(smem_gen + s * Cfg::STAGE_BYTES + Cfg::RAW_BYTES);
+            constexpr int kVecs = Cfg::RAW_BYTES / 16;
+            static_assert(kVecs % XT == 0, "whole passes");
 #pragma unroll 8
-              for (int i = 0; i < kVecs / XT; ++i) {
-                const uint4 x = src[i * XT + xt];
-                uint4 y;
-                y.x = split_small(x.x); y.y = split_small(x.y);
-                y.z = split_small(x.z); y.w = split_small(x.w);
-                dst[i * XT + xt] = y;
-              }
-              fence_proxy_async_smem();
+            for (int i = 0; i < kVecs / XT; ++i) {
+              const uint4 x = src[i * XT + xt];
+              uint4 y;
+              y.x = split_small(x.x); y.y = split_small(x.y);
+              y.z = split_small(x.z); y.w = split_small(x.w);
+              dst[i * XT + xt] = y;
             }
+            fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
               if constexpr (CG == 2) mbar_arrive_cluster(ready_bar(s), 0);

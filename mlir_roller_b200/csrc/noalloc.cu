@@ -183,6 +183,10 @@ extern "C" int roller_b200_gemm_static_scratch(const roller_ktile* tile, int mod
   args.flags = 0;
   if ((ldc % 4) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) args.flags |= kFlagVecStore;
   args.status = status;
+  args.sk_tiles = 0;  // whole tiles only: the stream-K schedule needs a scratch area per CTA
+  args.sk_ws = nullptr;
+  args.sk_flags = nullptr;
+  args.epoch = 0;
   const long long tiles = static_cast<long long>(args.tiles_m) * args.tiles_n;
   const int workers = dev->sm_count / kv->cta_group;
   const int grid = static_cast<int>(tiles < workers ? tiles : workers) * kv->cta_group;

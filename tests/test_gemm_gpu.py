@@ -22,7 +22,8 @@ ALL_TILES = [(256, 256, 2), (256, 128, 2), (256, 64, 2), (128, 256, 1), (128, 12
 GOLDEN = np.load(Path(__file__).resolve().parent / "golden" / "gemm_golden.npz")
 
 
-def gpu_gemm(A, B, tile, mode, *, lda=None, ldb=None, ldc=None, flags=0, C0=None, chunk=None):
+def gpu_gemm(A, B, tile, mode, *, lda=None, ldb=None, ldc=None, flags=0, C0=None, chunk=None,
+             stream_k=None, info=None):
     """Run one GEMM through roller_b200_gemm_create/run on numpy operands; returns C (numpy)."""
     M, K = A.shape
     N = B.shape[1]
@@ -38,6 +39,10 @@ def gpu_gemm(A, B, tile, mode, *, lda=None, ldb=None, ldc=None, flags=0, C0=None
                          flags=flags)
     if chunk is not None:
         plan.set_chunk(chunk)
+    if stream_k is not None:
+        plan.set_stream_k(stream_k)
+    if info is not None:
+        info.update(plan.launch_info())
     plan.run(dA, dB, dC)
     torch.cuda.synchronize()
     plan.check_status()
@@ -120,10 +125,11 @@ def test_chunk_length_trades_accuracy():
 
 
 def test_all_tiles_agree_bit_for_bit():
-    # every tile walks k in the same order and drains at the same chunk boundaries
+    # every tile walks k in the same order and drains at the same chunk boundaries (with whole
+    # tiles per worker; a stream-K split changes the association of the chunk sums)
     A, B = g.make_inputs(300, 520, 700, "normal", seed=2)
     for mode in (1, 3):
-        outs = [gpu_gemm(A, B, t, mode) for t in ALL_TILES]
+        outs = [gpu_gemm(A, B, t, mode, stream_k=0) for t in ALL_TILES]
         for o in outs[1:]:
             assert np.array_equal(o, outs[0]), mode
 
@@ -266,9 +272,52 @@ def test_row_shards_equal_the_whole():
     # concatenation of shard results is bit-identical to the unsharded result
     M, N, K = 2048, 1024, 1536
     A, B = g.make_inputs(M, N, K, "uniform", seed=13)
-    whole = gpu_gemm(A, B, (256, 256, 2), 3)
-    parts = [gpu_gemm(A[r:r + 512], B, (128, 128, 1), 3) for r in range(0, M, 512)]
+    whole = gpu_gemm(A, B, (256, 256, 2), 3, stream_k=0)
+    parts = [gpu_gemm(A[r:r + 512], B, (128, 128, 1), 3, stream_k=0) for r in range(0, M, 512)]
     assert np.array_equal(np.concatenate(parts), whole)
+    # with the automatic schedule (stream-K where it pays) the shards agree to rounding
+    auto = np.concatenate([gpu_gemm(A[r:r + 512], B, (128, 128, 1), 3) for r in range(0, M, 512)])
+    assert np.abs(auto - whole).max() <= 4e-6 * np.abs(whole).max()
+
+
+@pytest.mark.parametrize("tile", ALL_TILES)
+@pytest.mark.parametrize("mode", [1, 3])
+def test_stream_k_schedule(tile, mode):
+    # leftover tiles are cut along K and dealt to all workers; partial tiles meet in scratch memory
+    cases = [(512, 512, 2048),     # 4..32 tiles, each split many ways (one chunk per worker)
+             (2048, 2048, 2048),   # README M0: fewer tiles than workers
+             (1300, 1100, 1000),   # ragged, a few whole tiles plus split ones
+             (2560, 2304, 512)]    # more tiles than workers: whole tiles + split leftovers
+    for (M, N, K) in cases:
+        A, B = g.make_inputs(M, N, K, "uniform", seed=K)
+        C64 = g.matmul_fp64(A, B)
+        info = {}
+        on = gpu_gemm(A, B, tile, mode, stream_k=1, chunk=128, info=info)
+        assert not np.isnan(on).any()
+        err = g.err_norm(on, C64)
+        assert err <= (TIGHT_3X if mode == 3 else TOL_1X), (tile, mode, (M, N, K), err, info)
+        off = gpu_gemm(A, B, tile, mode, stream_k=0, chunk=128)
+        assert np.abs(on - off).max() <= (4e-6 if mode == 3 else 1e-5) * np.abs(C64).max()
+        assert np.array_equal(gpu_gemm(A, B, tile, mode, stream_k=1, chunk=128), on)  # deterministic
+
+
+def test_stream_k_back_to_back_launches_reuse_the_scratch_area():
+    M, N, K = 2048, 2048, 1024
+    A, B = g.make_inputs(M, N, K, "normal", seed=3)
+    dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    plan = _lib.GemmPlan(_lib.find_tile(256, 256, 2), M, N, K, mode=3)
+    plan.set_stream_k(1)
+    outs = []
+    for _ in range(4):
+        dC = torch.full((M, N), float("nan"), device="cuda")
+        plan.run(dA, dB, dC)
+        outs.append(dC)
+    torch.cuda.synchronize()
+    plan.check_status()
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])
+    assert g.err_norm(outs[0].cpu().numpy(), g.matmul_fp64(A, B)) <= TIGHT_3X
+    plan.destroy()
 
 
 def test_linearity_in_scale():
