@@ -105,13 +105,26 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------ CPU baseline / reference arm
+_blas_limit = None
+
+
+def _use_all_host_threads() -> None:
+    """torchrun exports OMP_NUM_THREADS=1; the CPU baseline is meant to use every host core, so
+    the BLAS pool is widened again at run time."""
+    global _blas_limit
+    if _blas_limit is None:
+        from threadpoolctl import threadpool_limits
+        from oracle import gemm_oracle
+        _blas_limit = threadpool_limits(limits=gemm_oracle.host_threads())
+
+
 def cpu_reference_pass(shapes, budget_s: float):
     """One pass of the reference's CPU path over `shapes` (numpy fp32 matmul on all host
     threads + the search restatement), stopped once `budget_s` of matmul time is spent.
     Returns (flops done, matmul seconds, mean search ms, shapes done)."""
-    import numpy as np
     from oracle import gemm_oracle, search_port
     flops, secs, done, search_ms = 0.0, 0.0, 0, []
+    _use_all_host_threads()
     for i, (m, n, k) in enumerate(shapes):
         t0 = time.perf_counter()
         search_port.roller_hints(m, n, k, topk=20)
