@@ -326,7 +326,10 @@ class BlackwellPolicy:
                    + bytes the MMAs read) / smem_bytes_per_clk                   clocks
         l2      = raw operand bytes / l2_bytes_per_clk                            clocks
       a tile takes ceil(K / rstep) * max(tensor, smem, l2) clocks, a persistent worker runs
-      ceil(tiles / workers) tiles, and the whole GEMM cannot beat its HBM floor.
+      ceil(tiles / workers) tiles (a fractional last wave when the library would use its
+      stream-K schedule), and the whole GEMM cannot beat its HBM floor.
+    Where the device model carries measured per-k-block times for a tile (`B200.kblock_us`),
+    those replace the analytic per-k-block term.
     """
 
     def __init__(self, config: MatmulConfig, arch: B200, mode: int = MODE_3XTF32) -> None:
@@ -356,18 +359,35 @@ class BlackwellPolicy:
         td.num_wave = -(-td.grid_size // workers)
 
         num_kb = -(-cfg.K // dev.rstep)
-        tensor_clk = rows_cta * block_n * dev.rstep * mode / dev.tf32_macs_per_clk_sm
-        mma_reads = (rows_cta + cols_cta) * dev.mma_k * 4 * (dev.rstep // dev.mma_k) * mode
-        split_rw = 2 * raw if mode == MODE_3XTF32 else 0
-        smem_clk = (raw + split_rw + mma_reads) / dev.smem_bytes_per_clk_sm
-        l2_clk = raw / dev.l2_bytes_per_clk_sm
-        tile_clk = num_kb * max(tensor_clk, smem_clk, l2_clk)
-        # drain of the accumulator into registers + C stores, exposed once per worker
-        tail_clk = rows_cta * block_n / 128.0 * 4
-        worker_us = (td.num_wave * tile_clk + tail_clk) / dev.sm_clock_mhz
+        measured = dev.kblock_us.get((block_m, block_n, cta_group))
+        if measured is not None:
+            kb_us = measured[0] if mode == MODE_1XTF32 else measured[1]
+        else:
+            tensor_clk = rows_cta * block_n * dev.rstep * mode / dev.tf32_macs_per_clk_sm
+            mma_reads = (rows_cta + cols_cta) * dev.mma_k * 4 * (dev.rstep // dev.mma_k) * mode
+            split_rw = 2 * raw if mode == MODE_3XTF32 else 0
+            smem_clk = (raw + split_rw + mma_reads) / dev.smem_bytes_per_clk_sm
+            l2_clk = raw / dev.l2_bytes_per_clk_sm
+            kb_us = max(tensor_clk, smem_clk, l2_clk) / dev.sm_clock_mhz
+        # Whole tiles go round-robin; leftover tiles are dealt out in k-chunks (stream-K) when
+        # whole tiles follow them and that shortens the schedule by 3 % or more -- the same rule
+        # the library applies (3xTF32 only: 1xTF32 reduces a tile in one chunk).
+        full, left = divmod(td.grid_size, workers)
+        waves = float(td.num_wave)
+        if mode == MODE_3XTF32 and left and full >= 1 and (1.0 - left / workers) >= 0.03 * (full + 1):
+            waves = full + left / workers
+        # launch, pipeline fill, last drain and the C stores of the final tile
+        fixed_us = 8.0 + rows_cta * block_n * 4 / 32768.0
+        worker_us = waves * num_kb * kb_us + fixed_us
         hbm_bytes = 4.0 * (cfg.M * cfg.K + cfg.K * cfg.N + cfg.M * cfg.N)
-        hbm_us = hbm_bytes / (dev.hbm_gbs * 1e3)
-        td.est_us = max(worker_us, hbm_us) + 3.0  # launch + pipeline fill
+        hbm_us = hbm_bytes / (dev.hbm_gbs * 1e3) + 4.0
+        td.est_us = max(worker_us, hbm_us)
+        # operands whose rows are not 16-byte aligned are first copied into padded buffers
+        # (one read + one write each, ahead of the GEMM)
+        if cfg.K % 4:
+            td.est_us += 8.0 * cfg.M * cfg.K / (dev.hbm_gbs * 1e3) * 1.5 + 3.0
+        if cfg.N % 4:
+            td.est_us += 8.0 * cfg.K * cfg.N / (dev.hbm_gbs * 1e3) * 1.5 + 3.0
         td.kernel = f"gemm_tf32<{block_m}x{block_n}x{dev.rstep},cg{cta_group},{mode}x>"
         return td
 

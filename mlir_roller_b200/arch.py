@@ -67,6 +67,21 @@ B200_KERNEL_TILES: Tuple[Tuple[int, int, int, int, int], ...] = (
 )
 
 
+# Measured steady-state cost of one 32-deep k-block on one worker (CTA or CTA pair), in
+# microseconds, per compiled rTile: (block_m, block_n, cta_group) -> (1xTF32, 3xTF32).
+# Taken on a B200 at 4096 x 8192 x 16384 (clock ~1.7 GHz under the power cap). The 256x256 pair
+# tile runs near the tensor rate; narrower tiles are held back by shared-memory bandwidth and,
+# in 3xTF32, by the split pass competing with fewer pipeline stages.
+B200_KBLOCK_US = {
+    (256, 256, 2): (0.410, 1.114),
+    (256, 128, 2): (0.320, 0.803),
+    (256, 64, 2): (0.275, 0.690),
+    (128, 256, 1): (0.515, 1.521),
+    (128, 128, 1): (0.321, 0.927),
+    (128, 64, 1): (0.278, 0.702),
+}
+
+
 @dataclass
 class B200(TileDevice):
     """NVIDIA B200 (sm_100a): 148 SMs, 227 KiB shared memory per block, tensor memory.
@@ -100,6 +115,7 @@ class B200(TileDevice):
     hbm_gbs: float = 6532.0             # measured copy bandwidth
     tf32_tflops: float = 790.0          # measured dense TF32 rate (cuBLAS, 8192^3)
     kernel_tiles: Tuple[Tuple[int, int, int, int, int], ...] = B200_KERNEL_TILES
+    kblock_us: dict = field(default_factory=lambda: dict(B200_KBLOCK_US))
 
     @classmethod
     def from_device(cls, dev: int = 0) -> "B200":

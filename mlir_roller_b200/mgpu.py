@@ -99,20 +99,29 @@ def gather_blocks(local, blocks: Sequence[Block], M: int, N: int, rank: int, roo
         raise ValueError(f"rank {rank}: block is {tuple(local.shape)}, expected {(mine.rows, mine.cols)}")
     if rank != root:
         if mine.rows * mine.cols > 0:
-            dist.send(local.contiguous(), dst=root, group=group)
+            for req in dist.batch_isend_irecv([dist.P2POp(dist.isend, local.contiguous(), root,
+                                                          group=group)]):
+                req.wait()
         return None
     full = out if out is not None else torch.empty((M, N), dtype=local.dtype, device=local.device)
     full[mine.row0:mine.row1, mine.col0:mine.col1].copy_(local)
+    ops, staged = [], []
     for b in blocks:
         if b.rank == root or b.rows * b.cols == 0:
             continue
         if b.col0 == 0 and b.col1 == N:
             # a band of whole rows is contiguous in C: receive in place
-            dist.recv(full[b.row0:b.row1], src=b.rank, group=group)
+            ops.append(dist.P2POp(dist.irecv, full[b.row0:b.row1], b.rank, group=group))
         else:
             tmp = torch.empty((b.rows, b.cols), dtype=local.dtype, device=local.device)
-            dist.recv(tmp, src=b.rank, group=group)
-            full[b.row0:b.row1, b.col0:b.col1].copy_(tmp)
+            ops.append(dist.P2POp(dist.irecv, tmp, b.rank, group=group))
+            staged.append((b, tmp))
+    if ops:
+        # one batch: all senders stream into the root at once instead of one after another
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+    for b, tmp in staged:
+        full[b.row0:b.row1, b.col0:b.col1].copy_(tmp)
     return full
 
 

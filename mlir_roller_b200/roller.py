@@ -83,13 +83,14 @@ class Compiler:
 
     def __init__(self, config: MatmulConfig, hint: TileDict, pipeline_depth: int = 2,
                  dump_path: Optional[Path] = None, mode: Optional[int] = None,
-                 accumulate: bool = False):
+                 accumulate: bool = False, stream_k: int = -1):
         self.config = config
         self.hint = hint
         self.pipeline_depth = pipeline_depth
         self.dump_path = dump_path
         self.mode = mode if mode is not None else (getattr(hint, "mode", None) or MODE_3XTF32)
         self.accumulate = accumulate
+        self.stream_k = stream_k  # -1 automatic, 0 off, 1 whenever tiles are left over
 
     def compile(self) -> CompiledGemm:
         _torch()
@@ -98,6 +99,8 @@ class Compiler:
         tile = kernel_tile_for(self.hint)
         plan = _lib.GemmPlan(tile, self.config.M, self.config.N, self.config.K, mode=self.mode,
                              flags=_lib.FLAG_ACCUMULATE if self.accumulate else 0)
+        if self.stream_k != -1:
+            plan.set_stream_k(self.stream_k)
         return CompiledGemm(plan, self.hint)
 
 
@@ -225,6 +228,7 @@ def _main(argv=None) -> None:
     ap.add_argument("--topk", type=int, default=20)
     ap.add_argument("--repeat", type=int, default=20)
     ap.add_argument("--no-baseline", action="store_true")
+    ap.add_argument("--stream-k", type=int, default=-1, choices=[-1, 0, 1])
     args = ap.parse_args(argv)
     M, N, K = args.shape
     config = MatmulConfig(M=M, N=N, K=K, el_bits=32)
@@ -235,7 +239,7 @@ def _main(argv=None) -> None:
     result_dict = {}
     for hint in hints:
         cuda_func = Compiler(config, hint, pipeline_depth, dump_path=Path("log"),
-                             mode=args.mode).compile()
+                             mode=args.mode, stream_k=args.stream_k).compile()
         print(hint)
         t, gflops = run_eval(cuda_func, pipeline_depth, hint, repeat_times=args.repeat)
         print("---\n")

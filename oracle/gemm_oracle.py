@@ -90,10 +90,10 @@ def tf32_trunc(x: np.ndarray) -> np.ndarray:
 
 def split_small(x: np.ndarray) -> np.ndarray:
     """What the split warps store: x - trunc19(x), exact in fp32, then rounded to the 19-bit
-    grid by adding half a unit before the hardware truncation; zero for inf/nan."""
+    grid by adding half a unit before the hardware truncation; nan for inf/nan (inf - inf)."""
     x = x.astype(np.float32)
-    small = x - tf32_trunc(x)
-    small = np.where(np.isfinite(x), small, np.float32(0)).astype(np.float32)
+    with np.errstate(invalid="ignore"):
+        small = (x - tf32_trunc(x)).astype(np.float32)
     bits = (small.view(np.uint32) + np.uint32(0x1000)) & np.uint32(0xFFFFE000)
     return bits.view(np.float32)
 

@@ -22,11 +22,9 @@ static uint32_t float_to_bits(float f) { uint32_t b; memcpy(&b, &f, 4); return b
 /* the 19 bits of an fp32 word the tensor core reads */
 static float trunc19(float x) { return bits_to_float(float_to_bits(x) & 0xFFFFE000u); }
 
-/* x - trunc19(x), rounded to nearest on the 19-bit grid; 0 for inf/nan */
+/* x - trunc19(x), rounded to nearest on the 19-bit grid; nan for inf/nan (inf - inf) */
 float oracle_split_small(float x) {
-  uint32_t xb = float_to_bits(x);
   float s = x - trunc19(x);
-  if ((xb & 0x7F800000u) == 0x7F800000u) s = 0.0f;
   return bits_to_float((float_to_bits(s) + 0x1000u) & 0xFFFFE000u);
 }
 
