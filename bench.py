@@ -279,11 +279,21 @@ def e2e_sweep(torch, cases, steps):
     for c, (hA, hB, hC) in zip(cases, host):   # warm-up: allocates the plan-owned buffers
         c.plan.run_host(hA, hB, hC)
     torch.cuda.synchronize()
+    # Shapes are spread over three streams so that one GEMM's upload, another's kernel and a
+    # third's readback overlap (the two PCIe directions are independent); a shape always uses
+    # the same stream, so its plan-owned buffers are never touched by two launches at once.
+    streams = [torch.cuda.Stream() for _ in range(3)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
+    for st in streams:
+        st.wait_event(e0)
     for _ in range(steps):
-        for c, (hA, hB, hC) in zip(cases, host):
-            c.plan.run_host(hA, hB, hC)
+        for i, (c, (hA, hB, hC)) in enumerate(zip(cases, host)):
+            c.plan.run_host(hA, hB, hC, stream=streams[i % 3], wait=False)
+    for st in streams:
+        done = torch.cuda.Event()
+        done.record(st)
+        torch.cuda.current_stream().wait_event(done)
     e1.record()
     e1.synchronize()
     h2d = sum(a.numel() * 4 + b.numel() * 4 for a, b, _ in host)

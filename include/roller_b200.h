@@ -44,6 +44,10 @@ typedef enum roller_status {
 /* Flags for roller_b200_gemm_create. */
 #define ROLLER_FLAG_ACCUMULATE 1 /* C += A@B, the semantics of the reference's gemm_kernel, which
                                     accumulates into a host-zeroed C (src/roller.py:62,534) */
+#define ROLLER_FLAG_B_TRANSPOSED 2 /* B is passed as Bt[N,K] row-major (ldb >= K); the reference's
+                                      cost model already treats B that way (src/analyze.py:33-34)
+                                      and its tutorial kernels pre-transpose B
+                                      (src/cuda_matmul_opt.py:280-281,376-392) */
 
 /* Device facts feeding the B200 device model of the search (reference: the constants hard-coded
  * in arch.CUDA, src/arch.py:47-61). */
@@ -76,6 +80,8 @@ typedef struct roller_ktile {
   int tmem_cols; /* TMEM columns allocated (double-buffered accumulator) */
   int threads_1x;
   int threads_3x;
+  int layout;    /* 0 = general tile; 2 = "skinny": for a C with few rows the tensor core works on
+                    C^T, block_m (32 or 64) rows of C by block_n = 128 columns per tile */
 } roller_ktile;
 
 typedef struct roller_plan roller_plan;
@@ -109,6 +115,13 @@ int roller_b200_gemm_time(roller_plan* plan, const float* A, const float* B, flo
  * has arrived. The device buffers are allocated on the first call and kept. */
 int roller_b200_gemm_host(roller_plan* plan, const float* hA, const float* hB, float* hC,
                           void* stream);
+
+/* Same data path as roller_b200_gemm_host (src/roller.py:532-550) without the final wait: the
+ * copies and the launch are only enqueued on `stream`, so GEMMs on different streams overlap
+ * their uploads, kernels and readbacks. Host buffers should be pinned; hC is valid once `stream`
+ * has been synchronised. */
+int roller_b200_gemm_host_async(roller_plan* plan, const float* hA, const float* hB, float* hC,
+                                void* stream);
 
 /* Launch geometry the plan chose (the reference derives grid/block from the hint,
  * src/roller.py:536-543). Any out pointer may be NULL. */

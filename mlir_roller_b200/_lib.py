@@ -13,6 +13,9 @@ LIB_PATH = Path(__file__).resolve().parent / "libroller_b200.so"
 MODE_1XTF32 = 1
 MODE_3XTF32 = 3
 FLAG_ACCUMULATE = 1
+FLAG_B_TRANSPOSED = 2
+LAYOUT_GENERAL = 0
+LAYOUT_SKINNY = 2
 
 OK = 0
 ERR_INVALID = -1
@@ -48,6 +51,7 @@ class KTile(C.Structure):
         ("smem_1x", C.c_int), ("smem_3x", C.c_int),
         ("tmem_cols", C.c_int),
         ("threads_1x", C.c_int), ("threads_3x", C.c_int),
+        ("layout", C.c_int),
     ]
 
     def as_dict(self) -> dict:
@@ -66,6 +70,8 @@ SIGNATURES = {
     "roller_b200_gemm_time": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                         C.c_int, C.c_int, C.POINTER(C.c_float)]),
     "roller_b200_gemm_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "roller_b200_gemm_host_async": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                              C.c_void_p]),
     "roller_b200_gemm_launch_info": (C.c_int, [C.c_void_p] + [C.POINTER(C.c_int)] * 6),
     "roller_b200_gemm_set_chunk": (C.c_int, [C.c_void_p, C.c_int]),
     "roller_b200_gemm_set_grid": (C.c_int, [C.c_void_p, C.c_int]),
@@ -134,12 +140,13 @@ def kernel_tiles() -> list[KTile]:
     return out
 
 
-def find_tile(block_m: int, block_n: int, cta_group: int | None = None) -> KTile:
+def find_tile(block_m: int, block_n: int, cta_group: int | None = None,
+              layout: int = LAYOUT_GENERAL) -> KTile:
     for kt in kernel_tiles():
-        if kt.block_m == block_m and kt.block_n == block_n and \
+        if kt.block_m == block_m and kt.block_n == block_n and kt.layout == layout and \
                 (cta_group is None or kt.cta_group == cta_group):
             return kt
-    raise RollerError(ERR_UNSUPPORTED, f"find_tile({block_m}, {block_n}, {cta_group})")
+    raise RollerError(ERR_UNSUPPORTED, f"find_tile({block_m}, {block_n}, {cta_group}, {layout})")
 
 
 def _stream_ptr(stream) -> C.c_void_p:
@@ -171,7 +178,7 @@ class GemmPlan:
         self.tile = tile
         self.M, self.N, self.K, self.mode = M, N, K, mode
         self.lda = K if lda is None else lda
-        self.ldb = N if ldb is None else ldb
+        self.ldb = (K if flags & FLAG_B_TRANSPOSED else N) if ldb is None else ldb
         self.ldc = N if ldc is None else ldc
         check(self._lib.roller_b200_gemm_create(C.byref(tile), M, N, K, self.lda, self.ldb,
                                                 self.ldc, mode, flags, C.byref(self._h)),
@@ -192,12 +199,13 @@ class GemmPlan:
               "roller_b200_gemm_time")
         return float(ms.value)
 
-    def run_host(self, hA, hB, hC, stream=None) -> None:
-        """hA/hB/hC: contiguous fp32 host arrays (numpy or pinned torch CPU tensors)."""
+    def run_host(self, hA, hB, hC, stream=None, wait: bool = True) -> None:
+        """hA/hB/hC: contiguous fp32 host arrays (numpy or pinned torch CPU tensors). With
+        `wait=False` the upload, kernel and readback are only enqueued on `stream`."""
         def ptr(x):
             return x.ctypes.data if hasattr(x, "ctypes") else x.data_ptr()
-        check(self._lib.roller_b200_gemm_host(self._h, ptr(hA), ptr(hB), ptr(hC),
-                                              _stream_ptr(stream)), "roller_b200_gemm_host")
+        fn = self._lib.roller_b200_gemm_host if wait else self._lib.roller_b200_gemm_host_async
+        check(fn(self._h, ptr(hA), ptr(hB), ptr(hC), _stream_ptr(stream)), "roller_b200_gemm_host")
 
     def set_chunk(self, k_elems: int) -> None:
         check(self._lib.roller_b200_gemm_set_chunk(self._h, k_elems), "roller_b200_gemm_set_chunk")

@@ -109,7 +109,7 @@ class TileDict:
     `matmul_config` (src/roller.py:363-366,385,531-543); the Blackwell policy adds the fields
     listed in `BLACKWELL_FIELDS`."""
 
-    BLACKWELL_FIELDS = ("cta_group", "stages", "mode", "tmem_cols", "est_us", "kernel")
+    BLACKWELL_FIELDS = ("cta_group", "stages", "mode", "tmem_cols", "est_us", "kernel", "layout")
 
     def __init__(self, block_tile: List[int], matmul_config: MatmulConfig, rstep: int) -> None:
         self.matmul_config = matmul_config
@@ -129,6 +129,7 @@ class TileDict:
         self.tmem_cols: Optional[int] = None
         self.est_us: Optional[float] = None
         self.kernel: Optional[str] = None
+        self.layout: int = 0   # 0 general tile, 2 skinny tile (tensor core works on C^T)
 
     def __hash__(self) -> int:
         return hash(tuple(self.block_tile + self.thread_tile))
@@ -341,12 +342,14 @@ class BlackwellPolicy:
         self.arch = arch
         self.mode = mode
 
-    def _analyse(self, block_m: int, block_n: int, cta_group: int, stages: int) -> TileDict:
+    def _analyse(self, block_m: int, block_n: int, cta_group: int, stages: int,
+                 layout: int = 0) -> TileDict:
         cfg, dev, mode = self.matmul_config, self.arch, self.mode
         td = TileDict([block_m, block_n], cfg, dev.rstep)
-        td.cta_group, td.stages, td.mode = cta_group, stages, mode
+        td.cta_group, td.stages, td.mode, td.layout = cta_group, stages, mode, layout
         td.thread_tile = [1, 32]  # what one epilogue thread reads from TMEM at a time
-        td.tmem_cols = 2 * block_n
+        # the accumulator's columns are the tile's N side, or its M side in the skinny layout
+        td.tmem_cols = 2 * (block_m if layout == 2 else block_n)
         rows_cta = block_m // cta_group          # A rows staged per CTA
         cols_cta = block_n // cta_group          # B columns staged per CTA
         raw = (rows_cta + cols_cta) * dev.rstep * 4
@@ -359,7 +362,8 @@ class BlackwellPolicy:
         td.num_wave = -(-td.grid_size // workers)
 
         num_kb = -(-cfg.K // dev.rstep)
-        measured = dev.kblock_us.get((block_m, block_n, cta_group))
+        measured = dev.kblock_us.get((block_m, block_n, cta_group)) if layout == 0 else \
+            dev.kblock_us.get((block_m, block_n, cta_group, layout))
         if measured is not None:
             kb_us = measured[0] if mode == MODE_1XTF32 else measured[1]
         else:
@@ -376,6 +380,8 @@ class BlackwellPolicy:
         waves = float(td.num_wave)
         if mode == MODE_3XTF32 and left and full >= 1 and (1.0 - left / workers) >= 0.03 * (full + 1):
             waves = full + left / workers
+        if layout == 2 and left:
+            waves = full + left / workers   # the skinny layout always splits along K
         # launch, pipeline fill, last drain and the C stores of the final tile
         fixed_us = 8.0 + rows_cta * block_n * 4 / 32768.0
         worker_us = waves * num_kb * kb_us + fixed_us
@@ -388,12 +394,13 @@ class BlackwellPolicy:
             td.est_us += 8.0 * cfg.M * cfg.K / (dev.hbm_gbs * 1e3) * 1.5 + 3.0
         if cfg.N % 4:
             td.est_us += 8.0 * cfg.K * cfg.N / (dev.hbm_gbs * 1e3) * 1.5 + 3.0
-        td.kernel = f"gemm_tf32<{block_m}x{block_n}x{dev.rstep},cg{cta_group},{mode}x>"
+        td.kernel = (f"gemm_tf32<{block_m}x{block_n}x{dev.rstep},cg{cta_group},{mode}x"
+                     + (",skinny>" if layout == 2 else ">"))
         return td
 
     def emit_config(self, topk: int = 10) -> List[TileDict]:
-        tiles = [self._analyse(bm, bn, cg, s1 if self.mode == MODE_1XTF32 else s3)
-                 for (bm, bn, cg, s1, s3) in self.arch.kernel_tiles]
+        tiles = [self._analyse(bm, bn, cg, s1 if self.mode == MODE_1XTF32 else s3, layout)
+                 for (bm, bn, cg, s1, s3, layout) in self.arch.kernel_tiles]
         tiles = [td for td in tiles if td.valid]
         tiles.sort(key=lambda td: (td.est_us, td.traffic * td.grid_size))
         return tiles[:topk]

@@ -55,15 +55,19 @@ class CUDA(TileDevice):
 
 
 # rTiles for which libroller_b200 carries a compiled kernel:
-# (block_m, block_n, cta_group, stages_1x, stages_3x). Kept in step with the library by a test
-# that compares it against roller_b200_kernel_desc().
-B200_KERNEL_TILES: Tuple[Tuple[int, int, int, int, int], ...] = (
-    (256, 256, 2, 7, 3),
-    (256, 128, 2, 8, 4),
-    (256, 64, 2, 8, 5),
-    (128, 256, 1, 4, 2),
-    (128, 128, 1, 7, 3),
-    (128, 64, 1, 8, 4),
+# (block_m, block_n, cta_group, stages_1x, stages_3x, layout). Layout 0 is the general tile;
+# layout 2 is the "skinny" tile for a C with few rows (the tensor core works on C^T, so the
+# narrow side, block_m, runs along M). Kept in step with the library by a test that compares
+# the table against roller_b200_kernel_desc().
+B200_KERNEL_TILES: Tuple[Tuple[int, int, int, int, int, int], ...] = (
+    (256, 256, 2, 7, 3, 0),
+    (256, 128, 2, 8, 4, 0),
+    (256, 64, 2, 8, 5, 0),
+    (128, 256, 1, 4, 2, 0),
+    (128, 128, 1, 7, 3, 0),
+    (128, 64, 1, 8, 4, 0),
+    (64, 128, 1, 8, 4, 2),
+    (32, 128, 1, 8, 5, 2),
 )
 
 
@@ -114,7 +118,7 @@ class B200(TileDevice):
     sm_clock_mhz: float = 1700.0        # typical clock under tensor load (1965 boost)
     hbm_gbs: float = 6532.0             # measured copy bandwidth
     tf32_tflops: float = 790.0          # measured dense TF32 rate (cuBLAS, 8192^3)
-    kernel_tiles: Tuple[Tuple[int, int, int, int, int], ...] = B200_KERNEL_TILES
+    kernel_tiles: Tuple[Tuple[int, int, int, int, int, int], ...] = B200_KERNEL_TILES
     kblock_us: dict = field(default_factory=lambda: dict(B200_KBLOCK_US))
 
     @classmethod
@@ -131,6 +135,6 @@ class B200(TileDevice):
         model.tmem_columns = info.tmem_columns
         model.compute_capability = f"{info.cc_major}{info.cc_minor}a"
         model.kernel_tiles = tuple(
-            (kt.block_m, kt.block_n, kt.cta_group, kt.stages_1x, kt.stages_3x)
+            (kt.block_m, kt.block_n, kt.cta_group, kt.stages_1x, kt.stages_3x, kt.layout)
             for kt in _lib.kernel_tiles())
         return model

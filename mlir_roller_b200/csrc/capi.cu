@@ -96,6 +96,7 @@ struct roller_plan {
   int M, N, K;
   long long lda, ldb, ldc;
   int mode, flags;
+  int layout;             // 0 plain, 1 B given transposed, 2 skinny (roles swapped)
   int tiles_m, tiles_n, grid;
   int chunk_kb;           // accumulation chunk, in 32-element k-blocks
   int max_clusters;       // co-resident CTA pairs the device reports (cta_group 2 only)
@@ -147,15 +148,31 @@ int roller_b200_device_info(int dev, roller_dev_info* out) {
   return ROLLER_OK;
 }
 
+// Index (into the variant table) of the 1xTF32 entry of the idx-th enumerable rTile. The table
+// holds the two modes of a tile next to each other; variants for a transposed B share the
+// geometry of the plain tiles and are reached through ROLLER_FLAG_B_TRANSPOSED instead.
+static int enumerable_variant(int idx) {
+  int seen = 0;
+  for (int i = 0; i + 1 < variant_count(); i += 2) {
+    if (variant_at(i).layout == 1) continue;
+    if (seen == idx) return i;
+    ++seen;
+  }
+  return -1;
+}
+
 int roller_b200_kernel_count(void) {
-  // One entry per (block_n, cta_group): the table holds both modes of each tile.
-  return variant_count() / 2;
+  int n = 0;
+  while (enumerable_variant(n) >= 0) ++n;
+  return n;
 }
 
 int roller_b200_kernel_desc(int idx, roller_ktile* out) {
-  if (!out || idx < 0 || idx >= roller_b200_kernel_count()) return ROLLER_ERR_INVALID;
-  const KernelVariant& v1 = variant_at(2 * idx);
-  const KernelVariant& v3 = variant_at(2 * idx + 1);
+  if (!out || idx < 0) return ROLLER_ERR_INVALID;
+  const int vi = enumerable_variant(idx);
+  if (vi < 0) return ROLLER_ERR_INVALID;
+  const KernelVariant& v1 = variant_at(vi);
+  const KernelVariant& v3 = variant_at(vi + 1);
   out->block_m = v1.block_m;
   out->block_n = v1.block_n;
   out->rstep = v1.rstep;
@@ -167,6 +184,7 @@ int roller_b200_kernel_desc(int idx, roller_ktile* out) {
   out->tmem_cols = v1.tmem_cols;
   out->threads_1x = v1.threads;
   out->threads_3x = v3.threads;
+  out->layout = v1.layout;
   return ROLLER_OK;
 }
 
@@ -174,11 +192,16 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
                             int mode, int flags, roller_plan** out) {
   if (!tile || !out) return ROLLER_ERR_INVALID;
   *out = nullptr;
-  if (M <= 0 || N <= 0 || K <= 0 || lda < K || ldb < N || ldc < N) return ROLLER_ERR_INVALID;
+  if (flags & ~(ROLLER_FLAG_ACCUMULATE | ROLLER_FLAG_B_TRANSPOSED)) return ROLLER_ERR_INVALID;
+  const bool b_transposed = (flags & ROLLER_FLAG_B_TRANSPOSED) != 0;
+  if (M <= 0 || N <= 0 || K <= 0 || lda < K || ldb < (b_transposed ? K : N) || ldc < N)
+    return ROLLER_ERR_INVALID;
   if (mode != ROLLER_MODE_1XTF32 && mode != ROLLER_MODE_3XTF32) return ROLLER_ERR_INVALID;
-  if (flags & ~ROLLER_FLAG_ACCUMULATE) return ROLLER_ERR_INVALID;
+  if (tile->layout != 0 && tile->layout != 2) return ROLLER_ERR_INVALID;
+  if (b_transposed && tile->layout != 0) return ROLLER_ERR_UNSUPPORTED;
+  const int layout = b_transposed ? 1 : tile->layout;
   const KernelVariant* kv =
-      find_variant(tile->block_m, tile->block_n, tile->rstep, tile->cta_group, mode);
+      find_variant(tile->block_m, tile->block_n, tile->rstep, tile->cta_group, mode, layout);
   if (!kv) return ROLLER_ERR_UNSUPPORTED;
 
   int dev = 0;
@@ -198,8 +221,15 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
   p->lda = lda; p->ldb = ldb; p->ldc = ldc;
   p->mode = mode;
   p->flags = flags;
-  p->tiles_m = (M + kv->block_m - 1) / kv->block_m;
-  p->tiles_n = (N + kv->block_n - 1) / kv->block_n;
+  p->layout = layout;
+  if (layout == 2) {
+    // the kernel works on C^T: its tile rows (128) run along N, its tile columns along M
+    p->tiles_m = (N + kv->block_n - 1) / kv->block_n;
+    p->tiles_n = (M + kv->block_m - 1) / kv->block_m;
+  } else {
+    p->tiles_m = (M + kv->block_m - 1) / kv->block_m;
+    p->tiles_n = (N + kv->block_n - 1) / kv->block_n;
+  }
   p->max_workers = p->sm_count / kv->cta_group;
   p->sk_mode = -1;
   p->epoch = 0;
@@ -207,6 +237,9 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
   // dominated by the 10-bit input mantissa, so one chunk spans the whole reduction.
   const int num_kb = (K + kv->rstep - 1) / kv->rstep;
   p->chunk_kb = (mode == ROLLER_MODE_3XTF32) ? 4 : num_kb;
+  // A skinny problem streams B once and is HBM-bound: it needs every SM pulling data, which
+  // only a split along K provides, so 1xTF32 gets chunks too (512 k).
+  if (layout == 2 && mode == ROLLER_MODE_1XTF32 && num_kb > 16) p->chunk_kb = 16;
   p->stage_a = (lda % 4) != 0;
   p->stage_b = (ldb % 4) != 0;
 
@@ -239,8 +272,8 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
     e = cudaMalloc(&p->ws_a, sizeof(float) * p->ws_lda * M);
   }
   if (e == cudaSuccess && p->stage_b) {
-    p->ws_ldb = round_up4(N);
-    e = cudaMalloc(&p->ws_b, sizeof(float) * p->ws_ldb * K);
+    p->ws_ldb = round_up4(b_transposed ? K : N);
+    e = cudaMalloc(&p->ws_b, sizeof(float) * p->ws_ldb * (b_transposed ? N : K));
   }
   if (e == cudaSuccess) e = cudaEventCreate(&p->ev0);
   if (e == cudaSuccess) e = cudaEventCreate(&p->ev1);
@@ -278,22 +311,34 @@ int roller_b200_gemm_run(roller_plan* p, const float* A, const float* B, float* 
     return ROLLER_ERR_INVALID;
   }
   if (p->stage_b) {
-    pad_rows_kernel<<<p->sm_count * 8, 256, 0, st>>>(B, p->ldb, p->ws_b, p->ws_ldb, p->K, p->N);
+    if (p->layout == 1)
+      pad_rows_kernel<<<p->sm_count * 8, 256, 0, st>>>(B, p->ldb, p->ws_b, p->ws_ldb, p->N, p->K);
+    else
+      pad_rows_kernel<<<p->sm_count * 8, 256, 0, st>>>(B, p->ldb, p->ws_b, p->ws_ldb, p->K, p->N);
     b_src = p->ws_b;
     ldb = p->ws_ldb;
   } else if (reinterpret_cast<uintptr_t>(B) & 15) {
     return ROLLER_ERR_INVALID;
   }
 
-  if (a_src != p->map_a_ptr) {
-    int rc = encode_matrix(&p->tmA, a_src, p->M, p->K, lda, 32, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+  // Which matrix feeds which MMA operand depends on the layout (see the kernel header).
+  if (a_src != p->map_a_ptr || b_src != p->map_b_ptr) {
+    int rc;
+    const int bnl = (p->layout == 2 ? kv->block_m : kv->block_n) / kv->cta_group;
+    if (p->layout == 2) {
+      rc = encode_matrix(&p->tmA, b_src, p->K, p->N, ldb, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+      if (rc == ROLLER_OK)
+        rc = encode_matrix(&p->tmB, a_src, p->M, p->K, lda, 32, bnl, CU_TENSOR_MAP_SWIZZLE_128B);
+    } else {
+      rc = encode_matrix(&p->tmA, a_src, p->M, p->K, lda, 32, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+      if (rc == ROLLER_OK && p->layout == 1)
+        rc = encode_matrix(&p->tmB, b_src, p->N, p->K, ldb, 32, bnl, CU_TENSOR_MAP_SWIZZLE_128B);
+      else if (rc == ROLLER_OK)
+        rc = encode_matrix(&p->tmB, b_src, p->K, p->N, ldb, 32, 32,
+                           CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+    }
     if (rc != ROLLER_OK) return rc;
     p->map_a_ptr = a_src;
-  }
-  if (b_src != p->map_b_ptr) {
-    int rc = encode_matrix(&p->tmB, b_src, p->K, p->N, ldb, 32, 32,
-                           CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
-    if (rc != ROLLER_OK) return rc;
     p->map_b_ptr = b_src;
   }
 
@@ -301,7 +346,9 @@ int roller_b200_gemm_run(roller_plan* p, const float* A, const float* B, float* 
   args.tmA = p->tmA;
   args.tmB = p->tmB;
   args.C = C;
-  args.M = p->M; args.N = p->N; args.K = p->K;
+  args.M = (p->layout == 2) ? p->N : p->M;
+  args.N = (p->layout == 2) ? p->M : p->N;
+  args.K = p->K;
   args.ldc = p->ldc;
   args.tiles_m = p->tiles_m;
   args.tiles_n = p->tiles_n;
@@ -339,11 +386,13 @@ int roller_b200_gemm_time(roller_plan* p, const float* A, const float* B, float*
   return ROLLER_OK;
 }
 
-int roller_b200_gemm_host(roller_plan* p, const float* hA, const float* hB, float* hC, void* stream) {
+int roller_b200_gemm_host_async(roller_plan* p, const float* hA, const float* hB, float* hC,
+                                void* stream) {
   if (!p || !hA || !hB || !hC) return ROLLER_ERR_INVALID;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t a_bytes = sizeof(float) * static_cast<size_t>(p->lda) * p->M;
-  const size_t b_bytes = sizeof(float) * static_cast<size_t>(p->ldb) * p->K;
+  const size_t b_bytes =
+      sizeof(float) * static_cast<size_t>(p->ldb) * (p->layout == 1 ? p->N : p->K);
   const size_t c_bytes = sizeof(float) * static_cast<size_t>(p->ldc) * p->M;
   if (!p->hd_a) {
     cudaError_t e = cudaMalloc(&p->hd_a, a_bytes);
@@ -363,7 +412,13 @@ int roller_b200_gemm_host(roller_plan* p, const float* hA, const float* hB, floa
   int rc = roller_b200_gemm_run(p, p->hd_a, p->hd_b, p->hd_c, stream);
   if (rc != ROLLER_OK) return rc;
   RB_CUDA(cudaMemcpyAsync(hC, p->hd_c, c_bytes, cudaMemcpyDeviceToHost, st));
-  RB_CUDA(cudaStreamSynchronize(st));
+  return ROLLER_OK;
+}
+
+int roller_b200_gemm_host(roller_plan* p, const float* hA, const float* hB, float* hC, void* stream) {
+  int rc = roller_b200_gemm_host_async(p, hA, hB, hC, stream);
+  if (rc != ROLLER_OK) return rc;
+  RB_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
   return ROLLER_OK;
 }
 
@@ -474,7 +529,9 @@ static int plan_configure(roller_plan* p) {
     const long long full = tiles / workers;
     const long long dp_time = (full + 1) * cpt;
     const long long sk_time = full * cpt + (r * cpt + workers - 1) / workers;
-    if (p->sk_mode == 1 || (full >= 1 && (dp_time - sk_time) * 100 >= 3 * dp_time))
+    // (the skinny layout is HBM-bound: it always splits, to put every SM to work on the stream)
+    if (p->sk_mode == 1 || p->layout == 2 ||
+        (full >= 1 && (dp_time - sk_time) * 100 >= 3 * dp_time))
       sk_tiles = static_cast<int>(r);
   }
   if (!p->grid_forced) {
@@ -491,7 +548,8 @@ static int plan_configure(roller_plan* p) {
     p->sk_ws = nullptr;
     p->sk_flags = nullptr;
     p->sk_slots = 0;
-    const size_t slot_bytes = sizeof(float) * 128 * static_cast<size_t>(kv->block_n);
+    const size_t slot_bytes =
+        sizeof(float) * 128 * static_cast<size_t>(p->layout == 2 ? kv->block_m : kv->block_n);
     const int slots = p->max_workers * kv->cta_group;
     cudaError_t e = cudaMalloc(&p->sk_ws, slot_bytes * slots);
     if (e == cudaSuccess) e = cudaMalloc(&p->sk_flags, sizeof(uint32_t) * slots);

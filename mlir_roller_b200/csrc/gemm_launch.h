@@ -33,6 +33,7 @@ struct KernelVariant {
   int rstep;      // k per stage
   int cta_group;  // 1 or 2
   int mode;       // 1 or 3
+  int layout;     // 0 = A[M,K], B[K,N]; 1 = B given as Bt[N,K]; 2 = skinny (roles swapped)
   int stages;
   int smem_bytes;
   int tmem_cols;
@@ -44,6 +45,7 @@ struct KernelVariant {
 int variant_count();
 const KernelVariant& variant_at(int idx);
 // Returns nullptr when no kernel was compiled for the combination.
-const KernelVariant* find_variant(int block_m, int block_n, int rstep, int cta_group, int mode);
+const KernelVariant* find_variant(int block_m, int block_n, int rstep, int cta_group, int mode,
+                                  int layout);
 
 }  // namespace rb200

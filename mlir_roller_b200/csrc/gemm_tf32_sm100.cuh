@@ -28,6 +28,17 @@
 // With a CTA pair in MODE 1 both CTAs' TMA loads report straight to the leader's barrier.
 // Ragged M/N/K need no special main loop: TMA zero-fills out-of-range elements.
 //
+// Operand layouts (template parameter LAYOUT). Each MMA operand tile is either "K-major" (its
+// rows are contiguous along k in global memory: one TMA box of ROWS x 32, 128-byte swizzle) or
+// "MN-major" (contiguous along m or n: boxes of 32 x 32, 128-byte swizzle on 32-byte chunks).
+//   0  A[M,K] row-major (K-major), B[K,N] row-major (MN-major): the reference's layout.
+//   1  A as above, B given transposed as Bt[N,K] row-major (K-major).
+//   2  "skinny": for a C with few rows the roles are swapped -- the tensor core computes
+//      C^T = B^T A^T, so the 128-row side of the MMA runs along N, the narrow side (32 or 64)
+//      along M, nothing but real data is staged, and the epilogue writes C transposed (which
+//      makes its stores coalesced). The kernel then sees M' = N, N' = M, A' = B (MN-major),
+//      B' = A (K-major).
+//
 // Work distribution. Tiles are handed to the persistent workers (CTAs or CTA pairs) round-robin.
 // When the tile count does not divide by the worker count, the last, partly filled wave would
 // leave SMs idle, so the first `sk_tiles` tiles are instead cut along K into chunk-sized units
@@ -39,24 +50,70 @@
 // like every other wait in the kernel.
 #pragma once
 
+#include <type_traits>
+
 #include "gemm_launch.h"
 #include "ptx_sm100.cuh"
 
 namespace rb200 {
 
-template <int BN_, int MODE_, int CG_>
+// One operand tile of ROWS (m or n) x 32 (k) whose global rows run along k.
+template <int ROWS>
+struct OperandK {
+  static constexpr int BYTES = ROWS * 128;
+  static constexpr uint32_t MAJOR = 0;   // instruction-descriptor major bit: K
+  static constexpr uint64_t KK_STEP = 2; // one MMA (8 k) further: 32 bytes along a row, >> 4
+  template <bool PAIR>
+  static __device__ __forceinline__ void load(uint32_t dst, const CUtensorMap* tm, uint32_t bar,
+                                              int row0, int k0) {
+    if constexpr (PAIR) tma_load_2d_pair(dst, tm, bar, k0, row0);
+    else tma_load_2d(dst, tm, bar, k0, row0);
+  }
+  // rows of 128 B, 8-row swizzle atoms 1024 B apart
+  static __device__ __forceinline__ uint64_t desc(uint32_t addr) {
+    return make_smem_desc(addr, 16, 1024, kLayoutSw128);
+  }
+};
+
+// One operand tile of ROWS (m or n) x 32 (k) whose global rows run along m/n.
+template <int ROWS>
+struct OperandMN {
+  static constexpr int BOXES = ROWS / 32;
+  static constexpr int BOX_BYTES = 32 * 128;
+  static constexpr int BYTES = BOXES * BOX_BYTES;
+  static constexpr uint32_t MAJOR = 1;    // MN
+  static constexpr uint64_t KK_STEP = 64; // one MMA (8 k) further: 8 rows of a box = 1024 B, >> 4
+  template <bool PAIR>
+  static __device__ __forceinline__ void load(uint32_t dst, const CUtensorMap* tm, uint32_t bar,
+                                              int row0, int k0) {
+#pragma unroll
+    for (int j = 0; j < BOXES; ++j) {
+      if constexpr (PAIR) tma_load_2d_pair(dst + j * BOX_BYTES, tm, bar, row0 + j * 32, k0);
+      else tma_load_2d(dst + j * BOX_BYTES, tm, bar, row0 + j * 32, k0);
+    }
+  }
+  // rows (one k each) of 128 B = 32 m/n; 4-row swizzle atoms 512 B apart along k, the next 32
+  // m/n one whole box further
+  static __device__ __forceinline__ uint64_t desc(uint32_t addr) {
+    return make_smem_desc(addr, BOX_BYTES, 512, kLayoutSw128Base32);
+  }
+};
+
+template <int BN_, int MODE_, int CG_, int LAYOUT_ = 0>
 struct GemmCfg {
   static constexpr int BN = BN_;      // tile columns (of the CTA pair when CG == 2)
   static constexpr int MODE = MODE_;  // 1 or 3 tensor-core products per fp32 product
   static constexpr int CG = CG_;      // CTAs cooperating on one tile (tcgen05 cta_group)
+  static constexpr int LAYOUT = LAYOUT_;
+  static constexpr bool TRANSPOSE_C = (LAYOUT == 2);
   static constexpr int BM = 128;      // tile rows held by one CTA
   static constexpr int BK = 32;       // reduce step: 32 fp32 = one 128-byte swizzle row
   static constexpr int BNL = BN / CG; // B columns staged by one CTA
-  static constexpr int A_BYTES = BM * BK * 4;
-  static constexpr int B_BOX_BYTES = 32 * BK * 4;
-  static constexpr int B_BOXES = BNL / 32;
-  static constexpr int B_BYTES = B_BOXES * B_BOX_BYTES;
-  static constexpr int RAW_BYTES = A_BYTES + B_BYTES;
+  using AOp = typename std::conditional<LAYOUT == 2, OperandMN<BM>, OperandK<BM>>::type;
+  using BOp = typename std::conditional<LAYOUT == 0, OperandMN<BNL>, OperandK<BNL>>::type;
+  static constexpr int A_BYTES = AOp::BYTES;
+  static constexpr int B_BYTES = BOp::BYTES;
+  static constexpr int RAW_BYTES = (A_BYTES + B_BYTES + 1023) / 1024 * 1024;
   static constexpr int STAGE_BYTES = (MODE == 3 ? 2 : 1) * RAW_BYTES;
   static constexpr int CTRL_BYTES = 256;
   static constexpr int SMEM_LIMIT = 232448;  // 227 KiB opt-in maximum per CTA
@@ -81,8 +138,11 @@ struct GemmCfg {
   static constexpr int REGS_CTRL = 64, REGS_XFORM = 80, REGS_EPI = 184;
 
   static_assert(BN % (32 * CG) == 0, "each CTA stages whole 32-column boxes of B");
-  static_assert(EPI_COLS % 32 == 0, "epilogue threads read whole 32-column slabs");
-  static_assert(TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512, "power of two");
+  static_assert(EPI_COLS % 16 == 0, "epilogue threads read whole 16-column slabs");
+  static_assert(TRANSPOSE_C || EPI_COLS % 32 == 0, "row-major C is stored in 32-column pieces");
+  static_assert(TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512,
+                "power of two");
+  static_assert(LAYOUT != 2 || CG == 1, "the skinny layout runs on single CTAs");
   static_assert(STAGES >= 2, "need at least a double buffer");
   static_assert(RAW_BYTES % 1024 == 0, "swizzle atoms must stay 1024-byte aligned");
   static_assert(4 * (REGS_CTRL + REGS_XFORM + 2 * REGS_EPI) * 32 <= 65536, "register file");
@@ -258,18 +318,14 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t b_dst = a_dst + Cfg::A_BYTES;
           if constexpr (CG == 2 && !Cfg::HAS_XFORM) {
             // The leader's barrier counts the bytes of both CTAs; only the leader arms it.
-            if (is_leader) mbar_expect_tx(full_bar(s), 2 * Cfg::RAW_BYTES);
+            if (is_leader) mbar_expect_tx(full_bar(s), 2 * (Cfg::A_BYTES + Cfg::B_BYTES));
             const uint32_t bar = map_to_cta(full_bar(s), 0);
-            tma_load_2d_pair(a_dst, &tmA, bar, kb * BK, m0);
-#pragma unroll
-            for (int j = 0; j < Cfg::B_BOXES; ++j)
-              tma_load_2d_pair(b_dst + j * Cfg::B_BOX_BYTES, &tmB, bar, n0 + j * 32, kb * BK);
+            Cfg::AOp::template load<true>(a_dst, &tmA, bar, m0, kb * BK);
+            Cfg::BOp::template load<true>(b_dst, &tmB, bar, n0, kb * BK);
           } else {
-            mbar_expect_tx(full_bar(s), Cfg::RAW_BYTES);
-            tma_load_2d(a_dst, &tmA, full_bar(s), kb * BK, m0);
-#pragma unroll
-            for (int j = 0; j < Cfg::B_BOXES; ++j)
-              tma_load_2d(b_dst + j * Cfg::B_BOX_BYTES, &tmB, full_bar(s), n0 + j * 32, kb * BK);
+            mbar_expect_tx(full_bar(s), Cfg::A_BYTES + Cfg::B_BYTES);
+            Cfg::AOp::template load<false>(a_dst, &tmA, full_bar(s), m0, kb * BK);
+            Cfg::BOp::template load<false>(b_dst, &tmB, full_bar(s), n0, kb * BK);
           }
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
@@ -281,7 +337,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     } else if (warp == 1 && lane == 0 && is_leader) {
       // ---------------------------------------------------------- MMA issuer
-      constexpr uint32_t idesc = make_idesc_tf32(Cfg::MMA_M, BN);
+      constexpr uint32_t idesc =
+          make_idesc_tf32(Cfg::MMA_M, BN, Cfg::AOp::MAJOR, Cfg::BOp::MAJOR);
+      constexpr uint64_t a_step = Cfg::AOp::KK_STEP, b_step = Cfg::BOp::KK_STEP;
       int s = 0;
       uint32_t ph = 0;
       int acc = 0;
@@ -301,36 +359,27 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (!mbar_wait(wait_bar, ph, status, kDevTimeoutReady)) { ok = false; break; }
             tcgen05_fence_after_sync();
             const uint32_t stage = smem_base + s * Cfg::STAGE_BYTES;
-            // A: rows of 128 B, 8-row swizzle atoms 1024 B apart.
-            const uint64_t a_raw = make_smem_desc(stage, 16, 1024, kLayoutSw128);
-            // B: rows (one k each) of 128 B = 32 columns; 4-row swizzle atoms 512 B apart along
-            // K, the next 32 columns one whole box further.
-            const uint64_t b_raw =
-                make_smem_desc(stage + Cfg::A_BYTES, Cfg::B_BOX_BYTES, 512, kLayoutSw128Base32);
-            // One MMA consumes 8 k: 32 bytes along an A row, 8 rows (1024 bytes) of a B box.
+            const uint64_t a_raw = Cfg::AOp::desc(stage);
+            const uint64_t b_raw = Cfg::BOp::desc(stage + Cfg::A_BYTES);
+            // One MMA consumes 8 k of both operand tiles.
             if constexpr (Cfg::MODE == 3) {
-              const uint64_t a_sml = make_smem_desc(stage + Cfg::RAW_BYTES, 16, 1024, kLayoutSw128);
-              const uint64_t b_sml = make_smem_desc(stage + Cfg::RAW_BYTES + Cfg::A_BYTES,
-                                                    Cfg::B_BOX_BYTES, 512, kLayoutSw128Base32);
+              const uint64_t a_sml = Cfg::AOp::desc(stage + Cfg::RAW_BYTES);
+              const uint64_t b_sml = Cfg::BOp::desc(stage + Cfg::RAW_BYTES + Cfg::A_BYTES);
               // Correction terms first: they are 2^-11 of the main term, so adding them while
               // the accumulator is still small costs the least rounding.
 #pragma unroll
               for (int kk = 0; kk < BK / 8; ++kk) {
-                const uint64_t a_off = static_cast<uint64_t>(kk * 2);
-                const uint64_t b_off = static_cast<uint64_t>(kk * 64);
-                umma_tf32<CG>(d_tmem, a_sml + a_off, b_raw + b_off, idesc,
+                umma_tf32<CG>(d_tmem, a_sml + kk * a_step, b_raw + kk * b_step, idesc,
                               (kb != kb0 || kk != 0) ? 1u : 0u);
-                umma_tf32<CG>(d_tmem, a_raw + a_off, b_sml + b_off, idesc, 1u);
+                umma_tf32<CG>(d_tmem, a_raw + kk * a_step, b_sml + kk * b_step, idesc, 1u);
               }
 #pragma unroll
               for (int kk = 0; kk < BK / 8; ++kk)
-                umma_tf32<CG>(d_tmem, a_raw + static_cast<uint64_t>(kk * 2),
-                              b_raw + static_cast<uint64_t>(kk * 64), idesc, 1u);
+                umma_tf32<CG>(d_tmem, a_raw + kk * a_step, b_raw + kk * b_step, idesc, 1u);
             } else {
 #pragma unroll
               for (int kk = 0; kk < BK / 8; ++kk)
-                umma_tf32<CG>(d_tmem, a_raw + static_cast<uint64_t>(kk * 2),
-                              b_raw + static_cast<uint64_t>(kk * 64), idesc,
+                umma_tf32<CG>(d_tmem, a_raw + kk * a_step, b_raw + kk * b_step, idesc,
                               (kb != kb0 || kk != 0) ? 1u : 0u);
             }
             umma_commit<CG>(empty_bar(s));
@@ -434,7 +483,22 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         if (!ok) break;
       }
-      if (row < M) {
+      if constexpr (Cfg::TRANSPOSE_C) {
+        // The kernel computed C^T: element (row, col) of its tile is C[col][row], so for one
+        // register the 32 lanes of a warp write 32 consecutive floats of a row of C.
+        if (row < M) {
+#pragma unroll
+          for (int j = 0; j < COLS; ++j) {
+            const int col = n0 + j;
+            if (col < N) {
+              float* dst = C + static_cast<size_t>(col) * static_cast<size_t>(ldc) + row;
+              float o = sum[j];
+              if (accumulate) o += *dst;
+              *dst = o;
+            }
+          }
+        }
+      } else if (row < M) {
         float* crow = C + static_cast<size_t>(row) * static_cast<size_t>(ldc);
 #pragma unroll
         for (int c = 0; c < COLS / 32; ++c) {

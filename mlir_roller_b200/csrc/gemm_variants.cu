@@ -25,12 +25,14 @@ static cudaError_t launch_variant(const GemmArgs& a, int grid, cudaStream_t stre
                             a.sk_flags, a.epoch);
 }
 
-template <int BN, int MODE, int CG>
+template <int BN, int MODE, int CG, int LAYOUT = 0>
 static KernelVariant make_variant() {
-  using Cfg = GemmCfg<BN, MODE, CG>;
+  using Cfg = GemmCfg<BN, MODE, CG, LAYOUT>;
   KernelVariant v;
-  v.block_m = Cfg::TILE_M;
-  v.block_n = BN;
+  // In the skinny layout the kernel's 128-row side runs along N of the caller's problem.
+  v.block_m = (LAYOUT == 2) ? BN : Cfg::TILE_M;
+  v.block_n = (LAYOUT == 2) ? Cfg::TILE_M : BN;
+  v.layout = LAYOUT;
   v.rstep = Cfg::BK;
   v.cta_group = CG;
   v.mode = MODE;
@@ -51,6 +53,13 @@ static const KernelVariant* table(int* n) {
       make_variant<256, 1, 1>(), make_variant<256, 3, 1>(),
       make_variant<128, 1, 1>(), make_variant<128, 3, 1>(),
       make_variant<64, 1, 1>(),  make_variant<64, 3, 1>(),
+      // B given transposed (Bt[N,K]): both operands K-major
+      make_variant<256, 1, 2, 1>(), make_variant<256, 3, 2, 1>(),
+      make_variant<128, 1, 1, 1>(), make_variant<128, 3, 1, 1>(),
+      make_variant<64, 1, 1, 1>(),  make_variant<64, 3, 1, 1>(),
+      // skinny C (few rows): roles swapped, tile = 64 or 32 rows of C x 128 columns
+      make_variant<64, 1, 1, 2>(),  make_variant<64, 3, 1, 2>(),
+      make_variant<32, 1, 1, 2>(),  make_variant<32, 3, 1, 2>(),
   };
   *n = static_cast<int>(sizeof(kTable) / sizeof(kTable[0]));
   return kTable;
@@ -67,12 +76,13 @@ const KernelVariant& variant_at(int idx) {
   return table(&n)[idx];
 }
 
-const KernelVariant* find_variant(int block_m, int block_n, int rstep, int cta_group, int mode) {
+const KernelVariant* find_variant(int block_m, int block_n, int rstep, int cta_group, int mode,
+                                  int layout) {
   int n;
   const KernelVariant* t = table(&n);
   for (int i = 0; i < n; ++i) {
     if (t[i].block_m == block_m && t[i].block_n == block_n && t[i].rstep == rstep &&
-        t[i].cta_group == cta_group && t[i].mode == mode)
+        t[i].cta_group == cta_group && t[i].mode == mode && t[i].layout == layout)
       return &t[i];
   }
   return nullptr;

@@ -126,7 +126,8 @@ extern "C" int roller_b200_gemm_static_scratch(const roller_ktile* tile, int mod
   if (M <= 0 || N <= 0 || K <= 0 || lda < K || ldb < N || ldc < N) return ROLLER_ERR_INVALID;
   if (mode != ROLLER_MODE_1XTF32 && mode != ROLLER_MODE_3XTF32) return ROLLER_ERR_INVALID;
   const KernelVariant* kv =
-      find_variant(tile->block_m, tile->block_n, tile->rstep, tile->cta_group, mode);
+      find_variant(tile->block_m, tile->block_n, tile->rstep, tile->cta_group, mode, 0);
+  if (tile->layout != 0) return ROLLER_ERR_UNSUPPORTED;
   if (!kv) return ROLLER_ERR_UNSUPPORTED;
 
   DeviceSetup* dev = nullptr;

@@ -230,13 +230,13 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_b
 }
 
 // Instruction descriptor for kind::tf32 with fp32 accumulation.
-// A is K-major (row-major A), B is MN-major (row-major B, i.e. N contiguous).
-__host__ __device__ constexpr uint32_t make_idesc_tf32(int mma_m, int mma_n) {
+// a_major / b_major: 0 = the operand tile is contiguous along k, 1 = along m (A) or n (B).
+__host__ __device__ constexpr uint32_t make_idesc_tf32(int mma_m, int mma_n, uint32_t a_major,
+                                                       uint32_t b_major) {
   return (1u << 4)      // D format: f32
          | (2u << 7)    // A format: tf32
          | (2u << 10)   // B format: tf32
-         | (0u << 15)   // A major: K
-         | (1u << 16)   // B major: MN
+         | (a_major << 15) | (b_major << 16)
          | (static_cast<uint32_t>(mma_n >> 3) << 17) | (static_cast<uint32_t>(mma_m >> 4) << 24);
 }
 

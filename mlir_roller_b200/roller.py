@@ -70,7 +70,7 @@ def kernel_tile_for(hint: TileDict) -> _lib.KTile:
     when the hint names one. Raises RollerError(UNSUPPORTED) when there is none."""
     bm, bn = hint.block_tile[0], hint.block_tile[1]
     cta_group = getattr(hint, "cta_group", None)
-    return _lib.find_tile(bm, bn, cta_group)
+    return _lib.find_tile(bm, bn, cta_group, getattr(hint, "layout", 0) or 0)
 
 
 class Compiler:
@@ -83,7 +83,7 @@ class Compiler:
 
     def __init__(self, config: MatmulConfig, hint: TileDict, pipeline_depth: int = 2,
                  dump_path: Optional[Path] = None, mode: Optional[int] = None,
-                 accumulate: bool = False, stream_k: int = -1):
+                 accumulate: bool = False, stream_k: int = -1, b_transposed: bool = False):
         self.config = config
         self.hint = hint
         self.pipeline_depth = pipeline_depth
@@ -91,6 +91,7 @@ class Compiler:
         self.mode = mode if mode is not None else (getattr(hint, "mode", None) or MODE_3XTF32)
         self.accumulate = accumulate
         self.stream_k = stream_k  # -1 automatic, 0 off, 1 whenever tiles are left over
+        self.b_transposed = b_transposed  # B is handed over as Bt[N,K] row-major
 
     def compile(self) -> CompiledGemm:
         _torch()
@@ -98,7 +99,8 @@ class Compiler:
             raise _lib.RollerError(_lib.ERR_UNSUPPORTED, "only fp32 (el_bits=32) kernels exist")
         tile = kernel_tile_for(self.hint)
         plan = _lib.GemmPlan(tile, self.config.M, self.config.N, self.config.K, mode=self.mode,
-                             flags=_lib.FLAG_ACCUMULATE if self.accumulate else 0)
+                             flags=(_lib.FLAG_ACCUMULATE if self.accumulate else 0)
+                             | (_lib.FLAG_B_TRANSPOSED if self.b_transposed else 0))
         if self.stream_k != -1:
             plan.set_stream_k(self.stream_k)
         return CompiledGemm(plan, self.hint)

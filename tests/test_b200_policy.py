@@ -8,15 +8,18 @@ from mlir_roller_b200 import analyze, arch
 from mlir_roller_b200.analyze import MODE_1XTF32, MODE_3XTF32, MatmulConfig, get_roller_hints
 
 TILES = {(t[0], t[1], t[2]) for t in arch.B200_KERNEL_TILES}
+SKINNY = {(t[0], t[1]) for t in arch.B200_KERNEL_TILES if t[5] == 2}
 
 
 def check_hint(h, M, N, K, mode):
     dev = arch.B200()
     assert (h.block_tile[0], h.block_tile[1], h.cta_group) in TILES
     assert h.rstep == 32 and h.mode == mode
-    assert h.tmem_cols == 2 * h.block_tile[1] <= dev.tmem_columns
+    skinny = h.layout == 2
+    assert skinny == ((h.block_tile[0], h.block_tile[1]) in SKINNY)
+    assert h.tmem_cols == 2 * h.block_tile[0 if skinny else 1] <= dev.tmem_columns
     assert h.smem_cost * h.stages + 2048 <= dev.smem_cap == 227 * 1024
-    assert h.block_tile[0] == 128 * h.cta_group
+    assert h.block_tile[1 if skinny else 0] == 128 * h.cta_group
     assert h.grid_size == -(-M // h.block_tile[0]) * -(-N // h.block_tile[1])
     assert h.num_wave == -(-h.grid_size // (dev.compute_max_core // h.cta_group))
     assert h.est_us > 0 and h.valid
@@ -66,11 +69,11 @@ def test_any_ragged_shape_gets_valid_hints(M, N, K, mode):
 def test_tile_table_matches_the_library():
     """The table the search ranks is exactly what libroller_b200 was compiled with."""
     from mlir_roller_b200 import _lib
-    lib_tiles = [(k.block_m, k.block_n, k.cta_group, k.stages_1x, k.stages_3x)
+    lib_tiles = [(k.block_m, k.block_n, k.cta_group, k.stages_1x, k.stages_3x, k.layout)
                  for k in _lib.kernel_tiles()]
     assert sorted(lib_tiles) == sorted(arch.B200_KERNEL_TILES)
     for k in _lib.kernel_tiles():
-        assert k.rstep == 32 and k.tmem_cols == 2 * k.block_n
+        assert k.rstep == 32 and k.tmem_cols == 2 * (k.block_m if k.layout == 2 else k.block_n)
         assert max(k.smem_1x, k.smem_3x) <= 227 * 1024
         assert isinstance(k, ctypes.Structure)
 

@@ -23,15 +23,21 @@ GOLDEN = np.load(Path(__file__).resolve().parent / "golden" / "gemm_golden.npz")
 
 
 def gpu_gemm(A, B, tile, mode, *, lda=None, ldb=None, ldc=None, flags=0, C0=None, chunk=None,
-             stream_k=None, info=None):
-    """Run one GEMM through roller_b200_gemm_create/run on numpy operands; returns C (numpy)."""
+             stream_k=None, info=None, b_transposed=False):
+    """Run one GEMM through roller_b200_gemm_create/run on numpy operands; returns C (numpy).
+    `tile` = (block_m, block_n, cta_group[, layout]). With `b_transposed` the device copy of B
+    is laid out as Bt[N,K] and the plan is told so."""
     M, K = A.shape
     N = B.shape[1]
     lda = K if lda is None else lda
-    ldb = N if ldb is None else ldb
+    ldb = (K if b_transposed else N) if ldb is None else ldb
     ldc = N if ldc is None else ldc
     dA = torch.zeros(M, lda, device="cuda"); dA[:, :K] = torch.from_numpy(A).cuda()
-    dB = torch.zeros(K, ldb, device="cuda"); dB[:, :N] = torch.from_numpy(B).cuda()
+    if b_transposed:
+        flags |= _lib.FLAG_B_TRANSPOSED
+        dB = torch.zeros(N, ldb, device="cuda"); dB[:, :K] = torch.from_numpy(np.ascontiguousarray(B.T)).cuda()
+    else:
+        dB = torch.zeros(K, ldb, device="cuda"); dB[:, :N] = torch.from_numpy(B).cuda()
     dC = torch.full((M, ldc), float("nan"), device="cuda")
     if C0 is not None:
         dC[:, :N] = torch.from_numpy(C0).cuda()
@@ -318,6 +324,59 @@ def test_stream_k_back_to_back_launches_reuse_the_scratch_area():
         assert torch.equal(o, outs[0])
     assert g.err_norm(outs[0].cpu().numpy(), g.matmul_fp64(A, B)) <= TIGHT_3X
     plan.destroy()
+
+
+SKINNY_TILES = [(64, 128, 1, 2), (32, 128, 1, 2)]
+
+
+@pytest.mark.parametrize("tile", SKINNY_TILES)
+@pytest.mark.parametrize("mode", [1, 3])
+def test_skinny_layout(tile, mode):
+    # few rows of C: the tensor core works on C^T; tails in all three extents, M above one tile
+    shapes = [(16, 1024, 512), (1, 300, 100), (64, 1000, 777), (100, 260, 90), (33, 129, 4100),
+              (16, 2048, 8192)]
+    for (M, N, K) in shapes:
+        A, B = g.make_inputs(M, N, K, "normal", seed=N)
+        C64 = g.matmul_fp64(A, B)
+        for sk in (0, None):
+            C = gpu_gemm(A, B, tile, mode, stream_k=sk)
+            assert C.shape == (M, N) and not np.isnan(C).any()
+            err = g.err_norm(C, C64)
+            assert err <= (TIGHT_3X if mode == 3 else TOL_1X), (tile, mode, (M, N, K), sk, err)
+
+
+def test_skinny_layout_options():
+    tile = (32, 128, 1, 2)
+    M, N, K = 24, 515, 333          # odd leading dimensions: both operands are staged
+    A, B = g.make_inputs(M, N, K, "uniform", seed=4)
+    C64 = g.matmul_fp64(A, B)
+    assert g.err_norm(gpu_gemm(A, B, tile, 3), C64) <= TIGHT_3X
+    assert g.err_norm(gpu_gemm(A, B, tile, 3, lda=K + 3, ldb=N + 1, ldc=N + 5), C64) <= TIGHT_3X
+    C0 = np.random.default_rng(1).uniform(-1, 1, (M, N)).astype(np.float32)
+    got = gpu_gemm(A, B, tile, 3, flags=_lib.FLAG_ACCUMULATE, C0=C0)
+    want = g.sgemm_ref_c(A, B, C=C0.copy())     # itself an fp32 result: compare to rounding
+    assert np.abs(got - want).max() <= 4e-6 * np.abs(want).max()
+    # same reduction order as the general tiles when every tile is reduced by one worker: bit
+    # for bit in 1xTF32; in 3xTF32 the two correction products are issued in the other order
+    assert np.array_equal(gpu_gemm(A, B, tile, 1, stream_k=0, chunk=128),
+                          gpu_gemm(A, B, (128, 64, 1), 1, stream_k=0, chunk=128))
+    wide = gpu_gemm(A, B, (128, 64, 1), 3, stream_k=0)
+    assert np.abs(gpu_gemm(A, B, tile, 3, stream_k=0) - wide).max() <= 2e-6 * np.abs(wide).max()
+
+
+@pytest.mark.parametrize("tile", [(256, 256, 2), (128, 128, 1), (128, 64, 1)])
+@pytest.mark.parametrize("mode", [1, 3])
+def test_b_given_transposed(tile, mode):
+    for (M, N, K) in [(300, 200, 100), (512, 384, 256), (1111, 777, 555)]:
+        A, B = g.make_inputs(M, N, K, "uniform", seed=K)
+        C64 = g.matmul_fp64(A, B)
+        C = gpu_gemm(A, B, tile, mode, b_transposed=True, stream_k=0)
+        err = g.err_norm(C, C64)
+        assert err <= (TIGHT_3X if mode == 3 else TOL_1X), (tile, mode, (M, N, K), err)
+        # identical arithmetic to the plain layout: only the staging of B differs
+        assert np.array_equal(C, gpu_gemm(A, B, tile, mode, stream_k=0))
+    with pytest.raises(_lib.RollerError):   # no transposed-B kernel for this tile
+        _lib.GemmPlan(_lib.find_tile(256, 128, 2), 64, 64, 64, flags=_lib.FLAG_B_TRANSPOSED)
 
 
 def test_linearity_in_scale():
