@@ -83,6 +83,10 @@ B200_KBLOCK_US = {
     (128, 256, 1): (0.515, 1.521),
     (128, 128, 1): (0.321, 0.927),
     (128, 64, 1): (0.278, 0.702),
+    # skinny tiles, keyed with their layout; measured at 16 x 16384 x 16384, where they stream B
+    # at 5.7 TB/s (1xTF32) / 3.6 TB/s (3xTF32)
+    (32, 128, 1, 2): (0.39, 0.63),
+    (64, 128, 1, 2): (0.40, 0.66),
 }
 
 

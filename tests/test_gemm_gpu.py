@@ -271,6 +271,9 @@ def test_config_ragged_and_skinny():
     assert _rows_check(4097, 2049, 8193, (256, 128, 2), 3, "normal", 0, TOL_3X) <= TOL_3X
     assert _rows_check(16, 8192, 8192, (128, 64, 1), 3, "normal", 0, TOL_3X) <= TOL_3X
     assert _rows_check(16, 8192, 8192, (128, 64, 1), 1, "normal", 0, TOL_1X) <= TOL_1X
+    # the tile the search picks for it: skinny layout, split along K over all SMs
+    assert _rows_check(16, 8192, 8192, (32, 128, 1, 2), 3, "normal", 0, TOL_3X) <= TOL_3X
+    assert _rows_check(16, 8192, 8192, (32, 128, 1, 2), 1, "normal", 0, TOL_1X) <= TOL_1X
 
 
 def test_row_shards_equal_the_whole():
