@@ -138,12 +138,6 @@ int roller_b200_gemm_set_chunk(roller_plan* plan, int k_elems);
  * at most one per tile). The reference derives its grid from the hint (src/roller.py:536). */
 int roller_b200_gemm_set_grid(roller_plan* plan, int ctas);
 
-/* Lets kernels launched on the current device address memory of `peer_device` (NVLink peer
- * access), which the fused multi-GPU output path needs: its epilogue stores C tiles straight
- * into another GPU's buffer. The reference is single-GPU (.env:5-6) and has no counterpart in
- * the reference for this call. Returns ROLLER_ERR_DEVICE when the two devices are not peers. */
-int roller_b200_enable_peer(int peer_device);
-
 /* Stream-K scheduling of the leftover tiles (those that do not fill a last wave of the persistent
  * grid): -1 = use it when it shortens the schedule by 3 % or more (default), 0 = never (every
  * tile is reduced by one worker; results are then bit-identical for every rTile and every

@@ -79,7 +79,6 @@ SIGNATURES = {
     "roller_b200_gemm_static_scratch": (C.c_int, [C.POINTER(KTile), C.c_int, C.c_int, C.c_int,
                                                   C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                                   C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
-    "roller_b200_enable_peer": (C.c_int, [C.c_int]),
     "roller_b200_last_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32)]),
     "roller_b200_gemm_destroy": (C.c_int, [C.c_void_p]),
     "roller_b200_strerror": (C.c_char_p, [C.c_int]),
@@ -128,11 +127,6 @@ def device_info(dev: int = 0) -> DevInfo:
     info = DevInfo()
     check(load().roller_b200_device_info(dev, C.byref(info)), "roller_b200_device_info")
     return info
-
-
-def enable_peer(peer_device: int) -> None:
-    """Allow kernels on the current device to address `peer_device`'s memory."""
-    check(load().roller_b200_enable_peer(peer_device), "roller_b200_enable_peer")
 
 
 def kernel_tiles() -> list[KTile]:

@@ -461,22 +461,6 @@ int roller_b200_gemm_set_stream_k(roller_plan* p, int mode) {
   return plan_configure(p);
 }
 
-int roller_b200_enable_peer(int peer_device) {
-  int dev = 0;
-  RB_CUDA(cudaGetDevice(&dev));
-  if (peer_device == dev) return ROLLER_OK;
-  int can = 0;
-  RB_CUDA(cudaDeviceCanAccessPeer(&can, dev, peer_device));
-  if (!can) return ROLLER_ERR_DEVICE;
-  cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
-  if (e == cudaErrorPeerAccessAlreadyEnabled) {
-    cudaGetLastError();
-    return ROLLER_OK;
-  }
-  if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceEnablePeerAccess");
-  return ROLLER_OK;
-}
-
 int roller_b200_last_status(roller_plan* p, uint32_t* device_status) {
   if (!p) return ROLLER_ERR_INVALID;
   uint32_t h = 0;

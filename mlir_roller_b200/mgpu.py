@@ -198,10 +198,7 @@ class ShardedGemm:
             self._root_view = C_full
         else:
             rebuild, args = payload[0]
-            self._root_view = rebuild(*args)   # mapping of the root's memory in this process
-            # the mapping belongs to the root's device; this rank's kernels run on another one
-            # and may only touch it once peer access between the two is switched on
-            _lib.enable_peer(self._root_view.device.index)
+            self._root_view = rebuild(*args)   # peer mapping of the root's memory
         self._root_plan = None
         if self.plan is not None:
             tile = roller.kernel_tile_for(self.hint)
