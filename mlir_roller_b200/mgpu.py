@@ -177,46 +177,5 @@ class ShardedGemm:
     def gather(self, C_block, root: int = 0, group=None, out=None):
         return gather_blocks(C_block, self.blocks, self.M, self.N, self.rank, root, group, out)
 
-    # ---- fused alternative to run() + gather(): the kernel's epilogue stores this rank's tiles
-    # straight into the root's C over NVLink peer memory, tile by tile as they finish, so the
-    # transfer overlaps the main loop of later tiles and no collective moves C afterwards.
-    def bind_root_output(self, C_full=None, root: int = 0, group=None):
-        """Share the root's M x N output with every rank (CUDA IPC through torch) and prepare a
-        plan that writes this rank's block into it. `C_full` is given on the root only. Call
-        once, outside any timed region; returns this rank's view of the root's buffer."""
-        import torch
-        import torch.distributed as dist
-        from torch.multiprocessing.reductions import reduce_tensor
-        from . import _lib, roller
-        payload = [None]
-        if self.rank == root:
-            if C_full is None or tuple(C_full.shape) != (self.M, self.N) or not C_full.is_contiguous():
-                raise ValueError("the root passes a contiguous M x N output tensor")
-            payload[0] = reduce_tensor(C_full)
-        dist.broadcast_object_list(payload, src=root, group=group)
-        if self.rank == root:
-            self._root_view = C_full
-        else:
-            rebuild, args = payload[0]
-            self._root_view = rebuild(*args)   # peer mapping of the root's memory
-        self._root_plan = None
-        if self.plan is not None:
-            tile = roller.kernel_tile_for(self.hint)
-            b = self.block
-            self._root_plan = _lib.GemmPlan(tile, b.rows, b.cols, self.K, lda=self.K, ldb=self.N,
-                                            ldc=self.N, mode=self.mode)
-        return self._root_view
-
-    def run_into_root(self, A_rows, B_full, stream=None) -> None:
-        """Enqueue the local GEMM with its output going directly to the root's C (see
-        `bind_root_output`). The root may read C after every rank's stream has finished, e.g.
-        behind a barrier."""
-        if self._root_plan is None:
-            return
-        b = self.block
-        elem = B_full.element_size()
-        c_ptr = self._root_view.data_ptr() + (b.row0 * self.N + b.col0) * elem
-        self._root_plan.run_ptr(A_rows.data_ptr(), B_full.data_ptr() + b.col0 * elem, c_ptr, stream)
-
     def flops(self) -> int:
         return 2 * self.block.rows * self.block.cols * self.K
