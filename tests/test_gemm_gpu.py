@@ -267,6 +267,15 @@ def test_config_m13_full_size():
     assert _rows_check(8192, 4096, 4096, (256, 256, 2), 3, "uniform", 13, TOL_3X) <= TOL_3X
 
 
+def test_config_16384_cubed_both_modes():
+    # the largest configuration (one GPU's worth of the 8-GPU case is 4096 x 8192 x 16384; the
+    # whole problem also fits one B200): sampled exact rows + full fp64 cross-check on the GPU
+    assert _rows_check(16384, 16384, 16384, (256, 256, 2), 3, "uniform", 0, TOL_3X) <= TOL_3X
+    torch.cuda.empty_cache()
+    assert _rows_check(16384, 16384, 16384, (256, 256, 2), 1, "uniform", 0, TOL_1X) <= TOL_1X
+    torch.cuda.empty_cache()
+
+
 def test_config_ragged_and_skinny():
     assert _rows_check(4097, 2049, 8193, (256, 128, 2), 3, "normal", 0, TOL_3X) <= TOL_3X
     assert _rows_check(16, 8192, 8192, (128, 64, 1), 3, "normal", 0, TOL_3X) <= TOL_3X
