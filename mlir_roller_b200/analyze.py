@@ -374,12 +374,16 @@ class BlackwellPolicy:
             l2_clk = raw / dev.l2_bytes_per_clk_sm
             kb_us = max(tensor_clk, smem_clk, l2_clk) / dev.sm_clock_mhz
         # Whole tiles go round-robin; leftover tiles are dealt out in k-chunks (stream-K) when
-        # whole tiles follow them and that shortens the schedule by 3 % or more -- the same rule
-        # the library applies (3xTF32 only: 1xTF32 reduces a tile in one chunk).
+        # that shortens the schedule by 3 % or more after charging the partial-tile exchange --
+        # the same rule the library applies (3xTF32 only: 1xTF32 reduces a tile in one chunk).
         full, left = divmod(td.grid_size, workers)
         waves = float(td.num_wave)
-        if mode == MODE_3XTF32 and left and full >= 1 and (1.0 - left / workers) >= 0.03 * (full + 1):
-            waves = full + left / workers
+        if mode == MODE_3XTF32 and left:
+            cpt = -(-num_kb // 4)                      # 128-deep chunks per tile
+            exchange = 1 if full >= 1 else 3           # partial-tile exchange, in chunks
+            split = full * cpt + -(-left * cpt // workers) + exchange
+            if cpt > 1 and (full + 1) * cpt - split >= 0.03 * (full + 1) * cpt:
+                waves = split / cpt
         if layout == 2 and left:
             waves = full + left / workers   # the skinny layout always splits along K
         # launch, pipeline fill, last drain and the C stores of the final tile

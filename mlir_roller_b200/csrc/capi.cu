@@ -511,10 +511,12 @@ const char* roller_b200_last_cuda_error(void) { return g_cuda_err; }
 // With T tiles on W workers the round-robin schedule takes ceil(T / W) tile-times. Dealing the
 // r = T mod W leftover tiles out in k-chunks instead takes floor(T / W) tile-times plus
 // ceil(r * chunks_per_tile / W) chunk-times, at the price of one partial-tile exchange per
-// worker. Measured on B200 this pays when whole tiles follow the split ones (4096^3: -11 %,
-// 2048x8192x8192: -15 %), and does not when there are fewer tiles than workers (2048^3: +6 %;
-// the idle SMs of the round-robin schedule leave the busy ones more of the power budget). So it
-// is used when T >= W and the schedule gets at least 3 % shorter.
+// worker. That exchange is hidden behind the whole tiles that follow (4096^3: -11 %,
+// 2048x8192x8192: -15 %) but exposed when there are fewer tiles than workers, where it costs
+// about as much as three 128-deep chunks (64 tiles on 74 CTA pairs: +6 % at K = 2048, -4 % at
+// K = 4096 and 8192, -5 % at K = 16384; 48 tiles at K = 8192: -22 %). So the split schedule is
+// charged one chunk (whole tiles follow) or three (they do not) and used when it is still at
+// least 3 % shorter.
 static int plan_configure(roller_plan* p) {
   const KernelVariant* kv = p->kv;
   const long long tiles = static_cast<long long>(p->tiles_m) * p->tiles_n;
@@ -528,10 +530,10 @@ static int plan_configure(roller_plan* p) {
   if (p->sk_mode != 0 && r != 0 && cpt > 1 && !(p->flags & ROLLER_FLAG_ACCUMULATE)) {
     const long long full = tiles / workers;
     const long long dp_time = (full + 1) * cpt;
-    const long long sk_time = full * cpt + (r * cpt + workers - 1) / workers;
+    const long long sk_time =
+        full * cpt + (r * cpt + workers - 1) / workers + (full >= 1 ? 1 : 3);
     // (the skinny layout is HBM-bound: it always splits, to put every SM to work on the stream)
-    if (p->sk_mode == 1 || p->layout == 2 ||
-        (full >= 1 && (dp_time - sk_time) * 100 >= 3 * dp_time))
+    if (p->sk_mode == 1 || p->layout == 2 || (dp_time - sk_time) * 100 >= 3 * dp_time)
       sk_tiles = static_cast<int>(r);
   }
   if (!p->grid_forced) {
