@@ -1,6 +1,7 @@
 """Generates tests/golden/search_golden.json by running the reference's own rTile search.
 
-Run in a container that has the reference checkout (default /root/reference):
+Run where a checkout of the reference is available (default: a directory named `reference`
+next to this repository):
 
     python tests/golden/gen_search_golden.py [/path/to/reference]
 
@@ -41,7 +42,8 @@ def hint_record(td) -> dict:
 
 
 def main() -> None:
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    ref = Path(sys.argv[1]) if len(sys.argv) > 1 else \
+        Path(__file__).resolve().parents[3] / "reference"
     stub = types.ModuleType("humanize")
     stub.naturalsize = lambda n, binary=False: str(n)
     sys.modules["humanize"] = stub

@@ -3,6 +3,7 @@
 Golden vectors: tests/golden/search_golden.json, recorded from the reference itself by
 tests/golden/gen_search_golden.py (README shapes M0-M13, shard shapes, ragged, skinny, primes,
 tiny shapes, other element widths, a modified device)."""
+import os
 import sys
 import types
 from pathlib import Path
@@ -12,7 +13,9 @@ import pytest
 from conftest import hint_record
 from mlir_roller_b200 import analyze, arch, utils
 
-REFERENCE_SRC = Path("/root/reference/src")
+# a checkout of the reference next to this repository (or named by MLIR_ROLLER_REFERENCE)
+REFERENCE_SRC = Path(os.environ.get("MLIR_ROLLER_REFERENCE",
+                                    Path(__file__).resolve().parents[2] / "reference")) / "src"
 
 
 def _cases(golden):
