@@ -5,8 +5,10 @@
 // instantiation exists per rTile the search may emit: block tile (128*CG) x BN, reduce step 32.
 //
 // Arithmetic: tcgen05.mma kind::tf32 with fp32 accumulation in TMEM.
-//   MODE 1 ("1xTF32"): one MMA per k-step on the raw fp32 words; the tensor core reads the top
-//          19 bits of each word (truncation, measured on B200).
+//   MODE 1 ("1xTF32"): one MMA per k-step. The tensor core reads only the top 19 bits of each
+//          32-bit word (truncation, measured on B200), so the host encodes the tensor maps of
+//          this mode with the TFLOAT32 data type: the TMA unit then rounds every element to the
+//          nearest TF32 value while copying it into shared memory.
 //   MODE 3 ("3xTF32"): each operand x is used as big(x) = the raw word (its low 13 bits are not
 //          read) and small(x) = x - trunc19(x), computed exactly in fp32 by the split warps and
 //          rounded to 19 bits; per k-step three MMAs small*big + big*small + big*big go into

@@ -64,14 +64,14 @@ EncodeTiledFn encode_fn() {
 }
 
 bool encode(CUtensorMap* tm, const float* base, long long rows, long long cols, long long ld,
-            int box_cols, int box_rows, CUtensorMapSwizzle swz) {
+            int box_cols, int box_rows, CUtensorMapSwizzle swz, bool round_to_tf32) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * sizeof(float)};
   cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
-  return fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box,
+  return fn(tm, round_to_tf32 ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box,
             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -171,8 +171,9 @@ extern "C" int roller_b200_gemm_static_scratch(const roller_ktile* tile, int mod
   }
 
   GemmArgs args;
-  if (!encode(&args.tmA, a_src, M, K, a_ld, 32, 128, CU_TENSOR_MAP_SWIZZLE_128B) ||
-      !encode(&args.tmB, b_src, K, N, b_ld, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))
+  const bool rnd = (mode == ROLLER_MODE_1XTF32);  // 1xTF32 operands are rounded by the TMA unit
+  if (!encode(&args.tmA, a_src, M, K, a_ld, 32, 128, CU_TENSOR_MAP_SWIZZLE_128B, rnd) ||
+      !encode(&args.tmB, b_src, K, N, b_ld, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, rnd))
     return ROLLER_ERR_CUDA;
   args.C = C;
   args.M = M; args.N = N; args.K = K;

@@ -98,9 +98,19 @@ def split_small(x: np.ndarray) -> np.ndarray:
     return bits.view(np.float32)
 
 
-def emulate_1xtf32(A: np.ndarray, B: np.ndarray) -> np.ndarray:
-    """1xTF32 with an ideal (fp64) accumulator: isolates the input-truncation error."""
-    return tf32_trunc(A).astype(np.float64) @ tf32_trunc(B).astype(np.float64)
+def tf32_round(x: np.ndarray) -> np.ndarray:
+    """fp32 rounded to the nearest TF32 value (ties away from zero): what the TMA unit delivers
+    for a tensor map of TFLOAT32 type, which is how the 1xTF32 kernels load their operands."""
+    bits = x.astype(np.float32).view(np.uint32)
+    return ((bits + np.uint32(0x1000)) & np.uint32(0xFFFFE000)).view(np.float32)
+
+
+def emulate_1xtf32(A: np.ndarray, B: np.ndarray, rounding: str = "nearest") -> np.ndarray:
+    """1xTF32 with an ideal (fp64) accumulator: isolates the error of the 10-bit-mantissa
+    inputs. "nearest" models the kernels (operands rounded on load), "trunc" what the tensor
+    core does with raw fp32 words."""
+    cut = tf32_round if rounding == "nearest" else tf32_trunc
+    return cut(A).astype(np.float64) @ cut(B).astype(np.float64)
 
 
 def emulate_3xtf32(A: np.ndarray, B: np.ndarray) -> np.ndarray:

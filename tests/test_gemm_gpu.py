@@ -2,7 +2,8 @@
 
 Tolerances (norm-wise error max|C - C64| / max|C64| against the fp64 product):
   3xTF32: <= 1e-5 (the stated bar); measured ~1e-6, so tests also hold it to 4e-6;
-  1xTF32: reported separately; <= 2e-3 (10-bit mantissa inputs, truncated).
+  1xTF32: reported separately; <= 2e-3 (10-bit mantissa inputs, rounded to nearest on load;
+          measured ~2.5e-4 on sign-mixed data).
 """
 import numpy as np
 import pytest
@@ -117,7 +118,8 @@ def test_error_band_matches_the_arithmetic_model(dist):
     C64 = g.matmul_fp64(A, B)
     e1 = g.err_norm(gpu_gemm(A, B, (128, 256, 1), 1), C64)
     m1 = g.err_norm(g.emulate_1xtf32(A, B), C64)
-    assert 0.3 * m1 <= e1 <= 3 * m1 + 1e-5, (dist, e1, m1)  # 1xTF32 = truncated inputs
+    assert 0.3 * m1 <= e1 <= 3 * m1 + 1e-5, (dist, e1, m1)  # 1xTF32 = inputs rounded to TF32
+    assert e1 < g.err_norm(g.emulate_1xtf32(A, B, rounding="trunc"), C64)
     e3 = g.err_norm(gpu_gemm(A, B, (128, 256, 1), 3), C64)
     assert e3 <= TIGHT_3X
 
