@@ -12,7 +12,9 @@ from the 126 MB L2. Times are CUDA-event times on the launching stream, max over
 With N > 1 (launched by torchrun, one rank per GPU) every rank runs the same sweep as its row
 shard of an N-times-taller GEMM (operands replicated, no data-path collective): weak scaling.
 The strong-scaling shapes of the sharded configurations (8192x4096x4096 row-sharded, and
-16384^3 on a 4x2 grid at N = 8) are timed as well and reported under "strong".
+16384^3 row-sharded and on a 4x2 grid at N = 8) are timed as well and reported under "strong":
+the kernels alone, with an NCCL gather of C, and with the exchange of C overlapped with the
+computation.
 
 `--impl reference` times the reference's CPU path for the same workload (numpy fp32 matmul on
 the host cores + the CPU restatement of its rTile search under oracle/), rank 0 only.
@@ -303,12 +305,34 @@ def e2e_sweep(torch, cases, steps):
 
 
 def strong_scaling(torch, dist, rank, world, steps, warmup, mode):
-    """Strong-scaling shapes of the sharded configurations; compute-only and with the gather of
-    C to rank 0. Returns a list of records (identical on all ranks)."""
+    """Strong-scaling shapes of the sharded configurations. Per job: the local kernels alone
+    ("compute"), followed by an NCCL gather of C to rank 0 ("with_gather"), and with the exchange
+    of C running underneath the computation over symmetric memory, to rank 0
+    ("overlapped_root") and to every rank ("overlapped_all"). Returns a list of records
+    (identical on all ranks); times are the max over ranks."""
     from mlir_roller_b200 import mgpu
     jobs = [("M13 8192x4096x4096 row-sharded", (8192, 4096, 4096), (world, 1), 13)]
     if world == 8:
+        jobs.append(("16384^3 row-sharded", (16384, 16384, 16384), (8, 1), 0))
         jobs.append(("16384^3 on a 4x2 grid", (16384, 16384, 16384), (4, 2), 0))
+
+    def timed(fn):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     out = []
     for name, (M, N, K), grid, seed in jobs:
         sg = mgpu.ShardedGemm(M, N, K, rank, world, grid=grid, mode=mode, measure=True)
@@ -320,30 +344,29 @@ def strong_scaling(torch, dist, rank, world, steps, warmup, mode):
         B_full = torch.rand(K, N, device="cuda", generator=g) * 2 - 1
         C_blk = torch.empty(b.rows, b.cols, device="cuda")
         C_full = torch.empty(M, N, device="cuda") if rank == 0 else None
-        for _ in range(warmup):
-            sg.run(A_rows, B_full, C_blk)
-        sg.gather(C_blk, out=C_full)
-        torch.cuda.synchronize()
         rec = {"name": name, "grid": list(grid), "tile": sg.hint.block_tile if sg.hint else None}
-        for label, with_gather in (("compute", False), ("with_gather", True)):
-            dist.barrier()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(steps):
-                sg.run(A_rows, B_full, C_blk)
-                if with_gather:
-                    sg.gather(C_blk, out=C_full)
-            e1.record()
-            torch.cuda.synchronize()
-            dist.barrier()
-            t = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
+
+        def put(label, ms):
             rec[label + "_ms"] = ms
             rec[label + "_tflops"] = 2.0 * M * N * K / ms / 1e9
+
+        put("compute", timed(lambda: sg.run(A_rows, B_full, C_blk)))
+        put("with_gather", timed(lambda: (sg.run(A_rows, B_full, C_blk),
+                                          sg.gather(C_blk, out=C_full))))
+        del C_full
+        for dest in ("root", "all"):
+            og = mgpu.OverlappedGemm(M, N, K, rank, world, grid=grid, mode=mode, dest=dest)
+            put("overlapped_" + dest, timed(lambda: (og.run(A_rows, B_full), og.finish())))
+            rec["bands"] = len(og.bands)
+            for p in og.plans:
+                p.check_status()
+            og.destroy()
+            del og
+            torch.cuda.empty_cache()
+        # lower bound of any exchange that ends with C on one rank: its ingress over NVLink
+        rec["gather_link_bound_ms"] = (world - 1) / world * M * N * 4 / 770e9 * 1e3
         out.append(rec)
-        del A_rows, B_full, C_blk, C_full, sg
+        del A_rows, B_full, C_blk, sg
         torch.cuda.empty_cache()
     return out
 

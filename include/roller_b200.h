@@ -123,6 +123,14 @@ int roller_b200_gemm_host(roller_plan* plan, const float* hA, const float* hB, f
 int roller_b200_gemm_host_async(roller_plan* plan, const float* hA, const float* hB, float* hC,
                                 void* stream);
 
+/* Copies a rows x cols block of fp32 between two device matrices (leading dimensions in
+ * elements) with the driver's copy engines, enqueued on `stream`; either side may be another
+ * GPU's memory mapped into this process. The multi-GPU driver uses it to push a finished band of
+ * C into the destination rank's matrix while the next band is still being computed. There is
+ * no counterpart in the reference, which runs on one device (.env:5-6). */
+int roller_b200_copy_block_async(float* dst, long long dst_ld, const float* src, long long src_ld,
+                                 long long rows, long long cols, void* stream);
+
 /* Launch geometry the plan chose (the reference derives grid/block from the hint,
  * src/roller.py:536-543). Any out pointer may be NULL. */
 int roller_b200_gemm_launch_info(const roller_plan* plan, int* grid, int* block, int* smem_bytes,

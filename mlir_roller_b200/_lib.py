@@ -67,6 +67,8 @@ SIGNATURES = {
                                           C.c_int, C.c_int, C.c_int, C.c_int,
                                           C.POINTER(C.c_void_p)]),
     "roller_b200_gemm_run": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "roller_b200_copy_block_async": (C.c_int, [C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong,
+                                               C.c_longlong, C.c_longlong, C.c_void_p]),
     "roller_b200_gemm_time": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                         C.c_int, C.c_int, C.POINTER(C.c_float)]),
     "roller_b200_gemm_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
@@ -165,6 +167,15 @@ def gemm_static_scratch(tile: KTile, mode: int, M: int, N: int, K: int, lda: int
                                                  a_ptr, b_ptr, c_ptr, status_ptr or None,
                                                  _stream_ptr(stream)),
           "roller_b200_gemm_static_scratch")
+
+
+def copy_block_async(dst_ptr: int, dst_ld: int, src_ptr: int, src_ld: int, rows: int, cols: int,
+                     stream=None) -> None:
+    """Enqueue a copy-engine copy of a rows x cols fp32 block between two device matrices
+    (either may be a peer GPU's mapped memory)."""
+    check(load().roller_b200_copy_block_async(dst_ptr, dst_ld, src_ptr, src_ld, rows, cols,
+                                              _stream_ptr(stream)),
+          "roller_b200_copy_block_async")
 
 
 class GemmPlan:

@@ -426,6 +426,23 @@ int roller_b200_gemm_host(roller_plan* p, const float* hA, const float* hB, floa
   return ROLLER_OK;
 }
 
+int roller_b200_copy_block_async(float* dst, long long dst_ld, const float* src, long long src_ld,
+                                 long long rows, long long cols, void* stream) {
+  if (rows < 0 || cols < 0 || dst_ld < cols || src_ld < cols) return ROLLER_ERR_INVALID;
+  if (rows == 0 || cols == 0) return ROLLER_OK;
+  if (!dst || !src) return ROLLER_ERR_INVALID;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t width = sizeof(float) * static_cast<size_t>(cols);
+  if (dst_ld == cols && src_ld == cols) {
+    RB_CUDA(cudaMemcpyAsync(dst, src, width * static_cast<size_t>(rows), cudaMemcpyDefault, st));
+  } else {
+    RB_CUDA(cudaMemcpy2DAsync(dst, sizeof(float) * static_cast<size_t>(dst_ld), src,
+                              sizeof(float) * static_cast<size_t>(src_ld), width,
+                              static_cast<size_t>(rows), cudaMemcpyDefault, st));
+  }
+  return ROLLER_OK;
+}
+
 int roller_b200_gemm_launch_info(const roller_plan* p, int* grid, int* block, int* smem_bytes,
                                  int* tiles_m, int* tiles_n, int* max_clusters) {
   if (!p) return ROLLER_ERR_INVALID;

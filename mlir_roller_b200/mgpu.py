@@ -179,3 +179,147 @@ class ShardedGemm:
 
     def flops(self) -> int:
         return 2 * self.block.rows * self.block.cols * self.K
+
+
+def split_bands(row0: int, row1: int, bands: int, align: int = 256) -> List[Tuple[int, int]]:
+    """Cut the rows [row0, row1) of one rank's block into at most `bands` non-empty bands whose
+    inner boundaries fall on multiples of `align` rows counted from row0 (one pair tile), the
+    earlier bands taking the remainder units."""
+    if bands < 1:
+        raise ValueError("bands must be positive")
+    return [(row0 + a, row0 + b) for a, b in _split(row1 - row0, bands, align) if b > a]
+
+
+def default_bands(rows: int, cols: int) -> int:
+    """Bands per block for the overlapped exchange. More bands hide more of the copy but leave
+    each kernel fewer 256 x 256 tiles to spread over the device (74 CTA pairs). Measured on
+    B200s: blocks of 512 tiles (2048 x 16384, 4096 x 8192) are best cut in 4, blocks of 64 to 256
+    tiles (1024 x 4096, 4096 x 4096) in 2."""
+    tiles = -(-rows // 256) * -(-cols // 256)
+    if tiles >= 384:
+        return 4
+    if tiles >= 48:
+        return 2
+    return 1
+
+
+def push_order(rank: int, world_size: int, dest: str, root: int = 0) -> List[int]:
+    """Ranks this rank pushes its finished bands to. "root": only the root (nothing when this
+    rank is the root); "all": every other rank, starting with the next one so that at any
+    moment the ranks write to different destinations instead of all converging on rank 0."""
+    if dest == "root":
+        return [] if rank == root else [root]
+    if dest == "all":
+        return [(rank + d) % world_size for d in range(1, world_size)]
+    raise ValueError(f"dest must be 'root' or 'all', not {dest!r}")
+
+
+class OverlappedGemm:
+    """Sharded C = A @ B whose exchange of C runs underneath the computation.
+
+    Every rank holds the whole C in symmetric memory (one allocation per rank, mapped into the
+    other ranks' address spaces over NVLink). A rank computes its block band by band; as soon as
+    a band is finished it is pushed into the destination ranks' C by the copy engines on side
+    streams while the tensor cores work on the next band, so only the last band's copy is
+    exposed. `finish` closes the step with one small all-reduce enqueued behind the copies: when
+    it has completed on a rank, every rank's pushes had completed before it.
+
+    dest = "root": the whole C ends up on `root` (a gather); dest = "all": on every rank.
+    C must not be read while another rank may still be pushing the next step into it: separate
+    consecutive steps by whatever makes the readers finish first (the bench only times).
+
+        og = OverlappedGemm(M, N, K, rank, world, bands=4, dest="all")
+        og.run(A_rows, B_full); og.finish()       # og.C now holds the product
+    """
+
+    def __init__(self, M: int, N: int, K: int, rank: int, world_size: int,
+                 grid: Optional[Tuple[int, int]] = None, mode: int = 3,
+                 bands: Optional[int] = None, dest: str = "root", root: int = 0, group=None, arch=None, measure: bool = False,
+                 comm_streams: int = 2):
+        import os
+        # plain peer mappings only: no NVLink multicast object is bound to the buffer
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import _lib, roller
+        from .analyze import MatmulConfig
+
+        self.M, self.N, self.K = M, N, K
+        self.rank, self.world_size = rank, world_size
+        self.grid = grid if grid is not None else default_grid(world_size, M, N)
+        if self.grid[0] * self.grid[1] != world_size:
+            raise ValueError(f"grid {self.grid} does not match world size {world_size}")
+        self.blocks = partition(M, N, self.grid[0], self.grid[1], align_m=256)
+        self.block = self.blocks[rank]
+        self.mode = mode
+        self.group = group if group is not None else dist.group.WORLD
+        self.dests = push_order(rank, world_size, dest, root)
+        self._lib = _lib
+        self._dist = dist
+        self._torch = torch
+
+        self.C = symm_mem.empty((M, N), dtype=torch.float32, device=torch.device("cuda"))
+        self.handle = symm_mem.rendezvous(self.C, self.group)
+        self.peer_C = {d: self.handle.get_buffer(d, (M, N), torch.float32) for d in self.dests}
+        self._token = torch.zeros(1, dtype=torch.float32, device="cuda")
+        self.comm = [torch.cuda.Stream() for _ in range(max(1, comm_streams))]
+        if bands is None:
+            bands = default_bands(self.block.rows, self.block.cols)
+        self.bands = (split_bands(self.block.row0, self.block.row1, bands)
+                      if self.block.cols > 0 else [])
+        self.plans, self.tiles, self._events = [], [], []
+        by_shape = {}
+        for r0, r1 in self.bands:
+            shape = (r1 - r0, self.block.cols)
+            if shape not in by_shape:
+                cfg = MatmulConfig(shape[0], shape[1], K, 32)
+                hint, _fn, _ms = roller.best_hint(cfg, arch, mode=mode, measure=measure)
+                by_shape[shape] = roller.kernel_tile_for(hint)
+            tile = by_shape[shape]
+            self.tiles.append(tile)
+            self.plans.append(_lib.GemmPlan(tile, shape[0], shape[1], K, lda=K, ldb=N, ldc=N,
+                                            mode=mode))
+            self._events.append(torch.cuda.Event())
+
+    def run(self, A_rows, B_full, stream=None) -> None:
+        """Enqueue this rank's bands and their pushes. `A_rows` = A[rows of this rank's block, :]
+        contiguous, `B_full` = the whole K x N matrix, contiguous."""
+        torch = self._torch
+        cs = stream if stream is not None else torch.cuda.current_stream()
+        b, N, K = self.block, self.N, self.K
+        for st in self.comm:
+            st.wait_stream(cs)          # the previous step's consumers are ordered before the pushes
+        n = 0
+        for (r0, r1), plan, ev in zip(self.bands, self.plans, self._events):
+            off = (r0 * N + b.col0) * 4
+            plan.run_ptr(A_rows.data_ptr() + (r0 - b.row0) * K * 4, B_full.data_ptr() + b.col0 * 4,
+                         self.C.data_ptr() + off, cs)
+            ev.record(cs)
+            for d in self.dests:
+                st = self.comm[n % len(self.comm)]
+                n += 1
+                st.wait_event(ev)
+                self._lib.copy_block_async(self.peer_C[d].data_ptr() + off, N,
+                                           self.C.data_ptr() + off, N, r1 - r0, b.cols, st)
+
+    def finish(self, stream=None) -> None:
+        """Enqueue the closing fence; once `stream` has passed it, every rank's pushes of this
+        step have landed."""
+        torch = self._torch
+        cs = stream if stream is not None else torch.cuda.current_stream()
+        lead = self.comm[0]
+        for st in self.comm[1:]:
+            lead.wait_stream(st)
+        lead.wait_stream(cs)
+        with torch.cuda.stream(lead):
+            self._dist.all_reduce(self._token, group=self.group)
+        cs.wait_stream(lead)
+
+    def flops(self) -> int:
+        return 2 * self.block.rows * self.block.cols * self.K
+
+    def destroy(self) -> None:
+        for p in self.plans:
+            p.destroy()
+        self.plans = []

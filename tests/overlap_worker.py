@@ -1,0 +1,67 @@
+"""Worker for test_overlap_gpu.py: one process per GPU (launched through torch.distributed.run),
+checks mgpu.OverlappedGemm -- bands pushed into the destination ranks' C over symmetric memory
+-- against an fp64 product. Exits non-zero on any mismatch."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from mlir_roller_b200 import mgpu  # noqa: E402
+
+TOL_3X = 1e-5
+
+
+def main() -> int:
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    M, N, K = 2048, 1024, 640
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)                       # the same A and B on every rank
+    A = torch.rand(M, K, device="cuda", generator=g) * 2 - 1
+    B = torch.rand(K, N, device="cuda", generator=g) * 2 - 1
+    ref = A.double() @ B.double()
+    scale = float(ref.abs().max())
+    grids = [(world, 1)] + ([(1, world), (2, world // 2)] if world % 2 == 0 else [])
+    bad = 0
+    for grid in grids:
+        for dest in ("root", "all"):
+            for bands in (1, 3):
+                og = mgpu.OverlappedGemm(M, N, K, rank, world, grid=grid, bands=bands, dest=dest)
+                assert og.handle.multicast_ptr == 0
+                b = og.block
+                og.C.fill_(float("nan"))
+                torch.cuda.synchronize()
+                dist.barrier()
+                for _ in range(2):          # twice: the second step overwrites the first
+                    og.run(A[b.row0:b.row1].contiguous(), B)
+                    og.finish()
+                    torch.cuda.synchronize()
+                    dist.barrier()
+                for p in og.plans:
+                    p.check_status()
+                if dest == "all" or rank == 0:
+                    err = float((og.C.double() - ref).abs().max()) / scale
+                else:                       # only this rank's own block is defined
+                    err = float((og.C[b.row0:b.row1, b.col0:b.col1].double()
+                                 - ref[b.row0:b.row1, b.col0:b.col1]).abs().max()) / scale \
+                        if b.rows * b.cols else 0.0
+                ok = err <= TOL_3X          # NaN compares false
+                if not ok:
+                    bad += 1
+                print(f"rank {rank} grid {grid} dest {dest} bands {bands}: err {err:.2e} "
+                      f"{'ok' if ok else 'FAIL'}", flush=True)
+                og.destroy()
+                del og
+                dist.barrier()
+    t = torch.tensor([bad], device="cuda")
+    dist.all_reduce(t)
+    dist.destroy_process_group()
+    return 1 if int(t.item()) else 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

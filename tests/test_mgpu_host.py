@@ -105,3 +105,48 @@ def test_gather_checks_block_shape():
     blocks = mgpu.partition(16, 16, 1, 1, align_m=8, align_n=4)
     with pytest.raises(ValueError):
         mgpu.gather_blocks(torch.zeros(3, 3), blocks, 16, 16, rank=0)
+
+
+@settings(max_examples=200, deadline=None)
+@given(st.integers(0, 4096), st.integers(0, 9000), st.integers(1, 9))
+def test_bands_tile_the_block(row0, rows, bands):
+    out = mgpu.split_bands(row0, row0 + rows, bands)
+    assert len(out) <= bands
+    if rows == 0:
+        assert out == []
+        return
+    assert out[0][0] == row0 and out[-1][1] == row0 + rows
+    for (a0, a1), (b0, b1) in zip(out, out[1:]):
+        assert a1 == b0
+    for r0, r1 in out:
+        assert r1 > r0 and (r0 - row0) % 256 == 0
+
+
+def test_bands_of_a_16384_row_shard():
+    assert mgpu.split_bands(2048, 4096, 4) == [(2048, 2560), (2560, 3072), (3072, 3584), (3584, 4096)]
+    assert mgpu.split_bands(0, 1000, 4) == [(0, 256), (256, 512), (512, 768), (768, 1000)]
+    with pytest.raises(ValueError):
+        mgpu.split_bands(0, 10, 0)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_push_order(world):
+    orders = [mgpu.push_order(r, world, "all") for r in range(world)]
+    for r, o in enumerate(orders):
+        assert sorted(o) == [x for x in range(world) if x != r]
+    # at every step of the rotation the ranks write to pairwise different destinations
+    for step in range(world - 1):
+        assert len({o[step] for o in orders}) == world
+    assert mgpu.push_order(0, world, "root") == []
+    if world > 1:
+        assert mgpu.push_order(1, world, "root") == [0]
+        assert mgpu.push_order(0, world, "root", root=1) == [1]
+    with pytest.raises(ValueError):
+        mgpu.push_order(0, world, "ring")
+
+
+def test_default_bands():
+    assert mgpu.default_bands(2048, 16384) == 4
+    assert mgpu.default_bands(4096, 4096) == 2
+    assert mgpu.default_bands(1024, 4096) == 2
+    assert mgpu.default_bands(512, 1024) == 1
