@@ -218,10 +218,11 @@ class ShapeCase:
         m, n, k = shape
         g = torch.Generator(device="cuda")
         g.manual_seed(idx)
-        self.A = torch.rand(m, k, device="cuda", generator=g) * 2 - 1
-        self.B = torch.rand(k, n, device="cuda", generator=g) * 2 - 1
+        dt = roller.operand_dtype(mode)      # fp32, or bf16 / fp16 for the 16-bit modes
+        self.A = (torch.rand(m, k, device="cuda", generator=g) * 2 - 1).to(dt)
+        self.B = (torch.rand(k, n, device="cuda", generator=g) * 2 - 1).to(dt)
         self.C = torch.empty(m, n, device="cuda")
-        cfg = MatmulConfig(m, n, k, 32)
+        cfg = MatmulConfig(m, n, k, 16 if dt != torch.float32 else 32)
         t0 = time.perf_counter()
         self.hint, self.fn, self.pick_ms = roller.best_hint(cfg, arch, topk=6, mode=mode,
                                                             measure=measure)
@@ -241,6 +242,17 @@ class ShapeCase:
         torch.cuda.synchronize()
         c64 = self.A.double() @ self.B.double()
         return float((self.C.double() - c64).abs().max() / c64.abs().max())
+
+
+class LibraryCase:
+    """The library GEMM (cuBLAS through torch) on a ShapeCase's operands, output in their type."""
+
+    def __init__(self, torch, case):
+        self.torch, self.A, self.B = torch, case.A, case.B
+        self.C = torch.empty(case.C.shape, dtype=case.A.dtype, device="cuda")
+
+    def launch(self):
+        self.torch.matmul(self.A, self.B, out=self.C)
 
 
 def timed_sweep(torch, cases, steps, warmup, dist=None):
@@ -374,7 +386,8 @@ def strong_scaling(torch, dist, rank, world, steps, warmup, mode):
 def run_gpu_arm(args) -> None:
     import torch
     from mlir_roller_b200 import _lib
-    from mlir_roller_b200.analyze import MODE_1XTF32, MODE_3XTF32, MatmulConfig, get_roller_hints
+    from mlir_roller_b200.analyze import (MODE_1XTF32, MODE_3XTF32, MODE_BF16, MatmulConfig,
+                                          get_roller_hints)
     from mlir_roller_b200.arch import B200, CUDA
 
     _lib.load()  # fail loudly if the CUDA library is missing
@@ -412,6 +425,17 @@ def run_gpu_arm(args) -> None:
     errs1 = [c.error(torch) for c in cases1]
     _, per_shape_ms1 = timed_sweep(torch, cases1, max(args.steps // 2, 1), 1, None)
     del cases1
+    torch.cuda.empty_cache()
+
+    # bf16 operands (the 16-bit kernels of the same family), with the library's bf16 GEMM timed
+    # on the same operands right after; not part of `value` either
+    cases16 = [ShapeCase(torch, i, s, MODE_BF16, arch, measure) for i, s in enumerate(README_SHAPES)]
+    errs16 = [c.error(torch) for c in cases16]
+    step_ms16, per_shape_ms16 = timed_sweep(torch, cases16, max(args.steps // 2, 1), 2, None)
+    lib16 = [LibraryCase(torch, c) for c in cases16]
+    step_ms16_lib, _ = timed_sweep(torch, lib16, max(args.steps // 2, 1), 2, None)
+    tiles16 = [(c.hint.block_tile, c.hint.cta_group) for c in cases16]
+    del cases16, lib16
     torch.cuda.empty_cache()
 
     e2e_ms, h2d, d2h, _ = e2e_sweep(torch, cases, max(args.steps // 2, 1))
@@ -505,6 +529,20 @@ def run_gpu_arm(args) -> None:
                       "reference_port": statistics.mean(t_ref) * 1e3},
         "max_err_3x": max(errs), "max_err_1x": max(errs1),
         "per_shape": per_shape,
+        # the same sweep with bf16 operands (fp32 accumulate and C); rank 0's own GPU only
+        "bf16": {
+            "value": sweep_flops() / step_ms16 / 1e9, "unit": UNIT, "ms_per_step": step_ms16,
+            "library_bf16_value": sweep_flops() / step_ms16_lib / 1e9,
+            "peak": peaks.get("bf16_tflops_sustained"),
+            "frac": (sweep_flops() / step_ms16 / 1e9 / peaks["bf16_tflops_sustained"]
+                     if "bf16_tflops_sustained" in peaks else None),
+            "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained (cuBLAS bf16 8192^3)",
+            "max_err": max(errs16),
+            "per_shape": [{"shape": f"M{i}", "tile": t[0], "cta_group": t[1], "ms": ms,
+                           "tflops": 2.0 * m * n * k / ms / 1e9}
+                          for i, ((m, n, k), t, ms) in enumerate(zip(README_SHAPES, tiles16,
+                                                                     per_shape_ms16))],
+        },
     }
     if strong is not None:
         line["strong"] = strong

@@ -40,6 +40,11 @@ typedef enum roller_status {
 /* Arithmetic modes of the tensor-core GEMM. */
 #define ROLLER_MODE_1XTF32 1 /* one TF32 product per fp32 product (10-bit mantissa inputs) */
 #define ROLLER_MODE_3XTF32 3 /* big/small split, three TF32 products: fp32-level accuracy */
+/* 16-bit operands: A and B hold bf16 / fp16 elements (leading dimensions in elements), products
+ * are exact, accumulation and C are fp32. The reference's MatmulConfig carries the element width
+ * (el_bits, src/analyze.py:31,39-41); its kernel generator only emits f32 (src/roller.py:47-68). */
+#define ROLLER_MODE_BF16 16
+#define ROLLER_MODE_F16 17
 
 /* Flags for roller_b200_gemm_create. */
 #define ROLLER_FLAG_ACCUMULATE 1 /* C += A@B, the semantics of the reference's gemm_kernel, which
@@ -71,7 +76,7 @@ typedef struct roller_dev_info {
 typedef struct roller_ktile {
   int block_m;   /* output tile rows (128 per CTA, 256 for a CTA pair) */
   int block_n;   /* output tile columns */
-  int rstep;     /* reduce step per pipeline stage, in elements */
+  int rstep;     /* reduce step per pipeline stage, in fp32 elements (one 128-byte row) */
   int cta_group; /* 1, or 2 = two SMs cooperate on one tile (tcgen05 cta_group::2) */
   int stages_1x; /* pipeline depth in 1xTF32 mode */
   int stages_3x; /* pipeline depth in 3xTF32 mode */
@@ -82,6 +87,10 @@ typedef struct roller_ktile {
   int threads_3x;
   int layout;    /* 0 = general tile; 2 = "skinny": for a C with few rows the tensor core works on
                     C^T, block_m (32 or 64) rows of C by block_n = 128 columns per tile */
+  int rstep_16;  /* reduce step of the tile's kernel for 16-bit operands, in elements (64);
+                    0 = the tile has no such kernel */
+  int stages_16; /* its pipeline depth and dynamic shared memory */
+  int smem_16;
 } roller_ktile;
 
 typedef struct roller_plan roller_plan;
@@ -95,32 +104,34 @@ int roller_b200_kernel_count(void);
 int roller_b200_kernel_desc(int idx, roller_ktile* out);
 
 /* Replaces Compiler(config, hint, ...).compile() (src/roller.py:345-387): bind an rTile to a
- * problem. May allocate device workspace (only when lda/ldb are not multiples of 4 elements or
- * A/B are not 16-byte aligned, in which case operands are staged through a padded copy). */
+ * problem. May allocate device workspace (only when the rows of A or B are not multiples of 16
+ * bytes long, in which case operands are staged through a padded copy). `mode` also fixes the
+ * operand element type: fp32 for the TF32 modes, bf16 / fp16 for ROLLER_MODE_BF16 / _F16. */
 int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int lda, int ldb,
                             int ldc, int mode, int flags, roller_plan** out);
 
 /* Replaces cuda_func(grid, block, (A, B, C), shared_mem=...) (src/roller.py:545-550): enqueue one
- * GEMM on `stream`. No allocation, no synchronisation. */
-int roller_b200_gemm_run(roller_plan* plan, const float* A, const float* B, float* C, void* stream);
+ * GEMM on `stream`. No allocation, no synchronisation. A and B point to elements of the type
+ * the plan's mode names; C is always fp32. */
+int roller_b200_gemm_run(roller_plan* plan, const void* A, const void* B, float* C, void* stream);
 
 /* Replaces the timed loop of run_eval (src/roller.py:564-584): `warmup` untimed launches, then
  * `iters` launches between two CUDA events on `stream`; *ms_per_iter is the mean. Blocks. */
-int roller_b200_gemm_time(roller_plan* plan, const float* A, const float* B, float* C, void* stream,
+int roller_b200_gemm_time(roller_plan* plan, const void* A, const void* B, float* C, void* stream,
                           int warmup, int iters, float* ms_per_iter);
 
 /* Host-buffer form of the whole run_eval data path -- allocate/upload operands, launch, read C
  * back (src/roller.py:532-550) -- used for end-to-end timing: copies A and B from host memory into
  * plan-owned device buffers, runs the GEMM and copies C back, all on `stream`; blocks until C
  * has arrived. The device buffers are allocated on the first call and kept. */
-int roller_b200_gemm_host(roller_plan* plan, const float* hA, const float* hB, float* hC,
+int roller_b200_gemm_host(roller_plan* plan, const void* hA, const void* hB, float* hC,
                           void* stream);
 
 /* Same data path as roller_b200_gemm_host (src/roller.py:532-550) without the final wait: the
  * copies and the launch are only enqueued on `stream`, so GEMMs on different streams overlap
  * their uploads, kernels and readbacks. Host buffers should be pinned; hC is valid once `stream`
  * has been synchronised. */
-int roller_b200_gemm_host_async(roller_plan* plan, const float* hA, const float* hB, float* hC,
+int roller_b200_gemm_host_async(roller_plan* plan, const void* hA, const void* hB, float* hC,
                                 void* stream);
 
 /* Copies a rows x cols block of fp32 between two device matrices (leading dimensions in

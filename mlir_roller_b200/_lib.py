@@ -12,6 +12,9 @@ LIB_PATH = Path(__file__).resolve().parent / "libroller_b200.so"
 
 MODE_1XTF32 = 1
 MODE_3XTF32 = 3
+MODE_BF16 = 16      # bf16 A and B, fp32 accumulation and C
+MODE_F16 = 17       # fp16 A and B, fp32 accumulation and C
+MODES_16BIT = (MODE_BF16, MODE_F16)
 FLAG_ACCUMULATE = 1
 FLAG_B_TRANSPOSED = 2
 LAYOUT_GENERAL = 0
@@ -52,6 +55,7 @@ class KTile(C.Structure):
         ("tmem_cols", C.c_int),
         ("threads_1x", C.c_int), ("threads_3x", C.c_int),
         ("layout", C.c_int),
+        ("rstep_16", C.c_int), ("stages_16", C.c_int), ("smem_16", C.c_int),
     ]
 
     def as_dict(self) -> dict:
@@ -200,10 +204,21 @@ class GemmPlan:
         check(self._lib.roller_b200_gemm_run(self._h, a_ptr, b_ptr, c_ptr, _stream_ptr(stream)),
               "roller_b200_gemm_run")
 
+    def _check_dtypes(self, A, B, Cout) -> None:
+        """A and B must hold the element type the plan's mode names, C fp32 (the C side only
+        sees pointers)."""
+        import torch
+        want = {MODE_BF16: torch.bfloat16, MODE_F16: torch.float16}.get(self.mode, torch.float32)
+        for name, t, dt in (("A", A, want), ("B", B, want), ("C", Cout, torch.float32)):
+            if getattr(t, "dtype", dt) != dt:
+                raise TypeError(f"{name} is {t.dtype}, this plan (mode {self.mode}) needs {dt}")
+
     def run(self, A, B, Cout, stream=None) -> None:
+        self._check_dtypes(A, B, Cout)
         self.run_ptr(A.data_ptr(), B.data_ptr(), Cout.data_ptr(), stream)
 
     def time(self, A, B, Cout, warmup: int = 3, iters: int = 20, stream=None) -> float:
+        self._check_dtypes(A, B, Cout)
         ms = C.c_float()
         check(self._lib.roller_b200_gemm_time(self._h, A.data_ptr(), B.data_ptr(), Cout.data_ptr(),
                                               _stream_ptr(stream), warmup, iters, C.byref(ms)),
@@ -211,7 +226,7 @@ class GemmPlan:
         return float(ms.value)
 
     def run_host(self, hA, hB, hC, stream=None, wait: bool = True) -> None:
-        """hA/hB/hC: contiguous fp32 host arrays (numpy or pinned torch CPU tensors). With
+        """hA/hB/hC: contiguous host arrays of the plan's element type (C fp32) (numpy or pinned torch CPU tensors). With
         `wait=False` the upload, kernel and readback are only enqueued on `stream`."""
         def ptr(x):
             return x.ctypes.data if hasattr(x, "ctypes") else x.data_ptr()

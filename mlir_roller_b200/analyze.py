@@ -311,8 +311,10 @@ class Policy:
 
 
 # --------------------------------------------------------------------------- Blackwell policy
-MODE_1XTF32 = 1
-MODE_3XTF32 = 3
+MODE_1XTF32 = 1     # fp32 operands, one TF32 product each
+MODE_3XTF32 = 3     # fp32 operands, big/small split: three TF32 products, fp32-level accuracy
+MODE_BF16 = 16      # bf16 operands (el_bits = 16), exact products, fp32 accumulation and C
+MODE_F16 = 17       # fp16 operands (el_bits = 16), likewise
 
 
 class BlackwellPolicy:
@@ -333,11 +335,19 @@ class BlackwellPolicy:
     those replace the analytic per-k-block term.
     """
 
-    def __init__(self, config: MatmulConfig, arch: B200, mode: int = MODE_3XTF32) -> None:
-        if config.el_bits != 32:
-            raise ValueError("the sm_100a kernel family is fp32-in / fp32-out (el_bits must be 32)")
-        if mode not in (MODE_1XTF32, MODE_3XTF32):
-            raise ValueError("mode must be 1 (1xTF32) or 3 (3xTF32)")
+    def __init__(self, config: MatmulConfig, arch: B200, mode: Optional[int] = None) -> None:
+        if config.el_bits == 32:
+            mode = MODE_3XTF32 if mode is None else mode
+            if mode not in (MODE_1XTF32, MODE_3XTF32):
+                raise ValueError("fp32 operands: mode must be 1 (1xTF32) or 3 (3xTF32)")
+        elif config.el_bits == 16:
+            # the element width says 16-bit; whether that is bf16 or fp16 is the mode's business
+            mode = MODE_BF16 if mode is None or mode in (MODE_1XTF32, MODE_3XTF32) else mode
+            if mode not in (MODE_BF16, MODE_F16):
+                raise ValueError("16-bit operands: mode must be 16 (bf16) or 17 (fp16)")
+        else:
+            raise ValueError("the sm_100a kernel family takes 32-bit or 16-bit operands "
+                             "(el_bits must be 32 or 16)")
         self.matmul_config = config
         self.arch = arch
         self.mode = mode
@@ -345,14 +355,21 @@ class BlackwellPolicy:
     def _analyse(self, block_m: int, block_n: int, cta_group: int, stages: int,
                  layout: int = 0) -> TileDict:
         cfg, dev, mode = self.matmul_config, self.arch, self.mode
-        td = TileDict([block_m, block_n], cfg, dev.rstep)
+        eb = cfg.el_bytes
+        sixteen = mode in (MODE_BF16, MODE_F16)
+        rstep = dev.rstep * 4 // eb              # one 128-byte swizzle row of k
+        # tensor-core products per operand product, and k per instruction
+        products = 1 if sixteen else mode
+        mma_k = dev.mma_k * 4 // eb
+        macs_per_clk = dev.tf32_macs_per_clk_sm * (2 if sixteen else 1)
+        td = TileDict([block_m, block_n], cfg, rstep)
         td.cta_group, td.stages, td.mode, td.layout = cta_group, stages, mode, layout
         td.thread_tile = [1, 32]  # what one epilogue thread reads from TMEM at a time
         # the accumulator's columns are the tile's N side, or its M side in the skinny layout
         td.tmem_cols = 2 * (block_m if layout == 2 else block_n)
         rows_cta = block_m // cta_group          # A rows staged per CTA
         cols_cta = block_n // cta_group          # B columns staged per CTA
-        raw = (rows_cta + cols_cta) * dev.rstep * 4
+        raw = (rows_cta + cols_cta) * rstep * eb
         td.smem_cost = raw * (2 if mode == MODE_3XTF32 else 1)
         td.valid = (td.smem_cost * stages + 2048 <= dev.smem_cap and td.tmem_cols <= dev.tmem_columns)
         td.grid_size = (-(-cfg.M // block_m)) * (-(-cfg.N // block_n))
@@ -361,14 +378,14 @@ class BlackwellPolicy:
         workers = max(dev.compute_max_core // cta_group, 1)
         td.num_wave = -(-td.grid_size // workers)
 
-        num_kb = -(-cfg.K // dev.rstep)
-        measured = dev.kblock_us.get((block_m, block_n, cta_group)) if layout == 0 else \
-            dev.kblock_us.get((block_m, block_n, cta_group, layout))
+        num_kb = -(-cfg.K // rstep)
+        key = (block_m, block_n, cta_group) if layout == 0 else (block_m, block_n, cta_group, layout)
+        measured = dev.kblock_us_16.get(key) if sixteen else dev.kblock_us.get(key)
         if measured is not None:
-            kb_us = measured[0] if mode == MODE_1XTF32 else measured[1]
+            kb_us = measured if sixteen else (measured[0] if mode == MODE_1XTF32 else measured[1])
         else:
-            tensor_clk = rows_cta * block_n * dev.rstep * mode / dev.tf32_macs_per_clk_sm
-            mma_reads = (rows_cta + cols_cta) * dev.mma_k * 4 * (dev.rstep // dev.mma_k) * mode
+            tensor_clk = rows_cta * block_n * rstep * products / macs_per_clk
+            mma_reads = (rows_cta + cols_cta) * mma_k * eb * (rstep // mma_k) * products
             split_rw = 2 * raw if mode == MODE_3XTF32 else 0
             smem_clk = (raw + split_rw + mma_reads) / dev.smem_bytes_per_clk_sm
             l2_clk = raw / dev.l2_bytes_per_clk_sm
@@ -389,31 +406,36 @@ class BlackwellPolicy:
         # launch, pipeline fill, last drain and the C stores of the final tile
         fixed_us = 8.0 + rows_cta * block_n * 4 / 32768.0
         worker_us = waves * num_kb * kb_us + fixed_us
-        hbm_bytes = 4.0 * (cfg.M * cfg.K + cfg.K * cfg.N + cfg.M * cfg.N)
+        hbm_bytes = float(eb) * (cfg.M * cfg.K + cfg.K * cfg.N) + 4.0 * cfg.M * cfg.N
         hbm_us = hbm_bytes / (dev.hbm_gbs * 1e3) + 4.0
         td.est_us = max(worker_us, hbm_us)
         # operands whose rows are not 16-byte aligned are first copied into padded buffers
         # (one read + one write each, ahead of the GEMM)
-        if cfg.K % 4:
-            td.est_us += 8.0 * cfg.M * cfg.K / (dev.hbm_gbs * 1e3) * 1.5 + 3.0
-        if cfg.N % 4:
-            td.est_us += 8.0 * cfg.K * cfg.N / (dev.hbm_gbs * 1e3) * 1.5 + 3.0
-        td.kernel = (f"gemm_tf32<{block_m}x{block_n}x{dev.rstep},cg{cta_group},{mode}x"
-                     + (",skinny>" if layout == 2 else ">"))
+        if cfg.K * eb % 16:
+            td.est_us += 2.0 * eb * cfg.M * cfg.K / (dev.hbm_gbs * 1e3) * 1.5 + 3.0
+        if cfg.N * eb % 16:
+            td.est_us += 2.0 * eb * cfg.K * cfg.N / (dev.hbm_gbs * 1e3) * 1.5 + 3.0
+        arith = {MODE_BF16: "bf16", MODE_F16: "f16"}.get(mode, f"{mode}x")
+        td.kernel = (f"gemm_{'f16' if sixteen else 'tf32'}<{block_m}x{block_n}x{rstep},"
+                     f"cg{cta_group},{arith}" + (",skinny>" if layout == 2 else ">"))
         return td
 
     def emit_config(self, topk: int = 10) -> List[TileDict]:
-        tiles = [self._analyse(bm, bn, cg, s1 if self.mode == MODE_1XTF32 else s3, layout)
-                 for (bm, bn, cg, s1, s3, layout) in self.arch.kernel_tiles]
+        sixteen = self.mode in (MODE_BF16, MODE_F16)
+        tiles = [self._analyse(bm, bn, cg, s16 if sixteen else (s1 if self.mode == MODE_1XTF32 else s3),
+                               layout)
+                 for (bm, bn, cg, s1, s3, layout, s16) in self.arch.kernel_tiles
+                 if not sixteen or s16 > 0]
         tiles = [td for td in tiles if td.valid]
         tiles.sort(key=lambda td: (td.est_us, td.traffic * td.grid_size))
         return tiles[:topk]
 
 
 def get_roller_hints(matmul_config: MatmulConfig, arch: TileDevice, topk: int = 10,
-                     mode: int = MODE_3XTF32) -> List[TileDict]:
+                     mode: Optional[int] = None) -> List[TileDict]:
     """Top-k rTile hints, best first (src/analyze.py:384-387). `mode` only matters for a
-    `B200` device model."""
+    `B200` device model: 1 / 3 (1xTF32 / 3xTF32, default 3) for 32-bit operands, 16 / 17
+    (bf16, the default, / fp16) for 16-bit operands."""
     if isinstance(arch, B200):
         return BlackwellPolicy(matmul_config, arch, mode).emit_config(topk)
     return Policy(matmul_config, arch).emit_config(topk)

@@ -55,19 +55,20 @@ class CUDA(TileDevice):
 
 
 # rTiles for which libroller_b200 carries a compiled kernel:
-# (block_m, block_n, cta_group, stages_1x, stages_3x, layout). Layout 0 is the general tile;
+# (block_m, block_n, cta_group, stages_1x, stages_3x, layout, stages_16); stages_16 is the
+# pipeline depth of the tile's kernel for 16-bit operands (0 = none). Layout 0 is the general tile;
 # layout 2 is the "skinny" tile for a C with few rows (the tensor core works on C^T, so the
 # narrow side, block_m, runs along M). Kept in step with the library by a test that compares
 # the table against roller_b200_kernel_desc().
-B200_KERNEL_TILES: Tuple[Tuple[int, int, int, int, int, int], ...] = (
-    (256, 256, 2, 7, 3, 0),
-    (256, 128, 2, 8, 4, 0),
-    (256, 64, 2, 8, 5, 0),
-    (128, 256, 1, 4, 2, 0),
-    (128, 128, 1, 7, 3, 0),
-    (128, 64, 1, 8, 4, 0),
-    (64, 128, 1, 8, 4, 2),
-    (32, 128, 1, 8, 5, 2),
+B200_KERNEL_TILES: Tuple[Tuple[int, int, int, int, int, int, int], ...] = (
+    (256, 256, 2, 7, 3, 0, 7),
+    (256, 128, 2, 8, 4, 0, 8),
+    (256, 64, 2, 8, 5, 0, 0),
+    (128, 256, 1, 4, 2, 0, 4),
+    (128, 128, 1, 7, 3, 0, 7),
+    (128, 64, 1, 8, 4, 0, 8),
+    (64, 128, 1, 8, 4, 2, 8),
+    (32, 128, 1, 8, 5, 2, 8),
 )
 
 
@@ -87,6 +88,21 @@ B200_KBLOCK_US = {
     # at 5.7 TB/s (1xTF32) / 3.6 TB/s (3xTF32)
     (32, 128, 1, 2): (0.39, 0.63),
     (64, 128, 1, 2): (0.40, 0.66),
+}
+
+
+# The same for the 16-bit kernels (bf16 / fp16 operands): one k-block is 64 deep, i.e. the same
+# 128 bytes per operand row and the same number of tensor-core clocks as a 1xTF32 k-block.
+# Measured at 8192^3 and 4096^3 in bf16; the narrow and skinny entries are the 1xTF32 figures
+# scaled by the ratio seen on the measured tiles (1.13).
+B200_KBLOCK_US_16 = {
+    (256, 256, 2): 0.445,
+    (256, 128, 2): 0.364,
+    (128, 256, 1): 0.575,
+    (128, 128, 1): 0.362,
+    (128, 64, 1): 0.314,
+    (32, 128, 1, 2): 0.44,
+    (64, 128, 1, 2): 0.45,
 }
 
 
@@ -122,8 +138,10 @@ class B200(TileDevice):
     sm_clock_mhz: float = 1700.0        # typical clock under tensor load (1965 boost)
     hbm_gbs: float = 6532.0             # measured copy bandwidth
     tf32_tflops: float = 790.0          # measured dense TF32 rate (cuBLAS, 8192^3)
-    kernel_tiles: Tuple[Tuple[int, int, int, int, int, int], ...] = B200_KERNEL_TILES
+    kernel_tiles: Tuple[Tuple[int, int, int, int, int, int, int], ...] = B200_KERNEL_TILES
     kblock_us: dict = field(default_factory=lambda: dict(B200_KBLOCK_US))
+    kblock_us_16: dict = field(default_factory=lambda: dict(B200_KBLOCK_US_16))
+    bf16_tflops: float = 1621.6         # measured dense bf16 rate (cuBLAS, 8192^3, burst)
 
     @classmethod
     def from_device(cls, dev: int = 0) -> "B200":
@@ -139,6 +157,7 @@ class B200(TileDevice):
         model.tmem_columns = info.tmem_columns
         model.compute_capability = f"{info.cc_major}{info.cc_minor}a"
         model.kernel_tiles = tuple(
-            (kt.block_m, kt.block_n, kt.cta_group, kt.stages_1x, kt.stages_3x, kt.layout)
+            (kt.block_m, kt.block_n, kt.cta_group, kt.stages_1x, kt.stages_3x, kt.layout,
+             kt.stages_16)
             for kt in _lib.kernel_tiles())
         return model

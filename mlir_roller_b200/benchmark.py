@@ -31,8 +31,10 @@ def _error_vs_fp64(cuda_func, config: MatmulConfig, seed: int = 0) -> float:
     import torch
     g = torch.Generator(device="cuda")
     g.manual_seed(seed)
-    A = torch.rand(config.M, config.K, device="cuda", generator=g) * 2 - 1
-    B = torch.rand(config.K, config.N, device="cuda", generator=g) * 2 - 1
+    from .roller import operand_dtype
+    dt = operand_dtype(cuda_func.plan.mode)     # 16-bit kernels: fp64 product of the rounded inputs
+    A = (torch.rand(config.M, config.K, device="cuda", generator=g) * 2 - 1).to(dt)
+    B = (torch.rand(config.K, config.N, device="cuda", generator=g) * 2 - 1).to(dt)
     C = torch.empty(config.M, config.N, device="cuda")
     cuda_func((1, 1), (1, 1), (A.data_ptr(), B.data_ptr(), C.data_ptr()))
     C64 = A.double() @ B.double()
@@ -45,11 +47,12 @@ def benchmark(test_shapes: list[tuple[int, int, int]], topk: int = 20, mode: int
     results = []
     for m, n, k in test_shapes:
         print(f"--- Benchmarking M={m}, N={n}, K={k} ---")
-        config = MatmulConfig(M=m, N=n, K=k, el_bits=32)
+        sixteen = mode in (16, 17)
+        config = MatmulConfig(M=m, N=n, K=k, el_bits=16 if sixteen else 32)
 
-        print("Running baseline (cuBLAS fp32 via torch)...")
+        print("Running baseline (cuBLAS via torch, same operand type)...")
         try:
-            baseline_time, baseline_gflops = run_baseline(config)
+            baseline_time, baseline_gflops = run_baseline(config, mode=mode)
             print(f"cuBLAS baseline: {baseline_time:.6f} ms, {baseline_gflops:.6f} GFLOPS")
         except Exception as e:  # noqa: BLE001 - mirror the reference: report and go on
             print(f"cuBLAS baseline failed: {e}")
@@ -85,7 +88,8 @@ def benchmark(test_shapes: list[tuple[int, int, int]], topk: int = 20, mode: int
             print("All roller hints failed.")
 
         err = _error_vs_fp64(best_func, config) if (best_func and check_error) else float("nan")
-        tensor_tflops = best_gflops * mode / 1e3
+        tensor_tflops = best_gflops * (1 if sixteen else mode) / 1e3
+        peak = getattr(arch, "bf16_tflops" if sixteen else "tf32_tflops", float("nan"))
         results.append({
             "M": m, "N": n, "K": k,
             "CuPy Time (ms)": baseline_time,
@@ -96,9 +100,9 @@ def benchmark(test_shapes: list[tuple[int, int, int]], topk: int = 20, mode: int
                                 if best_time > 0 and baseline_time != float("inf") else 0),
             "Best Hint": str(best_hint) if best_hint else "N/A",
             "search_ms": search_ms,
-            "mode": f"{mode}xTF32",
+            "mode": {16: "bf16", 17: "fp16"}.get(mode, f"{mode}xTF32"),
             "tflops": best_gflops / 1e3,
-            "roofline_frac": tensor_tflops / getattr(arch, "tf32_tflops", float("nan")),
+            "roofline_frac": tensor_tflops / peak,
             "max_rel_err": err,
         })
         # keep partial results if the sweep is interrupted

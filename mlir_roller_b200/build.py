@@ -14,8 +14,8 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libroller_b200.so"
 
-SOURCES = ["gemm_variants.cu", "capi.cu", "noalloc.cu"]
-HEADERS = ["ptx_sm100.cuh", "gemm_tf32_sm100.cuh", "gemm_launch.h"]
+SOURCES = ["gemm_variants.cu", "gemm_variants_16.cu", "capi.cu", "noalloc.cu"]
+HEADERS = ["ptx_sm100.cuh", "gemm_tf32_sm100.cuh", "gemm_launch.h", "gemm_variant_make.cuh"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -48,13 +48,17 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     objs = []
     build_dir = PKG_DIR / "build"
     build_dir.mkdir(exist_ok=True)
-    for src in SOURCES:
+    procs = []
+    for src in SOURCES:      # the translation units are independent: compile them side by side
         obj = build_dir / (src + ".o")
         cmd = [nvcc, *NVCC_FLAGS, "-c", str(CSRC / src), "-o", str(obj)]
         if verbose:
             cmd[1:1] = ["-Xptxas", "-v"]
-        subprocess.run(cmd, check=True)
+        procs.append((cmd, subprocess.Popen(cmd)))
         objs.append(str(obj))
+    failed = [cmd for cmd, pr in procs if pr.wait() != 0]
+    if failed:
+        raise subprocess.CalledProcessError(1, failed[0])
     subprocess.run([nvcc, "-shared", "-o", str(LIB_PATH), *objs, "-gencode",
                     "arch=compute_100a,code=sm_100a"], check=True)
     return LIB_PATH

@@ -45,23 +45,35 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// Row-major fp32 matrix `rows x cols` with row stride `ld` elements, loaded in boxes of
-// box_rows x box_cols; out-of-range elements read as zero. With `round_to_tf32` the TMA unit
-// rounds every element to the nearest TF32 value on its way into shared memory (measured on
+// Element types a tensor map can be encoded for.
+enum ElemType { kElemF32 = 0, kElemTf32 = 1, kElemBf16 = 2, kElemF16 = 3 };
+
+int elem_bytes_of_mode(int mode) {
+  return (mode == ROLLER_MODE_BF16 || mode == ROLLER_MODE_F16) ? 2 : 4;
+}
+
+// Row-major matrix `rows x cols` with row stride `ld` elements, loaded in boxes of
+// box_rows x box_cols; out-of-range elements read as zero. With kElemTf32 the TMA unit rounds
+// every fp32 element to the nearest TF32 value on its way into shared memory (measured on
 // B200: 1xTF32 error 6.4e-4 -> 2.4e-4 against truncation by the tensor core, at no cost); the
-// 3xTF32 mode needs the raw words and loads them untouched.
-int encode_matrix(CUtensorMap* tm, const float* base, long long rows, long long cols, long long ld,
-                  int box_cols, int box_rows, CUtensorMapSwizzle swz, bool round_to_tf32) {
+// 3xTF32 mode needs the raw words and loads them untouched (kElemF32).
+int encode_matrix(CUtensorMap* tm, const void* base, long long rows, long long cols, long long ld,
+                  int box_cols, int box_rows, CUtensorMapSwizzle swz, ElemType et) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) {
     snprintf(g_cuda_err, sizeof(g_cuda_err), "cuTensorMapEncodeTiled entry point not found");
     return ROLLER_ERR_CUDA;
   }
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * sizeof(float)};
+  const size_t eb = (et == kElemBf16 || et == kElemF16) ? 2 : 4;
+  const CUtensorMapDataType dt = et == kElemBf16  ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                 : et == kElemF16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                 : et == kElemTf32 ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32
+                                                   : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * eb};
   cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(tm, round_to_tf32 ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides,
+  CUresult r = fn(tm, dt, 2, const_cast<void*>(base), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -72,10 +84,11 @@ int encode_matrix(CUtensorMap* tm, const float* base, long long rows, long long 
   return ROLLER_OK;
 }
 
-// Copies a rows x cols matrix into a buffer whose row stride is a multiple of 4 elements, so
+// Copies a rows x cols matrix into a buffer whose rows are a multiple of 16 bytes long, so
 // that TMA's 16-byte stride rule holds for operands with odd leading dimensions.
-__global__ void pad_rows_kernel(const float* __restrict__ src, long long ld_src,
-                                float* __restrict__ dst, long long ld_dst, int rows, int cols) {
+template <typename T>
+__global__ void pad_rows_kernel(const T* __restrict__ src, long long ld_src,
+                                T* __restrict__ dst, long long ld_dst, int rows, int cols) {
   const long long total = static_cast<long long>(rows) * cols;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -85,7 +98,21 @@ __global__ void pad_rows_kernel(const float* __restrict__ src, long long ld_src,
   }
 }
 
-long long round_up4(long long x) { return (x + 3) & ~3LL; }
+// Smallest leading dimension >= x whose rows are a multiple of 16 bytes long.
+long long round_up_ld(long long x, int elem_bytes) {
+  const long long q = 16 / elem_bytes;
+  return (x + q - 1) / q * q;
+}
+
+void pad_rows(const void* src, long long ld_src, void* dst, long long ld_dst, int rows, int cols,
+              int elem_bytes, int blocks, cudaStream_t st) {
+  if (elem_bytes == 2)
+    pad_rows_kernel<uint16_t><<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(src), ld_src,
+                                                     static_cast<uint16_t*>(dst), ld_dst, rows, cols);
+  else
+    pad_rows_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(src), ld_src,
+                                                  static_cast<float*>(dst), ld_dst, rows, cols);
+}
 
 }  // namespace
 
@@ -99,9 +126,10 @@ struct roller_plan {
   int M, N, K;
   long long lda, ldb, ldc;
   int mode, flags;
+  int elem;               // bytes per element of A and B
   int layout;             // 0 plain, 1 B given transposed, 2 skinny (roles swapped)
   int tiles_m, tiles_n, grid;
-  int chunk_kb;           // accumulation chunk, in 32-element k-blocks
+  int chunk_kb;           // accumulation chunk, in k-blocks (one reduce step each)
   int max_clusters;       // co-resident CTA pairs the device reports (cta_group 2 only)
   int max_workers;        // persistent workers (CTAs or CTA pairs) that may run at once
   bool grid_forced;       // grid fixed by roller_b200_gemm_set_grid
@@ -112,16 +140,17 @@ struct roller_plan {
   int sk_slots;           // CTAs the scratch area was sized for
   uint32_t epoch;         // launch counter for the flags
   bool stage_a, stage_b;  // operands go through a padded copy
-  float* ws_a;            // padded copies (device), owned
-  float* ws_b;
+  void* ws_a;             // padded copies (device), owned
+  void* ws_b;
   long long ws_lda, ws_ldb;
   uint32_t* status;  // device status word, owned
   // cached tensor maps for the last (A, B) pointers seen
-  const float* map_a_ptr;
-  const float* map_b_ptr;
+  const void* map_a_ptr;
+  const void* map_b_ptr;
   CUtensorMap tmA, tmB;
   // host-buffer path
-  float *hd_a, *hd_b, *hd_c;
+  void *hd_a, *hd_b;
+  float* hd_c;
   cudaEvent_t ev0, ev1;
 };
 
@@ -188,6 +217,11 @@ int roller_b200_kernel_desc(int idx, roller_ktile* out) {
   out->threads_1x = v1.threads;
   out->threads_3x = v3.threads;
   out->layout = v1.layout;
+  const KernelVariant* v16 = find_variant(v1.block_m, v1.block_n, 2 * v1.rstep, v1.cta_group,
+                                          ROLLER_MODE_BF16, v1.layout);
+  out->rstep_16 = v16 ? v16->rstep : 0;
+  out->stages_16 = v16 ? v16->stages : 0;
+  out->smem_16 = v16 ? v16->smem_bytes : 0;
   return ROLLER_OK;
 }
 
@@ -199,12 +233,16 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
   const bool b_transposed = (flags & ROLLER_FLAG_B_TRANSPOSED) != 0;
   if (M <= 0 || N <= 0 || K <= 0 || lda < K || ldb < (b_transposed ? K : N) || ldc < N)
     return ROLLER_ERR_INVALID;
-  if (mode != ROLLER_MODE_1XTF32 && mode != ROLLER_MODE_3XTF32) return ROLLER_ERR_INVALID;
+  if (mode != ROLLER_MODE_1XTF32 && mode != ROLLER_MODE_3XTF32 && mode != ROLLER_MODE_BF16 &&
+      mode != ROLLER_MODE_F16)
+    return ROLLER_ERR_INVALID;
+  const int elem = elem_bytes_of_mode(mode);
   if (tile->layout != 0 && tile->layout != 2) return ROLLER_ERR_INVALID;
   if (b_transposed && tile->layout != 0) return ROLLER_ERR_UNSUPPORTED;
   const int layout = b_transposed ? 1 : tile->layout;
-  const KernelVariant* kv =
-      find_variant(tile->block_m, tile->block_n, tile->rstep, tile->cta_group, mode, layout);
+  // a 16-bit kernel reduces the same 128 bytes of k per step: twice the elements
+  const KernelVariant* kv = find_variant(tile->block_m, tile->block_n,
+                                         tile->rstep * (4 / elem), tile->cta_group, mode, layout);
   if (!kv) return ROLLER_ERR_UNSUPPORTED;
 
   int dev = 0;
@@ -223,6 +261,7 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
   p->M = M; p->N = N; p->K = K;
   p->lda = lda; p->ldb = ldb; p->ldc = ldc;
   p->mode = mode;
+  p->elem = elem;
   p->flags = flags;
   p->layout = layout;
   if (layout == 2) {
@@ -240,11 +279,15 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
   // dominated by the 10-bit input mantissa, so one chunk spans the whole reduction.
   const int num_kb = (K + kv->rstep - 1) / kv->rstep;
   p->chunk_kb = (mode == ROLLER_MODE_3XTF32) ? 4 : num_kb;
+  // 16-bit products are exact, so the accumulator's rounding is the whole error. Measured on
+  // B200 (uniform inputs): 2.3e-6 of max|C| with a drain every 2048 k at any K, 1.1e-5 at
+  // K = 8192 without drains; shorter chunks cost throughput (1024 k: -6 %, 512 k: -13 %).
+  if (elem == 2 && num_kb > 32) p->chunk_kb = 32;
   // A skinny problem streams B once and is HBM-bound: it needs every SM pulling data, which
   // only a split along K provides, so 1xTF32 gets chunks too (512 k).
-  if (layout == 2 && mode == ROLLER_MODE_1XTF32 && num_kb > 16) p->chunk_kb = 16;
-  p->stage_a = (lda % 4) != 0;
-  p->stage_b = (ldb % 4) != 0;
+  if (layout == 2 && mode != ROLLER_MODE_3XTF32 && num_kb > 16) p->chunk_kb = 16;
+  p->stage_a = (static_cast<long long>(lda) * elem % 16) != 0;
+  p->stage_b = (static_cast<long long>(ldb) * elem % 16) != 0;
 
   cudaError_t e = cudaFuncSetAttribute(kv->func, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kv->smem_bytes);
@@ -271,12 +314,12 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
   if (e == cudaSuccess) e = cudaMalloc(&p->status, sizeof(uint32_t));
   if (e == cudaSuccess) e = cudaMemset(p->status, 0, sizeof(uint32_t));
   if (e == cudaSuccess && p->stage_a) {
-    p->ws_lda = round_up4(K);
-    e = cudaMalloc(&p->ws_a, sizeof(float) * p->ws_lda * M);
+    p->ws_lda = round_up_ld(K, elem);
+    e = cudaMalloc(&p->ws_a, static_cast<size_t>(elem) * p->ws_lda * M);
   }
   if (e == cudaSuccess && p->stage_b) {
-    p->ws_ldb = round_up4(b_transposed ? K : N);
-    e = cudaMalloc(&p->ws_b, sizeof(float) * p->ws_ldb * (b_transposed ? N : K));
+    p->ws_ldb = round_up_ld(b_transposed ? K : N, elem);
+    e = cudaMalloc(&p->ws_b, static_cast<size_t>(elem) * p->ws_ldb * (b_transposed ? N : K));
   }
   if (e == cudaSuccess) e = cudaEventCreate(&p->ev0);
   if (e == cudaSuccess) e = cudaEventCreate(&p->ev1);
@@ -295,7 +338,7 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
   return ROLLER_OK;
 }
 
-int roller_b200_gemm_run(roller_plan* p, const float* A, const float* B, float* C, void* stream) {
+int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, float* C, void* stream) {
   if (!p || !A || !B || !C) return ROLLER_ERR_INVALID;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const KernelVariant* kv = p->kv;
@@ -303,11 +346,11 @@ int roller_b200_gemm_run(roller_plan* p, const float* A, const float* B, float* 
   // Operands that break TMA's rules (row stride or base not a multiple of 16 bytes) are staged
   // through a padded copy; the base-alignment case needs a workspace made on demand at create
   // time, so an unaligned base with an aligned stride is rejected here.
-  const float* a_src = A;
-  const float* b_src = B;
+  const void* a_src = A;
+  const void* b_src = B;
   long long lda = p->lda, ldb = p->ldb;
   if (p->stage_a) {
-    pad_rows_kernel<<<p->sm_count * 8, 256, 0, st>>>(A, p->lda, p->ws_a, p->ws_lda, p->M, p->K);
+    pad_rows(A, p->lda, p->ws_a, p->ws_lda, p->M, p->K, p->elem, p->sm_count * 8, st);
     a_src = p->ws_a;
     lda = p->ws_lda;
   } else if (reinterpret_cast<uintptr_t>(A) & 15) {
@@ -315,9 +358,9 @@ int roller_b200_gemm_run(roller_plan* p, const float* A, const float* B, float* 
   }
   if (p->stage_b) {
     if (p->layout == 1)
-      pad_rows_kernel<<<p->sm_count * 8, 256, 0, st>>>(B, p->ldb, p->ws_b, p->ws_ldb, p->N, p->K);
+      pad_rows(B, p->ldb, p->ws_b, p->ws_ldb, p->N, p->K, p->elem, p->sm_count * 8, st);
     else
-      pad_rows_kernel<<<p->sm_count * 8, 256, 0, st>>>(B, p->ldb, p->ws_b, p->ws_ldb, p->K, p->N);
+      pad_rows(B, p->ldb, p->ws_b, p->ws_ldb, p->K, p->N, p->elem, p->sm_count * 8, st);
     b_src = p->ws_b;
     ldb = p->ws_ldb;
   } else if (reinterpret_cast<uintptr_t>(B) & 15) {
@@ -328,18 +371,25 @@ int roller_b200_gemm_run(roller_plan* p, const float* A, const float* B, float* 
   if (a_src != p->map_a_ptr || b_src != p->map_b_ptr) {
     int rc;
     const int bnl = (p->layout == 2 ? kv->block_m : kv->block_n) / kv->cta_group;
-    const bool rnd = (p->mode == ROLLER_MODE_1XTF32);
+    const ElemType et = p->mode == ROLLER_MODE_1XTF32 ? kElemTf32
+                        : p->mode == ROLLER_MODE_BF16 ? kElemBf16
+                        : p->mode == ROLLER_MODE_F16  ? kElemF16
+                                                      : kElemF32;
+    // every box row is 128 bytes: `bk` elements, which is also the reduce step; an operand
+    // that is contiguous along m/n is fetched in square boxes (fp32: 32-byte swizzle chunks)
+    const int bk = 128 / p->elem;
+    const CUtensorMapSwizzle swz_mn =
+        p->elem == 4 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
     if (p->layout == 2) {
-      rc = encode_matrix(&p->tmA, b_src, p->K, p->N, ldb, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, rnd);
+      rc = encode_matrix(&p->tmA, b_src, p->K, p->N, ldb, bk, bk, swz_mn, et);
       if (rc == ROLLER_OK)
-        rc = encode_matrix(&p->tmB, a_src, p->M, p->K, lda, 32, bnl, CU_TENSOR_MAP_SWIZZLE_128B, rnd);
+        rc = encode_matrix(&p->tmB, a_src, p->M, p->K, lda, bk, bnl, CU_TENSOR_MAP_SWIZZLE_128B, et);
     } else {
-      rc = encode_matrix(&p->tmA, a_src, p->M, p->K, lda, 32, 128, CU_TENSOR_MAP_SWIZZLE_128B, rnd);
+      rc = encode_matrix(&p->tmA, a_src, p->M, p->K, lda, bk, 128, CU_TENSOR_MAP_SWIZZLE_128B, et);
       if (rc == ROLLER_OK && p->layout == 1)
-        rc = encode_matrix(&p->tmB, b_src, p->N, p->K, ldb, 32, bnl, CU_TENSOR_MAP_SWIZZLE_128B, rnd);
+        rc = encode_matrix(&p->tmB, b_src, p->N, p->K, ldb, bk, bnl, CU_TENSOR_MAP_SWIZZLE_128B, et);
       else if (rc == ROLLER_OK)
-        rc = encode_matrix(&p->tmB, b_src, p->K, p->N, ldb, 32, 32,
-                           CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, rnd);
+        rc = encode_matrix(&p->tmB, b_src, p->K, p->N, ldb, bk, bk, swz_mn, et);
     }
     if (rc != ROLLER_OK) return rc;
     p->map_a_ptr = a_src;
@@ -368,7 +418,7 @@ int roller_b200_gemm_run(roller_plan* p, const float* A, const float* B, float* 
   return ROLLER_OK;
 }
 
-int roller_b200_gemm_time(roller_plan* p, const float* A, const float* B, float* C, void* stream,
+int roller_b200_gemm_time(roller_plan* p, const void* A, const void* B, float* C, void* stream,
                           int warmup, int iters, float* ms_per_iter) {
   if (!p || !ms_per_iter || iters <= 0 || warmup < 0) return ROLLER_ERR_INVALID;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -390,13 +440,13 @@ int roller_b200_gemm_time(roller_plan* p, const float* A, const float* B, float*
   return ROLLER_OK;
 }
 
-int roller_b200_gemm_host_async(roller_plan* p, const float* hA, const float* hB, float* hC,
+int roller_b200_gemm_host_async(roller_plan* p, const void* hA, const void* hB, float* hC,
                                 void* stream) {
   if (!p || !hA || !hB || !hC) return ROLLER_ERR_INVALID;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const size_t a_bytes = sizeof(float) * static_cast<size_t>(p->lda) * p->M;
+  const size_t a_bytes = static_cast<size_t>(p->elem) * static_cast<size_t>(p->lda) * p->M;
   const size_t b_bytes =
-      sizeof(float) * static_cast<size_t>(p->ldb) * (p->layout == 1 ? p->N : p->K);
+      static_cast<size_t>(p->elem) * static_cast<size_t>(p->ldb) * (p->layout == 1 ? p->N : p->K);
   const size_t c_bytes = sizeof(float) * static_cast<size_t>(p->ldc) * p->M;
   if (!p->hd_a) {
     cudaError_t e = cudaMalloc(&p->hd_a, a_bytes);
@@ -404,7 +454,8 @@ int roller_b200_gemm_host_async(roller_plan* p, const float* hA, const float* hB
     if (e == cudaSuccess) e = cudaMalloc(&p->hd_c, c_bytes);
     if (e != cudaSuccess) {
       cudaFree(p->hd_a); cudaFree(p->hd_b); cudaFree(p->hd_c);
-      p->hd_a = p->hd_b = p->hd_c = nullptr;
+      p->hd_a = p->hd_b = nullptr;
+      p->hd_c = nullptr;
       cudaGetLastError();
       return ROLLER_ERR_NOMEM;
     }
@@ -419,7 +470,7 @@ int roller_b200_gemm_host_async(roller_plan* p, const float* hA, const float* hB
   return ROLLER_OK;
 }
 
-int roller_b200_gemm_host(roller_plan* p, const float* hA, const float* hB, float* hC, void* stream) {
+int roller_b200_gemm_host(roller_plan* p, const void* hA, const void* hB, float* hC, void* stream) {
   int rc = roller_b200_gemm_host_async(p, hA, hB, hC, stream);
   if (rc != ROLLER_OK) return rc;
   RB_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));

@@ -32,7 +32,7 @@ struct KernelVariant {
   int block_n;    // tile columns
   int rstep;      // k per stage
   int cta_group;  // 1 or 2
-  int mode;       // 1 or 3
+  int mode;       // 1 / 3 (fp32 operands: 1xTF32 / 3xTF32), 16 (bf16), 17 (fp16)
   int layout;     // 0 = A[M,K], B[K,N]; 1 = B given as Bt[N,K]; 2 = skinny (roles swapped)
   int stages;
   int smem_bytes;
@@ -44,6 +44,8 @@ struct KernelVariant {
 
 int variant_count();
 const KernelVariant& variant_at(int idx);
+// The kernels for 16-bit operands (mode 16 = bf16, 17 = fp16), kept in their own table.
+const KernelVariant* variants_16bit(int* n);
 // Returns nullptr when no kernel was compiled for the combination.
 const KernelVariant* find_variant(int block_m, int block_n, int rstep, int cta_group, int mode,
                                   int layout);

@@ -4,6 +4,9 @@
 // (schedule: src/roller.py:93-342, payload linalg.matmul: src/roller.py:47-68). One
 // instantiation exists per rTile the search may emit: block tile (128*CG) x BN, reduce step 32.
 //
+// The same template also serves 16-bit operands (bf16 / fp16 A and B, fp32 C): tcgen05.mma
+// kind::f16, reduce step 64, one MMA per 16 k; everything else below applies unchanged.
+//
 // Arithmetic: tcgen05.mma kind::tf32 with fp32 accumulation in TMEM.
 //   MODE 1 ("1xTF32"): one MMA per k-step. The tensor core reads only the top 19 bits of each
 //          32-bit word (truncation, measured on B200), so the host encodes the tensor maps of
@@ -59,12 +62,13 @@
 
 namespace rb200 {
 
-// One operand tile of ROWS (m or n) x 32 (k) whose global rows run along k.
+// One operand tile of ROWS (m or n) x 128 bytes of k (32 fp32 or 64 16-bit elements) whose
+// global rows run along k.
 template <int ROWS>
 struct OperandK {
   static constexpr int BYTES = ROWS * 128;
   static constexpr uint32_t MAJOR = 0;   // instruction-descriptor major bit: K
-  static constexpr uint64_t KK_STEP = 2; // one MMA (8 k) further: 32 bytes along a row, >> 4
+  static constexpr uint64_t KK_STEP = 2; // one MMA (32 bytes of k) further along a row, >> 4
   template <bool PAIR>
   static __device__ __forceinline__ void load(uint32_t dst, const CUtensorMap* tm, uint32_t bar,
                                               int row0, int k0) {
@@ -77,42 +81,54 @@ struct OperandK {
   }
 };
 
-// One operand tile of ROWS (m or n) x 32 (k) whose global rows run along m/n.
-template <int ROWS>
+// One operand tile of ROWS (m or n) x BK (k) whose global rows run along m/n, for elements of
+// EB bytes. It is staged as boxes of BK rows (one k each) of 128 bytes (32 fp32 or 64 16-bit
+// m/n values).
+template <int ROWS, int EB = 4>
 struct OperandMN {
-  static constexpr int BOXES = ROWS / 32;
-  static constexpr int BOX_BYTES = 32 * 128;
+  static constexpr int BOX_MN = 128 / EB;           // m/n values per box row
+  static constexpr int BOX_K = 128 / EB;            // k rows per box (= the reduce step)
+  static constexpr int BOXES = ROWS / BOX_MN;
+  static constexpr int BOX_BYTES = BOX_K * 128;
   static constexpr int BYTES = BOXES * BOX_BYTES;
   static constexpr uint32_t MAJOR = 1;    // MN
-  static constexpr uint64_t KK_STEP = 64; // one MMA (8 k) further: 8 rows of a box = 1024 B, >> 4
+  // one MMA further: 8 (fp32) or 16 (16-bit) rows of a box = 1024 or 2048 B, >> 4
+  static constexpr uint64_t KK_STEP = (EB == 4) ? 64 : 128;
+  static_assert(ROWS % BOX_MN == 0, "whole boxes");
   template <bool PAIR>
   static __device__ __forceinline__ void load(uint32_t dst, const CUtensorMap* tm, uint32_t bar,
                                               int row0, int k0) {
 #pragma unroll
     for (int j = 0; j < BOXES; ++j) {
-      if constexpr (PAIR) tma_load_2d_pair(dst + j * BOX_BYTES, tm, bar, row0 + j * 32, k0);
-      else tma_load_2d(dst + j * BOX_BYTES, tm, bar, row0 + j * 32, k0);
+      if constexpr (PAIR) tma_load_2d_pair(dst + j * BOX_BYTES, tm, bar, row0 + j * BOX_MN, k0);
+      else tma_load_2d(dst + j * BOX_BYTES, tm, bar, row0 + j * BOX_MN, k0);
     }
   }
-  // rows (one k each) of 128 B = 32 m/n; 4-row swizzle atoms 512 B apart along k, the next 32
-  // m/n one whole box further
+  // fp32: 4-row swizzle atoms (32-byte chunks) 512 B apart along k. 16-bit: the ordinary
+  // 128-byte swizzle, 8-row atoms 1024 B apart along k. Either way the next box_mn values of
+  // m/n are one whole box further.
   static __device__ __forceinline__ uint64_t desc(uint32_t addr) {
-    return make_smem_desc(addr, BOX_BYTES, 512, kLayoutSw128Base32);
+    if constexpr (EB == 4) return make_smem_desc(addr, BOX_BYTES, 512, kLayoutSw128Base32);
+    else return make_smem_desc(addr, BOX_BYTES, 1024, kLayoutSw128);
   }
 };
 
-template <int BN_, int MODE_, int CG_, int LAYOUT_ = 0>
+// DT_: operand element type. 0 = fp32 (tensor-core kind tf32), 1 = bf16, 2 = fp16 (kind f16).
+template <int BN_, int MODE_, int CG_, int LAYOUT_ = 0, int DT_ = 0>
 struct GemmCfg {
   static constexpr int BN = BN_;      // tile columns (of the CTA pair when CG == 2)
-  static constexpr int MODE = MODE_;  // 1 or 3 tensor-core products per fp32 product
+  static constexpr int MODE = MODE_;  // 1 or 3 tensor-core products per operand product
   static constexpr int CG = CG_;      // CTAs cooperating on one tile (tcgen05 cta_group)
   static constexpr int LAYOUT = LAYOUT_;
+  static constexpr int DT = DT_;
+  static constexpr int EB = (DT == 0) ? 4 : 2;  // bytes per operand element
   static constexpr bool TRANSPOSE_C = (LAYOUT == 2);
   static constexpr int BM = 128;      // tile rows held by one CTA
-  static constexpr int BK = 32;       // reduce step: 32 fp32 = one 128-byte swizzle row
+  static constexpr int BK = 128 / EB; // reduce step: one 128-byte swizzle row of k
+  static constexpr int MMA_K = 32 / EB;  // k per tensor-core instruction
   static constexpr int BNL = BN / CG; // B columns staged by one CTA
-  using AOp = typename std::conditional<LAYOUT == 2, OperandMN<BM>, OperandK<BM>>::type;
-  using BOp = typename std::conditional<LAYOUT == 0, OperandMN<BNL>, OperandK<BNL>>::type;
+  using AOp = typename std::conditional<LAYOUT == 2, OperandMN<BM, EB>, OperandK<BM>>::type;
+  using BOp = typename std::conditional<LAYOUT == 0, OperandMN<BNL, EB>, OperandK<BNL>>::type;
   static constexpr int A_BYTES = AOp::BYTES;
   static constexpr int B_BYTES = BOp::BYTES;
   static constexpr int RAW_BYTES = (A_BYTES + B_BYTES + 1023) / 1024 * 1024;
@@ -140,6 +156,7 @@ struct GemmCfg {
   static constexpr int REGS_CTRL = 64, REGS_XFORM = 80, REGS_EPI = 184;
 
   static_assert(BN % (32 * CG) == 0, "each CTA stages whole 32-column boxes of B");
+  static_assert(DT == 0 || MODE == 1, "split precision exists for fp32 operands only");
   static_assert(EPI_COLS % 16 == 0, "epilogue threads read whole 16-column slabs");
   static_assert(TRANSPOSE_C || EPI_COLS % 32 == 0, "row-major C is stored in 32-column pieces");
   static_assert(TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512,
@@ -340,7 +357,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     } else if (warp == 1 && lane == 0 && is_leader) {
       // ---------------------------------------------------------- MMA issuer
       constexpr uint32_t idesc =
-          make_idesc_tf32(Cfg::MMA_M, BN, Cfg::AOp::MAJOR, Cfg::BOp::MAJOR);
+          Cfg::DT == 0 ? make_idesc_tf32(Cfg::MMA_M, BN, Cfg::AOp::MAJOR, Cfg::BOp::MAJOR)
+                       : make_idesc_f16(Cfg::MMA_M, BN, Cfg::AOp::MAJOR, Cfg::BOp::MAJOR,
+                                        Cfg::DT == 1 ? 1u : 0u);
       constexpr uint64_t a_step = Cfg::AOp::KK_STEP, b_step = Cfg::BOp::KK_STEP;
       int s = 0;
       uint32_t ph = 0;
@@ -363,7 +382,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const uint32_t stage = smem_base + s * Cfg::STAGE_BYTES;
             const uint64_t a_raw = Cfg::AOp::desc(stage);
             const uint64_t b_raw = Cfg::BOp::desc(stage + Cfg::A_BYTES);
-            // One MMA consumes 8 k of both operand tiles.
+            // One MMA consumes 32 bytes of k (8 fp32 or 16 16-bit elements) of both tiles.
             if constexpr (Cfg::MODE == 3) {
               const uint64_t a_sml = Cfg::AOp::desc(stage + Cfg::RAW_BYTES);
               const uint64_t b_sml = Cfg::BOp::desc(stage + Cfg::RAW_BYTES + Cfg::A_BYTES);
@@ -378,11 +397,16 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
               for (int kk = 0; kk < BK / 8; ++kk)
                 umma_tf32<CG>(d_tmem, a_raw + kk * a_step, b_raw + kk * b_step, idesc, 1u);
-            } else {
+            } else if constexpr (Cfg::DT == 0) {
 #pragma unroll
               for (int kk = 0; kk < BK / 8; ++kk)
                 umma_tf32<CG>(d_tmem, a_raw + kk * a_step, b_raw + kk * b_step, idesc,
                               (kb != kb0 || kk != 0) ? 1u : 0u);
+            } else {
+#pragma unroll
+              for (int kk = 0; kk < BK / Cfg::MMA_K; ++kk)
+                umma_f16<CG>(d_tmem, a_raw + kk * a_step, b_raw + kk * b_step, idesc,
+                             (kb != kb0 || kk != 0) ? 1u : 0u);
             }
             umma_commit<CG>(empty_bar(s));
             if (++s == STAGES) { s = 0; ph ^= 1u; }

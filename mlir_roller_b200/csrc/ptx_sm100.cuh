@@ -260,6 +260,37 @@ __device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint
   }
 }
 
+// Instruction descriptor for kind::f16 with fp32 accumulation; fmt: 0 = fp16, 1 = bf16 operands.
+__host__ __device__ constexpr uint32_t make_idesc_f16(int mma_m, int mma_n, uint32_t a_major,
+                                                      uint32_t b_major, uint32_t fmt) {
+  return (1u << 4)        // D format: f32
+         | (fmt << 7)     // A format
+         | (fmt << 10)    // B format
+         | (a_major << 15) | (b_major << 16)
+         | (static_cast<uint32_t>(mma_n >> 3) << 17) | (static_cast<uint32_t>(mma_m >> 4) << 24);
+}
+
+// One MMA over 16 k of 16-bit operands.
+template <int kCtaGroup>
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                         uint32_t idesc, uint32_t accumulate) {
+  if constexpr (kCtaGroup == 1) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+
 // Make `bar` track completion of every MMA this thread has issued so far. With a CTA pair
 // the arrival is delivered to the barrier at the same offset in both CTAs.
 template <int kCtaGroup>

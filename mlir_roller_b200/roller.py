@@ -23,7 +23,8 @@ from pathlib import Path
 from typing import Optional
 
 from . import _lib
-from .analyze import MODE_1XTF32, MODE_3XTF32, MatmulConfig, TileDict, get_roller_hints
+from .analyze import (MODE_1XTF32, MODE_3XTF32, MODE_BF16, MODE_F16, MatmulConfig, TileDict,
+                      get_roller_hints)
 from .arch import B200, CUDA  # noqa: F401  (same names importable as from the reference module)
 from .utils import get_block_dims  # noqa: F401
 
@@ -78,7 +79,8 @@ class Compiler:
 
     `pipeline_depth` and `dump_path` are accepted for call compatibility: the pipeline depth is
     fixed per compiled kernel (reported in `launch_info`), and there is no IR to dump.
-    `mode` selects 3xTF32 (default, fp32-level accuracy) or 1xTF32.
+    `mode` selects 3xTF32 (default, fp32-level accuracy) or 1xTF32 for a 32-bit config, bf16
+    (default) or fp16 operands for a 16-bit config (`el_bits=16`; C stays fp32).
     """
 
     def __init__(self, config: MatmulConfig, hint: TileDict, pipeline_depth: int = 2,
@@ -88,15 +90,19 @@ class Compiler:
         self.hint = hint
         self.pipeline_depth = pipeline_depth
         self.dump_path = dump_path
-        self.mode = mode if mode is not None else (getattr(hint, "mode", None) or MODE_3XTF32)
+        self.mode = mode if mode is not None else (
+            getattr(hint, "mode", None) or default_mode(config))
         self.accumulate = accumulate
         self.stream_k = stream_k  # -1 automatic, 0 off, 1 whenever tiles are left over
         self.b_transposed = b_transposed  # B is handed over as Bt[N,K] row-major
 
     def compile(self) -> CompiledGemm:
         _torch()
-        if self.config.el_bits != 32:
-            raise _lib.RollerError(_lib.ERR_UNSUPPORTED, "only fp32 (el_bits=32) kernels exist")
+        if self.config.el_bits not in (32, 16):
+            raise _lib.RollerError(_lib.ERR_UNSUPPORTED, "kernels exist for 32- and 16-bit operands")
+        if (self.config.el_bits == 16) != (self.mode in _lib.MODES_16BIT):
+            raise _lib.RollerError(_lib.ERR_INVALID,
+                                   f"mode {self.mode} does not fit el_bits={self.config.el_bits}")
         tile = kernel_tile_for(self.hint)
         plan = _lib.GemmPlan(tile, self.config.M, self.config.N, self.config.K, mode=self.mode,
                              flags=(_lib.FLAG_ACCUMULATE if self.accumulate else 0)
@@ -104,6 +110,26 @@ class Compiler:
         if self.stream_k != -1:
             plan.set_stream_k(self.stream_k)
         return CompiledGemm(plan, self.hint)
+
+
+def default_mode(config: MatmulConfig) -> int:
+    """3xTF32 for fp32 operands, bf16 for 16-bit operands."""
+    return MODE_BF16 if config.el_bits == 16 else MODE_3XTF32
+
+
+def operand_dtype(mode: int):
+    """torch dtype of A and B for a mode (C is always fp32)."""
+    torch = _torch()
+    return {MODE_BF16: torch.bfloat16, MODE_F16: torch.float16}.get(mode, torch.float32)
+
+
+def _operands(config: MatmulConfig, mode: int):
+    """Random A[M,K], B[K,N] of the mode's element type on the device."""
+    torch = _torch()
+    dt = operand_dtype(mode)
+    dA = torch.rand(config.M, config.K, dtype=torch.float32, device="cuda").to(dt)
+    dB = torch.rand(config.K, config.N, dtype=torch.float32, device="cuda").to(dt)
+    return dA, dB
 
 
 @contextmanager
@@ -134,8 +160,8 @@ def run_eval(cuda_func, pipeline_depth, hint: TileDict, repeat_times: int = 20):
     torch = _torch()
     cfg = hint.matmul_config
     M, N, K = cfg.M, cfg.N, cfg.K
-    dA = torch.rand(M, K, dtype=torch.float32, device="cuda")
-    dB = torch.rand(K, N, dtype=torch.float32, device="cuda")
+    mode = getattr(getattr(cuda_func, "plan", None), "mode", None) or default_mode(cfg)
+    dA, dB = _operands(cfg, mode)
     dC = torch.zeros(M, N, dtype=torch.float32, device="cuda")
 
     grid_dims = (max(N // hint.block_tile[1], 1), max(M // hint.block_tile[0], 1))
@@ -145,7 +171,8 @@ def run_eval(cuda_func, pipeline_depth, hint: TileDict, repeat_times: int = 20):
     args = (dA.data_ptr(), dB.data_ptr(), dC.data_ptr())
 
     cuda_func(grid_dims, block_dims, args, shared_mem=shared_memory_usage)
-    ref = _strict_fp32_matmul(torch, dA, dB)
+    # 16-bit operands: the fp32 product of the same (exactly representable) values
+    ref = _strict_fp32_matmul(torch, dA.float(), dB.float())
     if not torch.allclose(dC, ref, rtol=1e-5, atol=1e-8):
         worst = float((dC - ref).abs().max() / ref.abs().max())
         print(f"result differs from the fp32 library product: max |diff| / max |ref| = {worst:.3e}")
@@ -164,14 +191,16 @@ def run_eval(cuda_func, pipeline_depth, hint: TileDict, repeat_times: int = 20):
     return t_gpu / repeat_times, gflops
 
 
-def run_baseline(config: MatmulConfig, repeat_times: int = 50, allow_tf32: bool = False):
+def run_baseline(config: MatmulConfig, repeat_times: int = 50, allow_tf32: bool = False,
+                 mode: Optional[int] = None):
     """Library GEMM baseline (cuBLAS through torch; the reference uses cuBLAS through CuPy,
-    src/roller.py:589-607): 10 warm-ups, `repeat_times` timed; returns (ms, GFLOPS)."""
+    src/roller.py:589-607): 10 warm-ups, `repeat_times` timed; returns (ms, GFLOPS). A 16-bit
+    config is timed in bf16 (or fp16 with `mode=MODE_F16`), output in the same type."""
     torch = _torch()
     M, N, K = config.M, config.N, config.K
-    dA = torch.rand(M, K, dtype=torch.float32, device="cuda")
-    dB = torch.rand(K, N, dtype=torch.float32, device="cuda")
-    dC = torch.zeros(M, N, dtype=torch.float32, device="cuda")
+    mode = default_mode(config) if mode is None else mode
+    dA, dB = _operands(config, mode)
+    dC = torch.zeros(M, N, dtype=dA.dtype, device="cuda")
     prev = torch.backends.cuda.matmul.allow_tf32
     torch.backends.cuda.matmul.allow_tf32 = allow_tf32
     try:
@@ -229,7 +258,7 @@ class TuneCache:
         tmp.replace(self.path)
 
 
-def best_hint(config: MatmulConfig, arch=None, topk: int = 20, mode: int = MODE_3XTF32,
+def best_hint(config: MatmulConfig, arch=None, topk: int = 20, mode: Optional[int] = None,
               measure: bool = True, cache: Optional[TuneCache] = None):
     """Search, then (like the reference's drivers, src/roller.py:617-633) time every hint and
     keep the fastest. Returns (hint, compiled kernel, ms). With `measure=False` the top-ranked
@@ -237,6 +266,7 @@ def best_hint(config: MatmulConfig, arch=None, topk: int = 20, mode: int = MODE_
     winner is recorded."""
     torch = _torch()
     arch = B200() if arch is None else arch
+    mode = default_mode(config) if mode is None else mode
     hints = get_roller_hints(config, arch, topk=topk, mode=mode) if isinstance(arch, B200) \
         else get_roller_hints(config, arch, topk=topk)
     if cache is not None:
@@ -248,8 +278,7 @@ def best_hint(config: MatmulConfig, arch=None, topk: int = 20, mode: int = MODE_
     if not measure:
         hint = hints[0]
         return hint, Compiler(config, hint, mode=mode).compile(), None
-    dA = torch.rand(config.M, config.K, dtype=torch.float32, device="cuda")
-    dB = torch.rand(config.K, config.N, dtype=torch.float32, device="cuda")
+    dA, dB = _operands(config, mode)
     dC = torch.empty(config.M, config.N, dtype=torch.float32, device="cuda")
     best = None
     for hint in hints:
@@ -277,18 +306,20 @@ def _main(argv=None) -> None:
     import argparse
     ap = argparse.ArgumentParser(description="Roller rTile search -> fp32 GEMM on B200, one shape")
     ap.add_argument("--shape", type=int, nargs=3, default=[4096, 4096, 4096], metavar=("M", "N", "K"))
-    ap.add_argument("--mode", type=int, default=MODE_3XTF32, choices=[MODE_1XTF32, MODE_3XTF32])
+    ap.add_argument("--mode", type=int, default=MODE_3XTF32,
+                    choices=[MODE_1XTF32, MODE_3XTF32, MODE_BF16, MODE_F16],
+                    help="1 = 1xTF32, 3 = 3xTF32 (fp32 operands); 16 = bf16, 17 = fp16 operands")
     ap.add_argument("--topk", type=int, default=20)
     ap.add_argument("--repeat", type=int, default=20)
     ap.add_argument("--no-baseline", action="store_true")
     ap.add_argument("--stream-k", type=int, default=-1, choices=[-1, 0, 1])
     args = ap.parse_args(argv)
     M, N, K = args.shape
-    config = MatmulConfig(M=M, N=N, K=K, el_bits=32)
+    config = MatmulConfig(M=M, N=N, K=K, el_bits=16 if args.mode in _lib.MODES_16BIT else 32)
     pipeline_depth = 2
     hints = get_roller_hints(config, B200(), topk=args.topk, mode=args.mode)
     if not args.no_baseline:
-        run_baseline(config)
+        run_baseline(config, mode=args.mode)
     result_dict = {}
     for hint in hints:
         cuda_func = Compiler(config, hint, pipeline_depth, dump_path=Path("log"),

@@ -120,6 +120,55 @@ def emulate_3xtf32(A: np.ndarray, B: np.ndarray) -> np.ndarray:
     return As @ Bb + Ab @ Bs + Ab @ Bb
 
 
+# ------------------------------------------------------------------ 16-bit operands
+def to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """fp32 -> bf16 bit patterns (uint16), round to nearest even; nan stays nan."""
+    bits = x.astype(np.float32).view(np.uint32)
+    rounded = (bits + np.uint32(0x7FFF) + ((bits >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)
+    nan = np.isnan(x.astype(np.float32))
+    return np.where(nan, np.uint32(0x7FC0), rounded).astype(np.uint16)
+
+
+def from_bf16_bits(b: np.ndarray) -> np.ndarray:
+    """bf16 bit patterns -> the fp32 values they denote (exact)."""
+    return (b.astype(np.uint32) << np.uint32(16)).view(np.float32)
+
+
+def to_f16_bits(x: np.ndarray) -> np.ndarray:
+    """fp32 -> fp16 bit patterns (uint16), round to nearest even (numpy's conversion)."""
+    return x.astype(np.float32).astype(np.float16).view(np.uint16)
+
+
+def from_f16_bits(b: np.ndarray) -> np.ndarray:
+    return b.view(np.float16).astype(np.float32)
+
+
+def make_inputs_16(M: int, N: int, K: int, kind: str, dist: str = "uniform", seed: int = 0):
+    """Seeded operands of `make_inputs`, rounded to bf16 or fp16: returns the bit patterns
+    (uint16, what the device receives) and the fp32 values they denote."""
+    A, B = make_inputs(M, N, K, dist, seed)
+    if kind == "bf16":
+        Ab, Bb = to_bf16_bits(A), to_bf16_bits(B)
+        return Ab, Bb, from_bf16_bits(Ab), from_bf16_bits(Bb)
+    if kind == "f16":
+        Ab, Bb = to_f16_bits(A), to_f16_bits(B)
+        return Ab, Bb, from_f16_bits(Ab), from_f16_bits(Bb)
+    raise ValueError(f"kind must be 'bf16' or 'f16', not {kind!r}")
+
+
+def emulate_16bit(Av: np.ndarray, Bv: np.ndarray, chunk: int = 2048) -> np.ndarray:
+    """Model of the 16-bit kernels' arithmetic on the VALUES of the rounded operands: products
+    of two 16-bit floats are exact in fp32; within a chunk of the reduction the accumulator is
+    modelled as ideal (fp64), each chunk result is rounded to fp32 and the chunk results are
+    added in fp32 with round-to-nearest, as the accumulate warps do."""
+    K = Av.shape[1]
+    out = np.zeros((Av.shape[0], Bv.shape[1]), dtype=np.float32)
+    for k0 in range(0, K, chunk):
+        part = Av[:, k0:k0 + chunk].astype(np.float64) @ Bv[k0:k0 + chunk].astype(np.float64)
+        out = (out + part.astype(np.float32)).astype(np.float32)
+    return out
+
+
 # ------------------------------------------------------------------ plain-C restatement
 _clib = None
 

@@ -5,16 +5,20 @@ import pytest
 from hypothesis import given, settings, strategies as st
 
 from mlir_roller_b200 import analyze, arch
-from mlir_roller_b200.analyze import MODE_1XTF32, MODE_3XTF32, MatmulConfig, get_roller_hints
+from mlir_roller_b200.analyze import (MODE_1XTF32, MODE_3XTF32, MODE_BF16, MODE_F16, MatmulConfig,
+                                      get_roller_hints)
 
 TILES = {(t[0], t[1], t[2]) for t in arch.B200_KERNEL_TILES}
 SKINNY = {(t[0], t[1]) for t in arch.B200_KERNEL_TILES if t[5] == 2}
+TILES_16 = {(t[0], t[1], t[2]) for t in arch.B200_KERNEL_TILES if t[6] > 0}
 
 
 def check_hint(h, M, N, K, mode):
     dev = arch.B200()
-    assert (h.block_tile[0], h.block_tile[1], h.cta_group) in TILES
-    assert h.rstep == 32 and h.mode == mode
+    sixteen = mode in (MODE_BF16, MODE_F16)
+    assert (h.block_tile[0], h.block_tile[1], h.cta_group) in (TILES_16 if sixteen else TILES)
+    assert h.rstep == (64 if sixteen else 32) and h.mode == mode
+    assert h.matmul_config.el_bits == (16 if sixteen else 32)
     skinny = h.layout == 2
     assert skinny == ((h.block_tile[0], h.block_tile[1]) in SKINNY)
     assert h.tmem_cols == 2 * h.block_tile[0 if skinny else 1] <= dev.tmem_columns
@@ -51,9 +55,33 @@ def test_topk_and_dispatch():
     # the generic policy is still what a non-B200 device model gets
     assert get_roller_hints(cfg, arch.CUDA(), topk=1)[0].block_tile == [128, 128]
     with pytest.raises(ValueError):
-        get_roller_hints(MatmulConfig(64, 64, 64, 16), arch.B200())
+        get_roller_hints(MatmulConfig(64, 64, 64, 8), arch.B200())
     with pytest.raises(ValueError):
         analyze.BlackwellPolicy(cfg, arch.B200(), mode=2)
+    with pytest.raises(ValueError):
+        analyze.BlackwellPolicy(cfg, arch.B200(), mode=MODE_BF16)   # fp32 elements, 16-bit mode
+
+
+@pytest.mark.parametrize("mode", [None, MODE_BF16, MODE_F16])
+def test_sixteen_bit_configs(mode):
+    """A 16-bit MatmulConfig (el_bits = 16, src/analyze.py:31) ranks the 16-bit kernels: reduce
+    step 64, same tiles, bf16 unless fp16 is asked for."""
+    shapes = [(2048, 2048, 2048), (8192, 4096, 4096), (4097, 2049, 8193), (16, 8192, 8192), (1, 1, 1)]
+    for M, N, K in shapes:
+        hints = get_roller_hints(MatmulConfig(M, N, K, 16), arch.B200(), topk=20, mode=mode)
+        assert 1 <= len(hints) <= len(TILES_16)
+        assert [h.est_us for h in hints] == sorted(h.est_us for h in hints)
+        for h in hints:
+            check_hint(h, M, N, K, MODE_BF16 if mode is None else mode)
+            assert h.smem_cost == (h.block_tile[0] + h.block_tile[1]) // h.cta_group * 128
+    top = get_roller_hints(MatmulConfig(8192, 8192, 8192, 16), arch.B200(), topk=1)[0]
+    assert (top.block_tile, top.cta_group) == ([256, 256], 2)
+    assert "bf16" in top.kernel
+    skinny = get_roller_hints(MatmulConfig(16, 8192, 8192, 16), arch.B200(), topk=1)[0]
+    assert skinny.layout == 2
+    # a TF32 mode on a 16-bit config falls back to bf16 rather than mixing types
+    assert get_roller_hints(MatmulConfig(512, 512, 512, 16), arch.B200(), topk=1,
+                            mode=MODE_3XTF32)[0].mode == MODE_BF16
 
 
 @settings(max_examples=150, deadline=None)
@@ -69,12 +97,13 @@ def test_any_ragged_shape_gets_valid_hints(M, N, K, mode):
 def test_tile_table_matches_the_library():
     """The table the search ranks is exactly what libroller_b200 was compiled with."""
     from mlir_roller_b200 import _lib
-    lib_tiles = [(k.block_m, k.block_n, k.cta_group, k.stages_1x, k.stages_3x, k.layout)
+    lib_tiles = [(k.block_m, k.block_n, k.cta_group, k.stages_1x, k.stages_3x, k.layout, k.stages_16)
                  for k in _lib.kernel_tiles()]
     assert sorted(lib_tiles) == sorted(arch.B200_KERNEL_TILES)
     for k in _lib.kernel_tiles():
         assert k.rstep == 32 and k.tmem_cols == 2 * (k.block_m if k.layout == 2 else k.block_n)
-        assert max(k.smem_1x, k.smem_3x) <= 227 * 1024
+        assert max(k.smem_1x, k.smem_3x, k.smem_16) <= 227 * 1024
+        assert k.rstep_16 in (0, 64) and (k.rstep_16 == 0) == (k.stages_16 == 0)
         assert isinstance(k, ctypes.Structure)
 
 

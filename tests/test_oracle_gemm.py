@@ -101,3 +101,46 @@ def test_edge_shapes():
     A, B = g.make_inputs(3, 5, 7, "normal", 0)
     assert np.allclose(g.sgemm_ref_c(A, B), A @ B, atol=1e-5)
     assert np.allclose(g.gemm_3xtf32_c(A, B), A @ B, atol=1e-5)
+
+
+# ------------------------------------------------------------------ 16-bit operands
+GOLDEN16 = np.load(Path(__file__).resolve().parent / "golden" / "gemm16_golden.npz")
+CASES16 = sorted({k.split("/")[0] for k in GOLDEN16.files})
+
+
+def _values16(name):
+    conv = g.from_bf16_bits if name.startswith("bf16") else g.from_f16_bits
+    return conv(GOLDEN16[f"{name}/A"]), conv(GOLDEN16[f"{name}/B"])
+
+
+@pytest.mark.parametrize("name", CASES16)
+def test_golden16_is_reproduced_by_the_generator_and_the_model(name):
+    M, N, K, seed = (int(v) for v in GOLDEN16[f"{name}/meta"])
+    kind = "bf16" if name.startswith("bf16") else "f16"
+    dist = {"bf16_uniform": "uniform", "bf16_ragged_normal": "normal", "f16_uniform": "uniform",
+            "f16_ktail_positive": "positive"}[name]
+    Ab, Bb, Av, Bv = g.make_inputs_16(M, N, K, kind, dist, seed)
+    assert np.array_equal(Ab, GOLDEN16[f"{name}/A"]) and np.array_equal(Bb, GOLDEN16[f"{name}/B"])
+    C64 = GOLDEN16[f"{name}/C64"]
+    assert np.array_equal(g.matmul_fp64(Av, Bv), C64)
+    # exact products + fp32 chunk sums: fp32-level error, far below the operands' own rounding
+    assert g.err_norm(g.emulate_16bit(Av, Bv, chunk=64), C64) < 5e-7
+    A32, B32 = g.make_inputs(M, N, K, dist, seed)
+    rounding = g.err_norm(C64, g.matmul_fp64(A32, B32))
+    assert (1e-4 if kind == "f16" else 1e-3) < rounding < (2e-3 if kind == "f16" else 2e-2)
+
+
+def test_bf16_and_f16_conversions():
+    x = np.array([0.0, -0.0, 1.0, 1.0 + 2.0**-8, 1.0 + 3 * 2.0**-8, 3.4028235e38, np.inf, -np.inf,
+                  1e-40, 65504.0, 65520.0, 2.0**-25], dtype=np.float32)
+    b = g.to_bf16_bits(x)
+    # ties go to the even neighbour: 1 + 2^-8 -> 1.0, 1 + 3*2^-8 -> 1 + 2^-6
+    assert list(g.from_bf16_bits(b)[:5]) == [0.0, 0.0, 1.0, 1.0, 1.0 + 2.0**-6]
+    assert np.signbit(g.from_bf16_bits(b)[1])
+    assert g.from_bf16_bits(b)[5] == np.inf            # rounds up past the largest bf16
+    assert g.from_bf16_bits(b)[6] == np.inf and g.from_bf16_bits(b)[7] == -np.inf
+    assert np.isnan(g.from_bf16_bits(g.to_bf16_bits(np.array([np.nan], np.float32)))[0])
+    f = g.from_f16_bits(g.to_f16_bits(x))
+    assert f[9] == 65504.0 and f[10] == np.inf and f[11] == 0.0
+    with pytest.raises(ValueError):
+        g.make_inputs_16(2, 2, 2, "fp8")
