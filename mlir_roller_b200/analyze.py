@@ -141,7 +141,7 @@ class TileDict:
                 f"smem_cost={_natural_size(self.smem_cost)}, block_per_SM={self.block_per_SM}, "
                 f"num_wave={self.num_wave}, grid_size={self.grid_size}")
         if self.cta_group is not None:
-            text += (f", cta_group={self.cta_group}, stages={self.stages}, mode={self.mode}xTF32, "
+            text += (f", cta_group={self.cta_group}, stages={self.stages}, mode={_mode_name(self.mode)}, "
                      f"tmem_cols={self.tmem_cols}, est={self.est_us:.1f} us")
         return text + ")"
 
@@ -315,6 +315,10 @@ MODE_1XTF32 = 1     # fp32 operands, one TF32 product each
 MODE_3XTF32 = 3     # fp32 operands, big/small split: three TF32 products, fp32-level accuracy
 MODE_BF16 = 16      # bf16 operands (el_bits = 16), exact products, fp32 accumulation and C
 MODE_F16 = 17       # fp16 operands (el_bits = 16), likewise
+
+
+def _mode_name(mode) -> str:
+    return {MODE_BF16: "bf16", MODE_F16: "fp16"}.get(mode, f"{mode}xTF32")
 
 
 class BlackwellPolicy:
