@@ -13,6 +13,8 @@ Differences a caller can observe, all deliberate:
   * a hint whose block tile has no compiled kernel raises (the reference can compile any hint);
     the sweep's per-hint try/except (src/benchmark.py:43-58) skips it the same way it skips a
     hint that fails to compile there;
+  * a 16-bit problem (`MatmulConfig(..., el_bits=16)`) binds bf16 (or, with `mode=MODE_F16`,
+    fp16) operands with an fp32 C; the reference's generator emits f32 only (src/roller.py:47-68);
   * there is no CPU fallback: without the shared library or without an sm_100 GPU, `compile()`
     raises.
 """
