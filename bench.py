@@ -375,6 +375,14 @@ def strong_scaling(torch, dist, rank, world, steps, warmup, mode):
             og.destroy()
             del og
             torch.cuda.empty_cache()
+        # the same GEMM, unsharded, on this rank's GPU alone (the strong-scaling numerator)
+        A_full = torch.rand(M, K, device="cuda", generator=g) * 2 - 1
+        C_one = torch.empty(M, N, device="cuda")
+        one = mgpu.ShardedGemm(M, N, K, 0, 1, grid=(1, 1), mode=mode, measure=True)
+        put("single_gpu", timed(lambda: one.run(A_full, B_full, C_one)))
+        one.plan.destroy()
+        del A_full, C_one, one
+        torch.cuda.empty_cache()
         # lower bound of any exchange that ends with C on one rank: its ingress over NVLink
         rec["gather_link_bound_ms"] = (world - 1) / world * M * N * 4 / 770e9 * 1e3
         out.append(rec)
