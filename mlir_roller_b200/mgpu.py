@@ -214,6 +214,31 @@ def push_order(rank: int, world_size: int, dest: str, root: int = 0) -> List[int
     raise ValueError(f"dest must be 'root' or 'all', not {dest!r}")
 
 
+@dataclass(frozen=True)
+class BandStep:
+    """One band of a rank's block in the overlapped exchange: the kernel computes rows
+    [row0, row1) of C, then the band is copied to every rank in `dests`. Offsets are in
+    elements: `a_off` into the rank's A rows, `b_off` into B (the block's first column), `c_off`
+    into the full C (the band's first element; the same in every rank's copy of C)."""
+    row0: int
+    row1: int
+    cols: int
+    a_off: int
+    b_off: int
+    c_off: int
+    dests: Tuple[int, ...]
+
+
+def band_schedule(block: Block, N: int, K: int, bands: int, dests: Sequence[int]) -> List[BandStep]:
+    """The steps of one rank: its block cut by `split_bands`, each band with its operand and
+    output offsets and the ranks it is pushed to."""
+    if block.cols <= 0:
+        return []
+    return [BandStep(r0, r1, block.cols, (r0 - block.row0) * K, block.col0, r0 * N + block.col0,
+                     tuple(dests))
+            for r0, r1 in split_bands(block.row0, block.row1, bands)]
+
+
 class OverlappedGemm:
     """Sharded C = A @ B whose exchange of C runs underneath the computation.
 
@@ -266,8 +291,8 @@ class OverlappedGemm:
         self.comm = [torch.cuda.Stream() for _ in range(max(1, comm_streams))]
         if bands is None:
             bands = default_bands(self.block.rows, self.block.cols)
-        self.bands = (split_bands(self.block.row0, self.block.row1, bands)
-                      if self.block.cols > 0 else [])
+        self.steps = band_schedule(self.block, N, K, bands, self.dests)
+        self.bands = [(st.row0, st.row1) for st in self.steps]
         self.plans, self.tiles, self._events = [], [], []
         by_shape = {}
         for r0, r1 in self.bands:
@@ -287,21 +312,21 @@ class OverlappedGemm:
         contiguous, `B_full` = the whole K x N matrix, contiguous."""
         torch = self._torch
         cs = stream if stream is not None else torch.cuda.current_stream()
-        b, N, K = self.block, self.N, self.K
+        N = self.N
         for st in self.comm:
             st.wait_stream(cs)          # the previous step's consumers are ordered before the pushes
         n = 0
-        for (r0, r1), plan, ev in zip(self.bands, self.plans, self._events):
-            off = (r0 * N + b.col0) * 4
-            plan.run_ptr(A_rows.data_ptr() + (r0 - b.row0) * K * 4, B_full.data_ptr() + b.col0 * 4,
-                         self.C.data_ptr() + off, cs)
+        for step, plan, ev in zip(self.steps, self.plans, self._events):
+            plan.run_ptr(A_rows.data_ptr() + step.a_off * 4, B_full.data_ptr() + step.b_off * 4,
+                         self.C.data_ptr() + step.c_off * 4, cs)
             ev.record(cs)
-            for d in self.dests:
+            for d in step.dests:
                 st = self.comm[n % len(self.comm)]
                 n += 1
                 st.wait_event(ev)
-                self._lib.copy_block_async(self.peer_C[d].data_ptr() + off, N,
-                                           self.C.data_ptr() + off, N, r1 - r0, b.cols, st)
+                self._lib.copy_block_async(self.peer_C[d].data_ptr() + step.c_off * 4, N,
+                                           self.C.data_ptr() + step.c_off * 4, N,
+                                           step.row1 - step.row0, step.cols, st)
 
     def finish(self, stream=None) -> None:
         """Enqueue the closing fence; once `stream` has passed it, every rank's pushes of this

@@ -150,3 +150,34 @@ def test_default_bands():
     assert mgpu.default_bands(4096, 4096) == 2
     assert mgpu.default_bands(1024, 4096) == 2
     assert mgpu.default_bands(512, 1024) == 1
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.integers(1, 1500), st.integers(1, 700), st.integers(1, 300), st.sampled_from([1, 2, 4, 8]),
+       st.integers(1, 5), st.sampled_from(["root", "all"]), st.booleans())
+def test_band_schedule_delivers_every_block(M, N, K, world, bands, dest, two_d):
+    """Replay every rank's schedule on flat host arrays (the 'kernel' writes the band into the
+    rank's own C, each push copies it to the destination's C at the same offset): afterwards
+    rank 0 -- or every rank -- holds the whole matrix, and no step reads outside its operands."""
+    grid = (world // 2, 2) if (two_d and world % 2 == 0) else (world, 1)
+    blocks = mgpu.partition(M, N, grid[0], grid[1], align_m=256)
+    truth = np.arange(M * N, dtype=np.float64).reshape(M, N)
+    Cs = [np.full(M * N, -1.0) for _ in range(world)]
+    for r, b in enumerate(blocks):
+        steps = mgpu.band_schedule(b, N, K, bands, mgpu.push_order(r, world, dest))
+        assert len(steps) <= bands
+        assert sum(s.row1 - s.row0 for s in steps) == (b.rows if b.cols else 0)
+        for s in steps:
+            rows = s.row1 - s.row0
+            assert 0 <= s.a_off and s.a_off + rows * K <= max(b.rows, 1) * K   # inside A[rows of block]
+            assert s.b_off == b.col0 and s.b_off + s.cols <= N
+            assert s.c_off == s.row0 * N + b.col0
+            for i in range(rows):       # the band, row by row, with leading dimension N
+                lo = s.c_off + i * N
+                Cs[r][lo:lo + s.cols] = truth[s.row0 + i, b.col0:b.col0 + s.cols]
+                for d in s.dests:
+                    assert d != r
+                    Cs[d][lo:lo + s.cols] = Cs[r][lo:lo + s.cols]
+    holders = range(world) if dest == "all" else [0]
+    for r in holders:
+        assert np.array_equal(Cs[r].reshape(M, N), truth)
