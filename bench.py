@@ -255,6 +255,21 @@ class LibraryCase:
         self.torch.matmul(self.A, self.B, out=self.C)
 
 
+class SixteenBitOutCase:
+    """A bf16 ShapeCase's kernel bound again with C in bf16 (what the library GEMM writes)."""
+
+    def __init__(self, torch, case):
+        from mlir_roller_b200 import _lib, roller
+        m, n, k = case.shape
+        self.C = torch.empty(m, n, dtype=case.A.dtype, device="cuda")
+        self.plan = _lib.GemmPlan(roller.kernel_tile_for(case.hint), m, n, k, mode=case.mode,
+                                  flags=_lib.FLAG_C_16BIT)
+        self.ptrs = (case.A.data_ptr(), case.B.data_ptr(), self.C.data_ptr())
+
+    def launch(self):
+        self.plan.run_ptr(*self.ptrs)
+
+
 def timed_sweep(torch, cases, steps, warmup, dist=None):
     """Returns (ms per step, per-shape mean ms). Barrier + synchronize on both sides."""
     for _ in range(warmup):
@@ -442,8 +457,13 @@ def run_gpu_arm(args) -> None:
     step_ms16, per_shape_ms16 = timed_sweep(torch, cases16, max(args.steps // 2, 1), 2, None)
     lib16 = [LibraryCase(torch, c) for c in cases16]
     step_ms16_lib, _ = timed_sweep(torch, lib16, max(args.steps // 2, 1), 2, None)
+    out16 = [SixteenBitOutCase(torch, c) for c in cases16]
+    step_ms16_out, _ = timed_sweep(torch, out16, max(args.steps // 2, 1), 2, None)
+    for c in out16:
+        c.plan.check_status()
+        c.plan.destroy()
     tiles16 = [(c.hint.block_tile, c.hint.cta_group) for c in cases16]
-    del cases16, lib16
+    del cases16, lib16, out16
     torch.cuda.empty_cache()
 
     e2e_ms, h2d, d2h, _ = e2e_sweep(torch, cases, max(args.steps // 2, 1))
@@ -540,7 +560,8 @@ def run_gpu_arm(args) -> None:
         # the same sweep with bf16 operands (fp32 accumulate and C); rank 0's own GPU only
         "bf16": {
             "value": sweep_flops() / step_ms16 / 1e9, "unit": UNIT, "ms_per_step": step_ms16,
-            "library_bf16_value": sweep_flops() / step_ms16_lib / 1e9,
+            "value_bf16_out": sweep_flops() / step_ms16_out / 1e9,   # same kernels, C in bf16
+            "library_bf16_value": sweep_flops() / step_ms16_lib / 1e9,   # bf16 C
             "peak": peaks.get("bf16_tflops_sustained"),
             "frac": (sweep_flops() / step_ms16 / 1e9 / peaks["bf16_tflops_sustained"]
                      if "bf16_tflops_sustained" in peaks else None),

@@ -54,6 +54,11 @@ typedef enum roller_status {
                                       and its tutorial kernels pre-transpose B
                                       (src/cuda_matmul_opt.py:280-281,376-392) */
 
+#define ROLLER_FLAG_C_16BIT 4 /* 16-bit modes only: C (and ldc) are in the operand type as well, as
+                                 the reference's MatmulConfig implies for its output tensor
+                                 (one el_bits for A, B and C, src/analyze.py:31-49); sums are
+                                 kept in fp32 and rounded to nearest even once, on the store */
+
 /* Device facts feeding the B200 device model of the search (reference: the constants hard-coded
  * in arch.CUDA, src/arch.py:47-61). */
 typedef struct roller_dev_info {
@@ -112,26 +117,26 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
 
 /* Replaces cuda_func(grid, block, (A, B, C), shared_mem=...) (src/roller.py:545-550): enqueue one
  * GEMM on `stream`. No allocation, no synchronisation. A and B point to elements of the type
- * the plan's mode names; C is always fp32. */
-int roller_b200_gemm_run(roller_plan* plan, const void* A, const void* B, float* C, void* stream);
+ * the plan's mode names; C is fp32 unless the plan was made with ROLLER_FLAG_C_16BIT. */
+int roller_b200_gemm_run(roller_plan* plan, const void* A, const void* B, void* C, void* stream);
 
 /* Replaces the timed loop of run_eval (src/roller.py:564-584): `warmup` untimed launches, then
  * `iters` launches between two CUDA events on `stream`; *ms_per_iter is the mean. Blocks. */
-int roller_b200_gemm_time(roller_plan* plan, const void* A, const void* B, float* C, void* stream,
+int roller_b200_gemm_time(roller_plan* plan, const void* A, const void* B, void* C, void* stream,
                           int warmup, int iters, float* ms_per_iter);
 
 /* Host-buffer form of the whole run_eval data path -- allocate/upload operands, launch, read C
  * back (src/roller.py:532-550) -- used for end-to-end timing: copies A and B from host memory into
  * plan-owned device buffers, runs the GEMM and copies C back, all on `stream`; blocks until C
  * has arrived. The device buffers are allocated on the first call and kept. */
-int roller_b200_gemm_host(roller_plan* plan, const void* hA, const void* hB, float* hC,
+int roller_b200_gemm_host(roller_plan* plan, const void* hA, const void* hB, void* hC,
                           void* stream);
 
 /* Same data path as roller_b200_gemm_host (src/roller.py:532-550) without the final wait: the
  * copies and the launch are only enqueued on `stream`, so GEMMs on different streams overlap
  * their uploads, kernels and readbacks. Host buffers should be pinned; hC is valid once `stream`
  * has been synchronised. */
-int roller_b200_gemm_host_async(roller_plan* plan, const void* hA, const void* hB, float* hC,
+int roller_b200_gemm_host_async(roller_plan* plan, const void* hA, const void* hB, void* hC,
                                 void* stream);
 
 /* Copies a rows x cols block of fp32 between two device matrices (leading dimensions in

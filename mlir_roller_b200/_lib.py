@@ -17,6 +17,7 @@ MODE_F16 = 17       # fp16 A and B, fp32 accumulation and C
 MODES_16BIT = (MODE_BF16, MODE_F16)
 FLAG_ACCUMULATE = 1
 FLAG_B_TRANSPOSED = 2
+FLAG_C_16BIT = 4    # 16-bit modes only: C is written in the operand type instead of fp32
 LAYOUT_GENERAL = 0
 LAYOUT_SKINNY = 2
 
@@ -192,6 +193,7 @@ class GemmPlan:
         self._h = C.c_void_p()
         self.tile = tile
         self.M, self.N, self.K, self.mode = M, N, K, mode
+        self.flags = flags
         self.lda = K if lda is None else lda
         self.ldb = (K if flags & FLAG_B_TRANSPOSED else N) if ldb is None else ldb
         self.ldc = N if ldc is None else ldc
@@ -205,11 +207,12 @@ class GemmPlan:
               "roller_b200_gemm_run")
 
     def _check_dtypes(self, A, B, Cout) -> None:
-        """A and B must hold the element type the plan's mode names, C fp32 (the C side only
-        sees pointers)."""
+        """A and B must hold the element type the plan's mode names, C fp32 -- or that type too
+        for a plan made with FLAG_C_16BIT (the C side only sees pointers)."""
         import torch
         want = {MODE_BF16: torch.bfloat16, MODE_F16: torch.float16}.get(self.mode, torch.float32)
-        for name, t, dt in (("A", A, want), ("B", B, want), ("C", Cout, torch.float32)):
+        c_want = want if self.flags & FLAG_C_16BIT else torch.float32
+        for name, t, dt in (("A", A, want), ("B", B, want), ("C", Cout, c_want)):
             if getattr(t, "dtype", dt) != dt:
                 raise TypeError(f"{name} is {t.dtype}, this plan (mode {self.mode}) needs {dt}")
 

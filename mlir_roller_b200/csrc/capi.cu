@@ -127,6 +127,7 @@ struct roller_plan {
   long long lda, ldb, ldc;
   int mode, flags;
   int elem;               // bytes per element of A and B
+  int c_elem;             // bytes per element of C
   int layout;             // 0 plain, 1 B given transposed, 2 skinny (roles swapped)
   int tiles_m, tiles_n, grid;
   int chunk_kb;           // accumulation chunk, in k-blocks (one reduce step each)
@@ -149,8 +150,7 @@ struct roller_plan {
   const void* map_b_ptr;
   CUtensorMap tmA, tmB;
   // host-buffer path
-  void *hd_a, *hd_b;
-  float* hd_c;
+  void *hd_a, *hd_b, *hd_c;
   cudaEvent_t ev0, ev1;
 };
 
@@ -229,7 +229,8 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
                             int mode, int flags, roller_plan** out) {
   if (!tile || !out) return ROLLER_ERR_INVALID;
   *out = nullptr;
-  if (flags & ~(ROLLER_FLAG_ACCUMULATE | ROLLER_FLAG_B_TRANSPOSED)) return ROLLER_ERR_INVALID;
+  if (flags & ~(ROLLER_FLAG_ACCUMULATE | ROLLER_FLAG_B_TRANSPOSED | ROLLER_FLAG_C_16BIT))
+    return ROLLER_ERR_INVALID;
   const bool b_transposed = (flags & ROLLER_FLAG_B_TRANSPOSED) != 0;
   if (M <= 0 || N <= 0 || K <= 0 || lda < K || ldb < (b_transposed ? K : N) || ldc < N)
     return ROLLER_ERR_INVALID;
@@ -237,6 +238,7 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
       mode != ROLLER_MODE_F16)
     return ROLLER_ERR_INVALID;
   const int elem = elem_bytes_of_mode(mode);
+  if ((flags & ROLLER_FLAG_C_16BIT) && elem != 2) return ROLLER_ERR_INVALID;
   if (tile->layout != 0 && tile->layout != 2) return ROLLER_ERR_INVALID;
   if (b_transposed && tile->layout != 0) return ROLLER_ERR_UNSUPPORTED;
   const int layout = b_transposed ? 1 : tile->layout;
@@ -262,6 +264,7 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
   p->lda = lda; p->ldb = ldb; p->ldc = ldc;
   p->mode = mode;
   p->elem = elem;
+  p->c_elem = (flags & ROLLER_FLAG_C_16BIT) ? 2 : 4;
   p->flags = flags;
   p->layout = layout;
   if (layout == 2) {
@@ -338,7 +341,7 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
   return ROLLER_OK;
 }
 
-int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, float* C, void* stream) {
+int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, void* C, void* stream) {
   if (!p || !A || !B || !C) return ROLLER_ERR_INVALID;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const KernelVariant* kv = p->kv;
@@ -399,7 +402,7 @@ int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, float* C,
   GemmArgs args;
   args.tmA = p->tmA;
   args.tmB = p->tmB;
-  args.C = C;
+  args.C = static_cast<float*>(C);
   args.M = (p->layout == 2) ? p->N : p->M;
   args.N = (p->layout == 2) ? p->M : p->N;
   args.K = p->K;
@@ -408,7 +411,9 @@ int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, float* C,
   args.tiles_n = p->tiles_n;
   args.chunk_kb = p->chunk_kb;
   args.flags = (p->flags & ROLLER_FLAG_ACCUMULATE) ? kFlagAccumulate : 0;
-  if ((p->ldc % 4) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) args.flags |= kFlagVecStore;
+  if ((p->ldc * p->c_elem % 16) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0)
+    args.flags |= kFlagVecStore;
+  if (p->c_elem == 2) args.flags |= kFlagC16;
   args.status = p->status;
   args.sk_tiles = p->sk_tiles;
   args.sk_ws = p->sk_ws;
@@ -418,7 +423,7 @@ int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, float* C,
   return ROLLER_OK;
 }
 
-int roller_b200_gemm_time(roller_plan* p, const void* A, const void* B, float* C, void* stream,
+int roller_b200_gemm_time(roller_plan* p, const void* A, const void* B, void* C, void* stream,
                           int warmup, int iters, float* ms_per_iter) {
   if (!p || !ms_per_iter || iters <= 0 || warmup < 0) return ROLLER_ERR_INVALID;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -440,22 +445,21 @@ int roller_b200_gemm_time(roller_plan* p, const void* A, const void* B, float* C
   return ROLLER_OK;
 }
 
-int roller_b200_gemm_host_async(roller_plan* p, const void* hA, const void* hB, float* hC,
+int roller_b200_gemm_host_async(roller_plan* p, const void* hA, const void* hB, void* hC,
                                 void* stream) {
   if (!p || !hA || !hB || !hC) return ROLLER_ERR_INVALID;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t a_bytes = static_cast<size_t>(p->elem) * static_cast<size_t>(p->lda) * p->M;
   const size_t b_bytes =
       static_cast<size_t>(p->elem) * static_cast<size_t>(p->ldb) * (p->layout == 1 ? p->N : p->K);
-  const size_t c_bytes = sizeof(float) * static_cast<size_t>(p->ldc) * p->M;
+  const size_t c_bytes = static_cast<size_t>(p->c_elem) * static_cast<size_t>(p->ldc) * p->M;
   if (!p->hd_a) {
     cudaError_t e = cudaMalloc(&p->hd_a, a_bytes);
     if (e == cudaSuccess) e = cudaMalloc(&p->hd_b, b_bytes);
     if (e == cudaSuccess) e = cudaMalloc(&p->hd_c, c_bytes);
     if (e != cudaSuccess) {
       cudaFree(p->hd_a); cudaFree(p->hd_b); cudaFree(p->hd_c);
-      p->hd_a = p->hd_b = nullptr;
-      p->hd_c = nullptr;
+      p->hd_a = p->hd_b = p->hd_c = nullptr;
       cudaGetLastError();
       return ROLLER_ERR_NOMEM;
     }
@@ -470,7 +474,7 @@ int roller_b200_gemm_host_async(roller_plan* p, const void* hA, const void* hB, 
   return ROLLER_OK;
 }
 
-int roller_b200_gemm_host(roller_plan* p, const void* hA, const void* hB, float* hC, void* stream) {
+int roller_b200_gemm_host(roller_plan* p, const void* hA, const void* hB, void* hC, void* stream) {
   int rc = roller_b200_gemm_host_async(p, hA, hB, hC, stream);
   if (rc != ROLLER_OK) return rc;
   RB_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));

@@ -10,6 +10,7 @@ namespace rb200 {
 // Kernel flag bits (GemmArgs::flags).
 constexpr int kFlagAccumulate = 1;  // C += A@B instead of C = A@B
 constexpr int kFlagVecStore = 2;    // C rows are 16-byte aligned: use 128-bit stores
+constexpr int kFlagC16 = 4;         // 16-bit kernels only: C holds elements of the operand type
 
 struct GemmArgs {
   CUtensorMap tmA;

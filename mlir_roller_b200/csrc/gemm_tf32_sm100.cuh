@@ -55,6 +55,9 @@
 // like every other wait in the kernel.
 #pragma once
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 #include <type_traits>
 
 #include "gemm_launch.h"
@@ -188,6 +191,22 @@ __device__ __forceinline__ uint32_t split_small(uint32_t xb) {
   // Three instructions per element: the split warps sit on the critical path of the narrower
   // tiles. An infinite x gives inf - inf = nan here, so infinities surface as nan in 3xTF32.
   return __float_as_uint(x - big) + 0x1000u;
+}
+
+// fp32 <-> the 16-bit operand type of a kernel (DT 1 = bf16, 2 = fp16), round to nearest even.
+template <int DT>
+__device__ __forceinline__ uint32_t to_16bit(float x) {
+  if constexpr (DT == 1) return __bfloat16_as_ushort(__float2bfloat16_rn(x));
+  else return __half_as_ushort(__float2half_rn(x));
+}
+template <int DT>
+__device__ __forceinline__ float from_16bit(uint32_t b) {
+  if constexpr (DT == 1) return __uint_as_float(b << 16);
+  else return __half2float(__ushort_as_half(static_cast<unsigned short>(b)));
+}
+template <int DT>
+__device__ __forceinline__ uint32_t pack_16bit(float lo, float hi) {
+  return to_16bit<DT>(lo) | (to_16bit<DT>(hi) << 16);
 }
 
 template <int N>
@@ -426,6 +445,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int et = static_cast<int>(threadIdx.x) - Cfg::FIRST_EPI_WARP * 32;  // 0..255
     const bool accumulate = (flags & kFlagAccumulate) != 0;
     const bool vec_store = (flags & kFlagVecStore) != 0;
+    // 16-bit kernels can also write C in their operand type (C then points to 16-bit elements)
+    const bool c16 = Cfg::DT != 0 && (flags & kFlagC16) != 0;
     // Stream-K scratch: one slot of 128 x BN floats per CTA; thread `et` owns every 256th float4.
     constexpr size_t kSlotFloats = static_cast<size_t>(Cfg::BM) * BN;
     int acc = 0;
@@ -517,10 +538,59 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int j = 0; j < COLS; ++j) {
             const int col = n0 + j;
             if (col < N) {
-              float* dst = C + static_cast<size_t>(col) * static_cast<size_t>(ldc) + row;
+              const size_t at = static_cast<size_t>(col) * static_cast<size_t>(ldc) + row;
               float o = sum[j];
+              if constexpr (Cfg::DT != 0) {
+                if (c16) {
+                  unsigned short* dst = reinterpret_cast<unsigned short*>(C) + at;
+                  if (accumulate) o += from_16bit<Cfg::DT>(*dst);
+                  *dst = static_cast<unsigned short>(to_16bit<Cfg::DT>(o));
+                  continue;
+                }
+              }
+              float* dst = C + at;
               if (accumulate) o += *dst;
               *dst = o;
+            }
+          }
+        }
+      } else if (row < M && c16) {
+        if constexpr (Cfg::DT != 0) {
+          unsigned short* crow =
+              reinterpret_cast<unsigned short*>(C) + static_cast<size_t>(row) * static_cast<size_t>(ldc);
+#pragma unroll
+          for (int c = 0; c < COLS / 32; ++c) {
+            const int col0 = n0 + c * 32;
+            if (col0 >= N) break;
+            unsigned short* dst = crow + col0;
+            if (vec_store && col0 + 32 <= N) {
+              uint4* dst4 = reinterpret_cast<uint4*>(dst);   // 8 elements per 128-bit store
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = sum[c * 32 + 8 * j + e];
+                if (accumulate) {
+                  const uint4 old = dst4[j];
+                  const uint32_t w[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    v[2 * e] += from_16bit<Cfg::DT>(w[e] & 0xFFFFu);
+                    v[2 * e + 1] += from_16bit<Cfg::DT>(w[e] >> 16);
+                  }
+                }
+                dst4[j] = make_uint4(pack_16bit<Cfg::DT>(v[0], v[1]), pack_16bit<Cfg::DT>(v[2], v[3]),
+                                     pack_16bit<Cfg::DT>(v[4], v[5]), pack_16bit<Cfg::DT>(v[6], v[7]));
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (col0 + j < N) {
+                  float o = sum[c * 32 + j];
+                  if (accumulate) o += from_16bit<Cfg::DT>(dst[j]);
+                  dst[j] = static_cast<unsigned short>(to_16bit<Cfg::DT>(o));
+                }
+              }
             }
           }
         }

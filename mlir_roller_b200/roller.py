@@ -82,12 +82,14 @@ class Compiler:
     `pipeline_depth` and `dump_path` are accepted for call compatibility: the pipeline depth is
     fixed per compiled kernel (reported in `launch_info`), and there is no IR to dump.
     `mode` selects 3xTF32 (default, fp32-level accuracy) or 1xTF32 for a 32-bit config, bf16
-    (default) or fp16 operands for a 16-bit config (`el_bits=16`; C stays fp32).
+    (default) or fp16 operands for a 16-bit config (`el_bits=16`); its C is fp32 unless
+    `out_16bit=True` asks for the operand type there too.
     """
 
     def __init__(self, config: MatmulConfig, hint: TileDict, pipeline_depth: int = 2,
                  dump_path: Optional[Path] = None, mode: Optional[int] = None,
-                 accumulate: bool = False, stream_k: int = -1, b_transposed: bool = False):
+                 accumulate: bool = False, stream_k: int = -1, b_transposed: bool = False,
+                 out_16bit: bool = False):
         self.config = config
         self.hint = hint
         self.pipeline_depth = pipeline_depth
@@ -97,6 +99,7 @@ class Compiler:
         self.accumulate = accumulate
         self.stream_k = stream_k  # -1 automatic, 0 off, 1 whenever tiles are left over
         self.b_transposed = b_transposed  # B is handed over as Bt[N,K] row-major
+        self.out_16bit = out_16bit        # 16-bit config: write C in the operand type, not fp32
 
     def compile(self) -> CompiledGemm:
         _torch()
@@ -108,7 +111,8 @@ class Compiler:
         tile = kernel_tile_for(self.hint)
         plan = _lib.GemmPlan(tile, self.config.M, self.config.N, self.config.K, mode=self.mode,
                              flags=(_lib.FLAG_ACCUMULATE if self.accumulate else 0)
-                             | (_lib.FLAG_B_TRANSPOSED if self.b_transposed else 0))
+                             | (_lib.FLAG_B_TRANSPOSED if self.b_transposed else 0)
+                             | (_lib.FLAG_C_16BIT if self.out_16bit else 0))
         if self.stream_k != -1:
             plan.set_stream_k(self.stream_k)
         return CompiledGemm(plan, self.hint)

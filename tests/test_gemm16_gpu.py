@@ -204,3 +204,55 @@ def test_compiler_run_eval_and_baseline_for_a_16_bit_config(capsys):
     assert "differs" not in capsys.readouterr().out
     with pytest.raises(_lib.RollerError):
         roller.Compiler(cfg, hint, mode=3).compile()
+
+
+@pytest.mark.parametrize("kind", ["bf16", "f16"])
+@pytest.mark.parametrize("tile", [(256, 256, 2), (128, 128, 1), (128, 64, 1), (32, 128, 1, 2)])
+def test_c_in_the_operand_type(kind, tile):
+    """FLAG_C_16BIT: the fp32 sums are rounded to nearest even once, on the store -- the result
+    equals the fp32-C result converted by torch, bit for bit; ragged shapes, padded and odd
+    leading dimensions and C += A@B included."""
+    mode, dt = KINDS[kind]
+    for (M, N, K, ldc) in ((300, 200, 136, 200), (256, 512, 192, 520), (70, 131, 64, 131)):
+        Ab, Bb, _, _ = g.make_inputs_16(M, N, K, kind, "normal", seed=M)
+        dA, dB = to_device(Ab, kind), to_device(Bb, kind)
+        C32 = torch.empty(M, N, device="cuda")
+        p32 = _lib.GemmPlan(_lib.find_tile(*tile), M, N, K, mode=mode)
+        p32.run(dA, dB, C32)
+        C16 = torch.full((M, ldc), 7.0, device="cuda", dtype=dt)
+        p16 = _lib.GemmPlan(_lib.find_tile(*tile), M, N, K, ldc=ldc, mode=mode, flags=_lib.FLAG_C_16BIT)
+        p16.run(dA, dB, C16)
+        torch.cuda.synchronize()
+        p16.check_status()
+        assert torch.equal(C16[:, :N], C32.to(dt))
+        assert (C16[:, N:] == 7.0).all()            # pad columns untouched
+        # accumulate: old C is read in the 16-bit type, the sum is rounded once
+        C0 = torch.randn(M, ldc, device="cuda").to(dt)
+        Cacc = C0.clone()
+        pacc = _lib.GemmPlan(_lib.find_tile(*tile), M, N, K, ldc=ldc, mode=mode,
+                             flags=_lib.FLAG_C_16BIT | _lib.FLAG_ACCUMULATE)
+        pacc.set_stream_k(0)
+        p32.set_stream_k(0)
+        p32.run(dA, dB, C32)
+        pacc.run(dA, dB, Cacc)
+        torch.cuda.synchronize()
+        assert torch.equal(Cacc[:, :N], (C32 + C0[:, :N].float()).to(dt))
+        with pytest.raises(TypeError):
+            p16.run(dA, dB, C32)
+        for p in (p32, p16, pacc):
+            p.destroy()
+    with pytest.raises(_lib.RollerError):           # fp32 operands have no 16-bit C
+        _lib.GemmPlan(_lib.find_tile(128, 128, 1), 64, 64, 64, mode=3, flags=_lib.FLAG_C_16BIT)
+
+
+def test_compiler_out_16bit():
+    cfg = MatmulConfig(512, 768, 256, 16)
+    hint = roller.get_roller_hints(cfg, roller.B200(), topk=1)[0]
+    fn = roller.Compiler(cfg, hint, out_16bit=True).compile()
+    A = torch.randn(512, 256, device="cuda").to(torch.bfloat16)
+    B = torch.randn(256, 768, device="cuda").to(torch.bfloat16)
+    C = torch.empty(512, 768, device="cuda", dtype=torch.bfloat16)
+    fn.plan.run(A, B, C)
+    torch.cuda.synchronize()
+    ref = (A.double() @ B.double())
+    assert float((C.double() - ref).abs().max() / ref.abs().max()) < 8e-3   # bf16 output rounding
