@@ -31,7 +31,7 @@ typedef enum roller_status {
   ROLLER_ERR_INVALID = -1,     /* bad argument (null pointer, non-positive size, bad stride) */
   ROLLER_ERR_UNSUPPORTED = -2, /* no compiled kernel for the requested rTile / mode */
   ROLLER_ERR_CUDA = -3,        /* a CUDA runtime/driver call failed; see roller_b200_last_cuda_error */
-  ROLLER_ERR_DEVICE = -4,      /* the current device is not an sm_100 part */
+  ROLLER_ERR_DEVICE = -4,      /* the current device is not an sm_100 part, or not the plan's device */
   ROLLER_ERR_TIMEOUT = -5,     /* a bounded device-side wait ran out; see roller_b200_last_status */
   ROLLER_ERR_NOMEM = -6,       /* workspace allocation failed */
   ROLLER_ERR_TOO_LARGE = -7    /* problem exceeds a fixed capacity of the entry point */

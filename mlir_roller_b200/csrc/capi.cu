@@ -343,6 +343,9 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
 
 int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, void* C, void* stream) {
   if (!p || !A || !B || !C) return ROLLER_ERR_INVALID;
+  // a plan's workspaces, tensor maps and status word live on the device it was created on
+  int cur = -1;
+  if (cudaGetDevice(&cur) != cudaSuccess || cur != p->device) return ROLLER_ERR_DEVICE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const KernelVariant* kv = p->kv;
 
@@ -569,7 +572,7 @@ const char* roller_b200_strerror(int status) {
     case ROLLER_ERR_INVALID: return "invalid argument";
     case ROLLER_ERR_UNSUPPORTED: return "no compiled kernel for this rTile and mode";
     case ROLLER_ERR_CUDA: return "CUDA call failed";
-    case ROLLER_ERR_DEVICE: return "current device is not an sm_100 GPU with enough shared memory";
+    case ROLLER_ERR_DEVICE: return "current device is not an sm_100 GPU with enough shared memory, or not the device the plan was created on";
     case ROLLER_ERR_TIMEOUT: return "a bounded device-side wait ran out";
     case ROLLER_ERR_NOMEM: return "device memory allocation failed";
     case ROLLER_ERR_TOO_LARGE: return "problem exceeds the capacity of this entry point";
