@@ -183,7 +183,14 @@ def run_eval(cuda_func, pipeline_depth, hint: TileDict, repeat_times: int = 20):
         worst = float((dC - ref).abs().max() / ref.abs().max())
         print(f"result differs from the fp32 library product: max |diff| / max |ref| = {worst:.3e}")
 
-    for _ in range(10):
+    # one launch inside an NVTX range named "roller", as the reference marks it for profilers
+    # (src/roller.py:556)
+    torch.cuda.nvtx.range_push("roller")
+    try:
+        cuda_func(grid_dims, block_dims, args, shared_mem=shared_memory_usage)
+    finally:
+        torch.cuda.nvtx.range_pop()
+    for _ in range(9):
         cuda_func(grid_dims, block_dims, args, shared_mem=shared_memory_usage)
     with time_cuda() as (start_gpu, end_gpu):
         for _ in range(repeat_times):
