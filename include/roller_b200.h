@@ -10,11 +10,14 @@
  * Conventions
  *   - every function returns 0 (ROLLER_OK) or a negative roller_status; nothing throws, aborts
  *     or exits across this boundary;
- *   - A is M x K, B is K x N, C is M x N, all row-major fp32 in device memory owned by the
- *     caller; lda/ldb/ldc are row strides in elements;
+ *   - A is M x K, B is K x N, C is M x N, all row-major in device memory owned by the caller
+ *     (fp32, or 16-bit floats in the 16-bit modes); lda/ldb/ldc are row strides in elements;
  *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream); *_run only
  *     enqueues work;
- *   - a plan is bound to the device that was current at create time and is not thread-safe.
+ *   - a plan is bound to the device that was current at create time and is not thread-safe;
+ *     launches of one plan must also be ordered on the device (same stream, or streams ordered
+ *     by events): a plan owns one staging area, one stream-K scratch area and one status word.
+ *     Use one plan per stream to overlap GEMMs.
  */
 #ifndef ROLLER_B200_H_
 #define ROLLER_B200_H_
