@@ -313,6 +313,51 @@ def best_hint(config: MatmulConfig, arch=None, topk: int = 20, mode: Optional[in
     return best
 
 
+def calibrate(arch: Optional[B200] = None, modes=(MODE_1XTF32, MODE_3XTF32, MODE_BF16),
+              k_short: int = 2048, k_long: int = 8192, iters: int = 10) -> B200:
+    """Measure the steady-state cost of one k-block for every compiled rTile on the current
+    device and write it into the device model (`kblock_us`, `kblock_us_16`), so that the
+    search ranks with this GPU's own figures instead of the table shipped in `arch`.
+
+    Per tile and mode two GEMMs are timed that differ only in K; their difference divided by
+    the extra k-blocks each worker runs is the per-k-block time, free of launch, fill and
+    epilogue cost. The problem is sized so that the tiles fill every wave exactly (M = 128 x
+    the SM count for the general tiles, N likewise for the skinny ones), so no schedule effect
+    enters. Returns `arch` (a fresh `B200.from_device()` when none is given)."""
+    torch = _torch()
+    arch = B200.from_device(torch.cuda.current_device()) if arch is None else arch
+    sms = arch.compute_max_core
+    for (bm, bn, cg, _s1, _s3, layout, s16) in arch.kernel_tiles:
+        key = (bm, bn, cg) if layout == 0 else (bm, bn, cg, layout)
+        M, N = (128 * sms, 512) if layout == 0 else (bm, 128 * sms)
+        tile = _lib.find_tile(bm, bn, cg, layout)
+        waves = (-(-M // bm) * -(-N // bn)) / (sms // cg)
+        fp32 = list(arch.kblock_us.get(key, (0.0, 0.0)))
+        for mode in modes:
+            if mode in _lib.MODES_16BIT and s16 == 0:
+                continue
+            rstep = 64 if mode in _lib.MODES_16BIT else 32
+            dt = operand_dtype(mode)
+            A = torch.rand(M, k_long, device="cuda").to(dt)
+            B = torch.rand(k_long, N, device="cuda").to(dt)
+            C = torch.empty(M, N, device="cuda")
+            ms = []
+            for K in (k_short, k_long):
+                plan = _lib.GemmPlan(tile, M, N, K, lda=k_long, mode=mode)
+                plan.set_stream_k(0)
+                ms.append(min(plan.time(A, B, C, warmup=2, iters=iters) for _ in range(2)))
+                plan.destroy()
+            kb_us = (ms[1] - ms[0]) * 1e3 / (waves * (k_long - k_short) / rstep)
+            if mode == MODE_1XTF32:
+                fp32[0] = kb_us
+            elif mode == MODE_3XTF32:
+                fp32[1] = kb_us
+            else:
+                arch.kblock_us_16[key] = kb_us
+        arch.kblock_us[key] = tuple(fp32)
+    return arch
+
+
 def _main(argv=None) -> None:
     """Single-problem driver (the reference's `python src/roller.py`, src/roller.py:610-633):
     baseline, search, then compile + run_eval each hint and report the fastest."""

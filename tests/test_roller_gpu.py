@@ -98,3 +98,20 @@ def test_best_hint_uses_and_fills_the_cache(tmp_path):
                                        cache=roller.TuneCache(tmp_path / "tune.json",
                                                               device_name=cache.device_name))
     assert hint2.block_tile == hint.block_tile and ms2 == ms
+
+
+def test_calibrate_measures_per_kblock_times():
+    """The device model's per-k-block table can be re-measured on the GPU at hand; the figures
+    land near the shipped table and the ranking of a large square problem is unchanged."""
+    from mlir_roller_b200 import arch as arch_mod
+    shipped = arch_mod.B200()
+    model = roller.calibrate(iters=3, k_short=1024, k_long=4096)
+    for key, (t1, t3) in model.kblock_us.items():
+        s1, s3 = shipped.kblock_us[key]
+        assert 0.5 * s1 < t1 < 2.0 * s1, (key, t1, s1)
+        assert 0.5 * s3 < t3 < 2.0 * s3, (key, t3, s3)
+    for key, t in model.kblock_us_16.items():
+        assert 0.5 * shipped.kblock_us_16[key] < t < 2.0 * shipped.kblock_us_16[key], (key, t)
+    for mode in (1, 3):
+        top = roller.get_roller_hints(roller.MatmulConfig(8192, 8192, 8192, 32), model, topk=1, mode=mode)[0]
+        assert (top.block_tile, top.cta_group) == ([256, 256], 2)
