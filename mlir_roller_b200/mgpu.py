@@ -181,13 +181,37 @@ class ShardedGemm:
         return 2 * self.block.rows * self.block.cols * self.K
 
 
-def split_bands(row0: int, row1: int, bands: int, align: int = 256) -> List[Tuple[int, int]]:
+def split_bands(row0: int, row1: int, bands: int, align: int = 256,
+                taper: bool = False) -> List[Tuple[int, int]]:
     """Cut the rows [row0, row1) of one rank's block into at most `bands` non-empty bands whose
     inner boundaries fall on multiples of `align` rows counted from row0 (one pair tile), the
-    earlier bands taking the remainder units."""
+    earlier bands taking the remainder units. With `taper` the bands shrink towards the end
+    (sizes in proportion bands : bands-1 : ... : 1): only the last band's copy is exposed, so it
+    should be the smallest, while the early bands stay large enough to fill the device."""
     if bands < 1:
         raise ValueError("bands must be positive")
-    return [(row0 + a, row0 + b) for a, b in _split(row1 - row0, bands, align) if b > a]
+    if not taper:
+        return [(row0 + a, row0 + b) for a, b in _split(row1 - row0, bands, align) if b > a]
+    extent = row1 - row0
+    units = -(-extent // align)
+    weights = list(range(bands, 0, -1))
+    sizes = [units * w // sum(weights) for w in weights]
+    for i in range(units - sum(sizes)):          # leftover units go to the earliest bands
+        sizes[i % bands] += 1
+    if units >= bands:                           # every band gets at least one unit
+        for i in range(bands - 1, 0, -1):
+            if sizes[i] == 0:
+                j = max(range(i), key=lambda t: sizes[t])
+                sizes[j] -= 1
+                sizes[i] = 1
+    sizes.sort(reverse=True)
+    out, start = [], 0
+    for n in sizes:
+        stop = min(start + n * align, extent)
+        if stop > start:
+            out.append((row0 + start, row0 + stop))
+        start = stop
+    return out
 
 
 def default_bands(rows: int, cols: int) -> int:
@@ -229,14 +253,15 @@ class BandStep:
     dests: Tuple[int, ...]
 
 
-def band_schedule(block: Block, N: int, K: int, bands: int, dests: Sequence[int]) -> List[BandStep]:
+def band_schedule(block: Block, N: int, K: int, bands: int, dests: Sequence[int],
+                  taper: bool = False) -> List[BandStep]:
     """The steps of one rank: its block cut by `split_bands`, each band with its operand and
     output offsets and the ranks it is pushed to."""
     if block.cols <= 0:
         return []
     return [BandStep(r0, r1, block.cols, (r0 - block.row0) * K, block.col0, r0 * N + block.col0,
                      tuple(dests))
-            for r0, r1 in split_bands(block.row0, block.row1, bands)]
+            for r0, r1 in split_bands(block.row0, block.row1, bands, taper=taper)]
 
 
 class OverlappedGemm:
@@ -250,6 +275,10 @@ class OverlappedGemm:
     it has completed on a rank, every rank's pushes had completed before it.
 
     dest = "root": the whole C ends up on `root` (a gather); dest = "all": on every rank.
+    With `fused=True` (dest = "root" only) there are no bands and no copies: each rank runs one
+    kernel over its whole block whose epilogue stores go straight into the root's C through the
+    peer mapping, tile by tile as tiles finish, so the transfer rides under the main loop of the
+    later tiles and nothing but the closing fence follows the kernel.
     C must not be read while another rank may still be pushing the next step into it: separate
     consecutive steps by whatever makes the readers finish first (the bench only times).
 
@@ -260,7 +289,7 @@ class OverlappedGemm:
     def __init__(self, M: int, N: int, K: int, rank: int, world_size: int,
                  grid: Optional[Tuple[int, int]] = None, mode: int = 3,
                  bands: Optional[int] = None, dest: str = "root", root: int = 0, group=None, arch=None, measure: bool = False,
-                 comm_streams: int = 2):
+                 comm_streams: int = 2, taper: bool = False, fused: bool = False):
         import os
         # plain peer mappings only: no NVLink multicast object is bound to the buffer
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
@@ -279,6 +308,9 @@ class OverlappedGemm:
         self.block = self.blocks[rank]
         self.mode = mode
         self.group = group if group is not None else dist.group.WORLD
+        if fused and dest != "root":
+            raise ValueError("the fused output path delivers C to the root only")
+        self.fused = fused
         self.dests = push_order(rank, world_size, dest, root)
         self._lib = _lib
         self._dist = dist
@@ -289,9 +321,11 @@ class OverlappedGemm:
         self.peer_C = {d: self.handle.get_buffer(d, (M, N), torch.float32) for d in self.dests}
         self._token = torch.zeros(1, dtype=torch.float32, device="cuda")
         self.comm = [torch.cuda.Stream() for _ in range(max(1, comm_streams))]
+        if fused:
+            bands = 1
         if bands is None:
             bands = default_bands(self.block.rows, self.block.cols)
-        self.steps = band_schedule(self.block, N, K, bands, self.dests)
+        self.steps = band_schedule(self.block, N, K, bands, self.dests, taper=taper)
         self.bands = [(st.row0, st.row1) for st in self.steps]
         self.plans, self.tiles, self._events = [], [], []
         by_shape = {}
@@ -316,6 +350,13 @@ class OverlappedGemm:
         for st in self.comm:
             st.wait_stream(cs)          # the previous step's consumers are ordered before the pushes
         n = 0
+        if self.fused:
+            # one kernel per rank; its C is the root's matrix (this rank's own on the root)
+            out = self.peer_C[self.dests[0]] if self.dests else self.C
+            for step, plan in zip(self.steps, self.plans):
+                plan.run_ptr(A_rows.data_ptr() + step.a_off * 4, B_full.data_ptr() + step.b_off * 4,
+                             out.data_ptr() + step.c_off * 4, cs)
+            return
         for step, plan, ev in zip(self.steps, self.plans, self._events):
             plan.run_ptr(A_rows.data_ptr() + step.a_off * 4, B_full.data_ptr() + step.b_off * 4,
                          self.C.data_ptr() + step.c_off * 4, cs)

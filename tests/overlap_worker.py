@@ -28,9 +28,11 @@ def main() -> int:
     grids = [(world, 1)] + ([(1, world), (2, world // 2)] if world % 2 == 0 else [])
     bad = 0
     for grid in grids:
-        for dest in ("root", "all"):
-            for bands in (1, 3):
-                og = mgpu.OverlappedGemm(M, N, K, rank, world, grid=grid, bands=bands, dest=dest)
+        for dest, bands, fused in (("root", 1, False), ("root", 3, False), ("all", 1, False),
+                                   ("all", 3, False), ("root", 3, True)):
+            if True:
+                og = mgpu.OverlappedGemm(M, N, K, rank, world, grid=grid, bands=bands, dest=dest,
+                                         taper=(bands == 3), fused=fused)
                 assert og.handle.multicast_ptr == 0
                 b = og.block
                 og.C.fill_(float("nan"))
@@ -45,6 +47,8 @@ def main() -> int:
                     p.check_status()
                 if dest == "all" or rank == 0:
                     err = float((og.C.double() - ref).abs().max()) / scale
+                elif fused:                 # nothing is written locally: the block went to rank 0
+                    err = 0.0
                 else:                       # only this rank's own block is defined
                     err = float((og.C[b.row0:b.row1, b.col0:b.col1].double()
                                  - ref[b.row0:b.row1, b.col0:b.col1]).abs().max()) / scale \
@@ -52,7 +56,7 @@ def main() -> int:
                 ok = err <= TOL_3X          # NaN compares false
                 if not ok:
                     bad += 1
-                print(f"rank {rank} grid {grid} dest {dest} bands {bands}: err {err:.2e} "
+                print(f"rank {rank} grid {grid} dest {dest} bands {bands} fused {fused}: err {err:.2e} "
                       f"{'ok' if ok else 'FAIL'}", flush=True)
                 og.destroy()
                 del og

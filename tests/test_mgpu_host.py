@@ -108,9 +108,9 @@ def test_gather_checks_block_shape():
 
 
 @settings(max_examples=200, deadline=None)
-@given(st.integers(0, 4096), st.integers(0, 9000), st.integers(1, 9))
-def test_bands_tile_the_block(row0, rows, bands):
-    out = mgpu.split_bands(row0, row0 + rows, bands)
+@given(st.integers(0, 4096), st.integers(0, 9000), st.integers(1, 9), st.booleans())
+def test_bands_tile_the_block(row0, rows, bands, taper):
+    out = mgpu.split_bands(row0, row0 + rows, bands, taper=taper)
     assert len(out) <= bands
     if rows == 0:
         assert out == []
@@ -120,11 +120,18 @@ def test_bands_tile_the_block(row0, rows, bands):
         assert a1 == b0
     for r0, r1 in out:
         assert r1 > r0 and (r0 - row0) % 256 == 0
+    if taper:       # later bands are never larger (in tile rows) than earlier ones
+        units = [-(-(r1 - r0) // 256) for r0, r1 in out]
+        assert units == sorted(units, reverse=True)
+        if rows >= 256 * bands:
+            assert len(out) == bands
 
 
 def test_bands_of_a_16384_row_shard():
     assert mgpu.split_bands(2048, 4096, 4) == [(2048, 2560), (2560, 3072), (3072, 3584), (3584, 4096)]
     assert mgpu.split_bands(0, 1000, 4) == [(0, 256), (256, 512), (512, 768), (768, 1000)]
+    assert mgpu.split_bands(0, 4096, 4, taper=True) == [(0, 1792), (1792, 3072), (3072, 3840), (3840, 4096)]
+    assert mgpu.split_bands(0, 2048, 4, taper=True) == [(0, 768), (768, 1536), (1536, 1792), (1792, 2048)]
     with pytest.raises(ValueError):
         mgpu.split_bands(0, 10, 0)
 
