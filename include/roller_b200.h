@@ -17,7 +17,11 @@
  *   - a plan is bound to the device that was current at create time and is not thread-safe;
  *     launches of one plan must also be ordered on the device (same stream, or streams ordered
  *     by events): a plan owns one staging area, one stream-K scratch area and one status word.
- *     Use one plan per stream to overlap GEMMs.
+ *     Use one plan per stream to overlap GEMMs;
+ *   - a launch is a persistent grid (at most one CTA per SM) whose CTAs may wait for one
+ *     another when leftover tiles are split along K, so all of them must get an SM eventually:
+ *     a kernel on another stream that occupies SMs must not itself wait for this launch. Every
+ *     such wait is bounded (~2 s) and ends in ROLLER_ERR_TIMEOUT rather than a hang.
  */
 #ifndef ROLLER_B200_H_
 #define ROLLER_B200_H_

@@ -38,6 +38,11 @@ class Block:
         return self.col1 - self.col0
 
 
+def _el_bits(mode: int) -> int:
+    """Operand width of an arithmetic mode: 16 for the bf16 / fp16 modes, else 32."""
+    return 16 if mode in (16, 17) else 32
+
+
 def _split(extent: int, parts: int, align: int) -> List[Tuple[int, int]]:
     """Cut [0, extent) into `parts` contiguous ranges whose boundaries are multiples of
     `align` (except the end); earlier ranges take the remainder units. Ranges may be empty
@@ -151,7 +156,7 @@ class ShardedGemm:
         self.plan = None
         self.hint = None
         if self.block.rows > 0 and self.block.cols > 0:
-            cfg = MatmulConfig(self.block.rows, self.block.cols, K, 32)
+            cfg = MatmulConfig(self.block.rows, self.block.cols, K, _el_bits(mode))
             hint, _fn, _ms = roller.best_hint(cfg, arch, mode=mode, measure=measure)
             self.hint = hint
             tile = roller.kernel_tile_for(hint)
@@ -332,7 +337,7 @@ class OverlappedGemm:
         for r0, r1 in self.bands:
             shape = (r1 - r0, self.block.cols)
             if shape not in by_shape:
-                cfg = MatmulConfig(shape[0], shape[1], K, 32)
+                cfg = MatmulConfig(shape[0], shape[1], K, _el_bits(mode))
                 hint, _fn, _ms = roller.best_hint(cfg, arch, mode=mode, measure=measure)
                 by_shape[shape] = roller.kernel_tile_for(hint)
             tile = by_shape[shape]
@@ -347,6 +352,7 @@ class OverlappedGemm:
         torch = self._torch
         cs = stream if stream is not None else torch.cuda.current_stream()
         N = self.N
+        eb = _el_bits(self.mode) // 8      # bytes per element of A and B; C is fp32
         for st in self.comm:
             st.wait_stream(cs)          # the previous step's consumers are ordered before the pushes
         n = 0
@@ -354,11 +360,11 @@ class OverlappedGemm:
             # one kernel per rank; its C is the root's matrix (this rank's own on the root)
             out = self.peer_C[self.dests[0]] if self.dests else self.C
             for step, plan in zip(self.steps, self.plans):
-                plan.run_ptr(A_rows.data_ptr() + step.a_off * 4, B_full.data_ptr() + step.b_off * 4,
+                plan.run_ptr(A_rows.data_ptr() + step.a_off * eb, B_full.data_ptr() + step.b_off * eb,
                              out.data_ptr() + step.c_off * 4, cs)
             return
         for step, plan, ev in zip(self.steps, self.plans, self._events):
-            plan.run_ptr(A_rows.data_ptr() + step.a_off * 4, B_full.data_ptr() + step.b_off * 4,
+            plan.run_ptr(A_rows.data_ptr() + step.a_off * eb, B_full.data_ptr() + step.b_off * eb,
                          self.C.data_ptr() + step.c_off * 4, cs)
             ev.record(cs)
             for d in step.dests:

@@ -61,6 +61,21 @@ def main() -> int:
                 og.destroy()
                 del og
                 dist.barrier()
+    # the same exchange with bf16 operands (the band offsets into A and B are in elements)
+    A16, B16 = A.to(torch.bfloat16), B.to(torch.bfloat16)
+    ref16 = A16.double() @ B16.double()
+    og = mgpu.OverlappedGemm(M, N, K, rank, world, grid=(world, 1), bands=3, dest="all", mode=16)
+    b = og.block
+    og.run(A16[b.row0:b.row1].contiguous(), B16)
+    og.finish()
+    torch.cuda.synchronize()
+    dist.barrier()
+    err = float((og.C.double() - ref16).abs().max()) / float(ref16.abs().max())
+    print(f"rank {rank} bf16 dest all bands 3: err {err:.2e} {'ok' if err <= TOL_3X else 'FAIL'}", flush=True)
+    bad += 0 if err <= TOL_3X else 1
+    og.destroy()
+    del og
+    dist.barrier()
     t = torch.tensor([bad], device="cuda")
     dist.all_reduce(t)
     dist.destroy_process_group()
