@@ -244,6 +244,39 @@ class ShapeCase:
         return float((self.C.double() - c64).abs().max() / c64.abs().max())
 
 
+def measure_pcie(torch, mib: int = 512):
+    """Pinned-memory copy rates of this box, GB/s: (host->device alone, device->host alone,
+    each way with both directions busy). They bound the end-to-end figure."""
+    n = mib * 1024 * 1024 // 4
+    h_up = torch.empty(n, dtype=torch.float32).pin_memory()
+    h_dn = torch.empty(n, dtype=torch.float32).pin_memory()
+    d_up = torch.empty(n, device="cuda")
+    d_dn = torch.empty(n, device="cuda")
+    s_up, s_dn = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def timed(up, down, reps=3):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        s_up.wait_event(e0)
+        s_dn.wait_event(e0)
+        for _ in range(reps):
+            if up:
+                with torch.cuda.stream(s_up):
+                    d_up.copy_(h_up, non_blocking=True)
+            if down:
+                with torch.cuda.stream(s_dn):
+                    h_dn.copy_(d_dn, non_blocking=True)
+        torch.cuda.current_stream().wait_stream(s_up)
+        torch.cuda.current_stream().wait_stream(s_dn)
+        e1.record()
+        e1.synchronize()
+        return n * 4.0 * reps / e0.elapsed_time(e1) / 1e6
+
+    timed(True, True, 1)
+    return timed(True, False), timed(False, True), timed(True, True)
+
+
 class LibraryCase:
     """The library GEMM (cuBLAS through torch) on a ShapeCase's operands, output in their type."""
 
@@ -487,6 +520,12 @@ def run_gpu_arm(args) -> None:
             dist.destroy_process_group()
         return
 
+    # ---- what the PCIe link allows for the end-to-end step: the readback runs beside the
+    # upload at the duplex rate, the rest of the upload at the one-way rate
+    up_gbs, down_gbs, duplex_gbs = measure_pcie(torch)
+    t_down = d2h / (duplex_gbs * 1e6)
+    e2e_bound_ms = t_down + max(h2d - t_down * duplex_gbs * 1e6, 0.0) / (up_gbs * 1e6)
+
     # ---- roofline of the dominant kernel (the tcgen05 GEMM): algorithmic tensor flops
     # (3 TF32 products per fp32 product) per launch over the mean launch duration.
     burst_tf32, sustained_tf32 = measure_tf32_library_peak(torch)
@@ -554,7 +593,9 @@ def run_gpu_arm(args) -> None:
         "roofline": roofline,
         "cpu_baseline": cpu_baseline,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                "pcie_gbs": {"h2d": up_gbs, "d2h": down_gbs, "each_way_duplex": duplex_gbs},
+                "pcie_bound_ms": e2e_bound_ms},
         "gpu_launches": len(cases) * args.steps,
         "search_ms": {"b200_policy": statistics.mean(t_new) * 1e3,
                       "a100_policy": statistics.mean(t_a100) * 1e3,
