@@ -1,0 +1,67 @@
+"""bench.py prints one JSON line with the keys its readers rely on: the reference arm (CPU
+only) here, the GPU arm on a B200."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+BASE_KEYS = {"metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step",
+             "higher_is_better", "scaling", "vs_baseline", "dtype", "data", "config",
+             "cpu_baseline", "e2e"}
+
+
+def run_bench(*args, timeout=900):
+    res = subprocess.run([sys.executable, str(ROOT / "bench.py"), *args], capture_output=True,
+                         text=True, timeout=timeout, cwd=str(ROOT))
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [ln for ln in res.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1, "exactly one JSON line on stdout"
+    return json.loads(lines[0])
+
+
+def test_reference_arm_line():
+    line = run_bench("--impl", "reference", "--steps", "1", "--warmup", "0")
+    assert BASE_KEYS <= set(line)
+    assert line["impl"] == "reference" and line["n_gpus"] == 1 and line["steps"] == 1
+    assert line["higher_is_better"] is True and line["vs_baseline"] is None
+    assert line["unit"] == "TFLOP/s" and line["value"] > 0 and line["ms_per_step"] > 0
+    assert "workload" in line["config"] and "model" not in line["config"]
+    cb = line["cpu_baseline"]
+    assert cb["kind"] == "port" and cb["cores"] >= 1 and cb["value"] == line["value"] and cb["sample"]
+    e2e = line["e2e"]
+    assert e2e["value"] == line["value"] and e2e["unit"] == line["unit"]
+    assert e2e["h2d_bytes_per_step"] == 0 and e2e["d2h_bytes_per_step"] == 0
+
+
+@pytest.mark.gpu
+def test_gpu_arm_line():
+    steps = 3
+    line = run_bench("--steps", str(steps), "--warmup", "3", "--select", "model")
+    assert BASE_KEYS | {"clocks", "roofline", "gpu_launches", "per_shape", "bf16"} <= set(line)
+    assert "impl" not in line or line["impl"] != "reference"
+    assert line["n_gpus"] == 1 and line["steps"] == steps and line["warmup"] >= 3
+    assert line["scaling"] == "weak" and line["data"] == "synthetic" and line["vs_baseline"] is None
+    assert line["gpu_launches"] == 14 * steps
+    assert 50 < line["value"] < 600                     # useful fp32 TFLOP/s of the 3xTF32 sweep
+    roof = line["roofline"]
+    assert roof["bound"] == "tensor" and roof["unit"] == "TFLOP/s"
+    assert abs(roof["frac"] - roof["achieved"] / roof["peak"]) < 1e-9 and roof["traffic"] > 0
+    cb = line["cpu_baseline"]
+    assert cb["kind"] == "port" and cb["value"] > 0 and cb["cores"] >= 1
+    e2e = line["e2e"]
+    assert 0 < e2e["value"] < line["value"]             # host copies inside the timed region
+    assert e2e["h2d_bytes_per_step"] == 4 * sum(m * k + k * n for m, n, k in SHAPES)
+    assert e2e["d2h_bytes_per_step"] == 4 * sum(m * n for m, n, k in SHAPES)
+    assert e2e["pcie_bound_ms"] <= e2e["ms_per_step"] * 1.05
+    assert {"sm_mhz", "sm_max_mhz", "reasons"} <= set(line["clocks"])
+    assert len(line["per_shape"]) == 14 and line["max_err_3x"] <= 1e-5
+    assert line["bf16"]["max_err"] <= 1e-5 and line["bf16"]["value"] > line["value"]
+
+
+SHAPES = [(2048, 2048, 2048), (2048, 2048, 8192), (2048, 4096, 2048), (2048, 4096, 4096),
+          (2048, 8192, 2048), (2048, 8192, 4096), (2048, 8192, 8192), (4096, 2048, 2048),
+          (4096, 4096, 8192), (4096, 8192, 2048), (4096, 8192, 4096), (8192, 2048, 8192),
+          (8192, 4096, 2048), (8192, 4096, 4096)]
