@@ -256,3 +256,31 @@ def test_compiler_out_16bit():
     torch.cuda.synchronize()
     ref = (A.double() @ B.double())
     assert float((C.double() - ref).abs().max() / ref.abs().max()) < 8e-3   # bf16 output rounding
+
+
+@pytest.mark.parametrize("kind", ["bf16", "f16"])
+def test_special_values(kind):
+    """IEEE behaviour of the 16-bit path: inf and nan propagate, inf * 0 along a row is nan,
+    a sum beyond the fp32 range would need > 3e38 (not reachable here), fp16 subnormal inputs
+    are exact, and a 16-bit C overflows to inf where the fp32 C holds a finite value."""
+    A = np.zeros((128, 64), np.float32)
+    B = np.zeros((64, 64), np.float32)
+    A[0, 0] = np.inf; B[0, 0] = 1.0
+    A[1, 1] = 2.0 ** -20; B[1, 1] = 2.0 ** -4            # fp16: subnormal times normal, exact
+    A[2, 2] = 300.0; B[2, 2] = 300.0                     # 9e4: beyond fp16's 65504 as an output
+    A[3, 3] = np.nan; B[3, 3] = 2.0
+    conv = g.to_bf16_bits if kind == "bf16" else g.to_f16_bits
+    Ab, Bb = conv(A), conv(B)
+    C = gpu_gemm16(Ab, Bb, kind, (128, 64, 1))
+    assert np.isinf(C[0, 0]) and C[0, 0] > 0
+    assert np.isnan(C[0, 1]) and np.isnan(C[3, 3])
+    assert C[1, 1] == np.float32(2.0 ** -24) and C[2, 2] == 90000.0
+    mode, dt = KINDS[kind]
+    plan = _lib.GemmPlan(_lib.find_tile(128, 64, 1), 128, 64, 64, mode=mode, flags=_lib.FLAG_C_16BIT)
+    C16 = torch.empty(128, 64, device="cuda", dtype=dt)
+    plan.run(to_device(Ab, kind), to_device(Bb, kind), C16)
+    torch.cuda.synchronize()
+    plan.destroy()
+    out = C16.float().cpu().numpy()
+    assert np.isinf(out[0, 0]) and np.isnan(out[3, 3])
+    assert (np.isinf(out[2, 2]) if kind == "f16" else out[2, 2] == 90112.0)   # bf16: nearest value
