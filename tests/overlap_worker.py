@@ -30,37 +30,36 @@ def main() -> int:
     for grid in grids:
         for dest, bands, fused in (("root", 1, False), ("root", 3, False), ("all", 1, False),
                                    ("all", 3, False), ("root", 3, True)):
-            if True:
-                og = mgpu.OverlappedGemm(M, N, K, rank, world, grid=grid, bands=bands, dest=dest,
-                                         taper=(bands == 3), fused=fused)
-                assert og.handle.multicast_ptr == 0
-                b = og.block
-                og.C.fill_(float("nan"))
+            og = mgpu.OverlappedGemm(M, N, K, rank, world, grid=grid, bands=bands, dest=dest,
+                                     taper=(bands == 3), fused=fused)
+            assert og.handle.multicast_ptr == 0
+            b = og.block
+            og.C.fill_(float("nan"))
+            torch.cuda.synchronize()
+            dist.barrier()
+            for _ in range(2):          # twice: the second step overwrites the first
+                og.run(A[b.row0:b.row1].contiguous(), B)
+                og.finish()
                 torch.cuda.synchronize()
                 dist.barrier()
-                for _ in range(2):          # twice: the second step overwrites the first
-                    og.run(A[b.row0:b.row1].contiguous(), B)
-                    og.finish()
-                    torch.cuda.synchronize()
-                    dist.barrier()
-                for p in og.plans:
-                    p.check_status()
-                if dest == "all" or rank == 0:
-                    err = float((og.C.double() - ref).abs().max()) / scale
-                elif fused:                 # nothing is written locally: the block went to rank 0
-                    err = 0.0
-                else:                       # only this rank's own block is defined
-                    err = float((og.C[b.row0:b.row1, b.col0:b.col1].double()
-                                 - ref[b.row0:b.row1, b.col0:b.col1]).abs().max()) / scale \
-                        if b.rows * b.cols else 0.0
-                ok = err <= TOL_3X          # NaN compares false
-                if not ok:
-                    bad += 1
-                print(f"rank {rank} grid {grid} dest {dest} bands {bands} fused {fused}: err {err:.2e} "
-                      f"{'ok' if ok else 'FAIL'}", flush=True)
-                og.destroy()
-                del og
-                dist.barrier()
+            for p in og.plans:
+                p.check_status()
+            if dest == "all" or rank == 0:
+                err = float((og.C.double() - ref).abs().max()) / scale
+            elif fused:                 # nothing is written locally: the block went to rank 0
+                err = 0.0
+            else:                       # only this rank's own block is defined
+                err = float((og.C[b.row0:b.row1, b.col0:b.col1].double()
+                             - ref[b.row0:b.row1, b.col0:b.col1]).abs().max()) / scale \
+                    if b.rows * b.cols else 0.0
+            ok = err <= TOL_3X          # NaN compares false
+            if not ok:
+                bad += 1
+            print(f"rank {rank} grid {grid} dest {dest} bands {bands} fused {fused}: err {err:.2e} "
+                  f"{'ok' if ok else 'FAIL'}", flush=True)
+            og.destroy()
+            del og
+            dist.barrier()
     # the same exchange with bf16 operands (the band offsets into A and B are in elements)
     A16, B16 = A.to(torch.bfloat16), B.to(torch.bfloat16)
     ref16 = A16.double() @ B16.double()
