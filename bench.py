@@ -23,6 +23,7 @@ Prints ONE JSON line on rank 0.
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -52,9 +53,11 @@ def sweep_flops(shapes=README_SHAPES) -> float:
 
 # ------------------------------------------------------------------ clocks
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons every 20 ms while running."""
+    """Samples nvidia-smi clocks and throttle reasons every 20 ms while running. nvidia-smi
+    needs a moment to start, so it is launched well before the timed region; `mark_begin` /
+    `mark_end` bracket that region and only samples stamped inside it are reported."""
 
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -63,6 +66,23 @@ class ClockSampler:
         self.rows = []
         self.proc = None
         self.thread = None
+        self.t_begin = None
+        self.t_end = None
+
+    def mark_begin(self):
+        self.t_begin = datetime.datetime.now()
+
+    def mark_end(self):
+        self.t_end = datetime.datetime.now()
+
+    def _inside(self, stamp: str) -> bool:
+        if self.t_begin is None or self.t_end is None:
+            return True
+        try:
+            t = datetime.datetime.strptime(stamp, "%Y/%m/%d %H:%M:%S.%f")
+        except ValueError:
+            return False
+        return self.t_begin <= t <= self.t_end
 
     def start(self):
         try:
@@ -90,12 +110,14 @@ class ClockSampler:
             self.proc.kill()
         if self.thread is not None:
             self.thread.join(timeout=2)
-        sm, mx, reasons = [], [], set()
+        sm, mx, power, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        inside = [r for r in self.rows if r and self._inside(r[0])]
+        for r in inside:
             try:
                 sm.append(float(r[1]))
                 mx.append(float(r[2]))
+                power.append(float(r[3]))
             except (ValueError, IndexError):
                 continue
             for name, val in zip(names, r[5:9]):
@@ -103,7 +125,9 @@ class ClockSampler:
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None,
                 "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "samples_outside_timed_region": len(self.rows) - len(inside),
+                "power_w_median": statistics.median(power) if power else None,
+                "reasons": sorted(reasons)}
 
 
 # ------------------------------------------------------------------ CPU baseline / reference arm
@@ -460,6 +484,9 @@ def run_gpu_arm(args) -> None:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     arch = B200.from_device(local_rank)
+    sampler = ClockSampler(local_rank)     # started early: see the class
+    if rank == 0:
+        sampler.start()
 
     measure = args.select == "measure"
     cases = [ShapeCase(torch, i, s, MODE_3XTF32, arch, measure) for i, s in enumerate(README_SHAPES)]
@@ -467,10 +494,9 @@ def run_gpu_arm(args) -> None:
     for c in cases:
         c.plan.check_status()
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
+    sampler.mark_begin()
     step_ms, per_shape_ms = timed_sweep(torch, cases, args.steps, args.warmup, dist)
+    sampler.mark_end()
     clocks = sampler.stop() if rank == 0 else None
     if dist is not None:
         t = torch.tensor([step_ms], device="cuda")
