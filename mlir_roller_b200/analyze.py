@@ -130,6 +130,10 @@ class TileDict:
         self.est_us: Optional[float] = None
         self.kernel: Optional[str] = None
         self.layout: int = 0   # 0 general tile, 2 skinny tile (tensor core works on C^T)
+        # 1xTF32 / 16-bit kernels on a grid with fewer tiles than workers: cut every tile's
+        # reduction in `split_k` pieces of `chunk_k` elements so that idle SMs take a share
+        self.split_k: int = 1
+        self.chunk_k: Optional[int] = None
 
     def __hash__(self) -> int:
         return hash(tuple(self.block_tile + self.thread_tile))
@@ -410,6 +414,21 @@ class BlackwellPolicy:
         # launch, pipeline fill, last drain and the C stores of the final tile
         fixed_us = 8.0 + rows_cta * block_n * 4 / 32768.0
         worker_us = waves * num_kb * kb_us + fixed_us
+        # An under-filled grid of a mode that reduces a tile in one piece (1xTF32, 16-bit): a
+        # cut of every tile along K lets the idle workers take a share. The partial tiles go
+        # through global memory; measured cost of that exchange 12 us for a 128 x 64 tile,
+        # 18 us for a 128 x 256 one. Worth it for long reductions only (8192 x 16 x 8192 in
+        # 1xTF32: 76 -> 55 us; 2048^3 would go from 35 to 40 us and is left alone).
+        if mode != MODE_3XTF32 and layout != 2 and td.grid_size < workers and num_kb >= 32:
+            exchange_us = 10.0 + 0.06 * rows_cta * block_n * 4 / 1024.0
+            for s in (2, 3, 4, 6, 8):
+                if td.grid_size * s > workers or num_kb // s < 8:
+                    break
+                cand = -(-num_kb // s) * kb_us + exchange_us + fixed_us
+                if cand < 0.9 * worker_us:
+                    worker_us = cand
+                    td.split_k = s
+                    td.chunk_k = -(-num_kb // s) * rstep
         hbm_bytes = float(eb) * (cfg.M * cfg.K + cfg.K * cfg.N) + 4.0 * cfg.M * cfg.N
         hbm_us = hbm_bytes / (dev.hbm_gbs * 1e3) + 4.0
         td.est_us = max(worker_us, hbm_us)

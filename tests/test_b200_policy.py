@@ -119,3 +119,24 @@ def test_tune_cache_roundtrip(tmp_path):
     assert again.get(cfg, 1) is None and again.get(MatmulConfig(1, 2, 3, 32), 3) is None
     (tmp_path / "broken.json").write_text("{not json")
     assert roller.TuneCache(tmp_path / "broken.json").table == {}
+
+
+def test_split_k_is_suggested_for_underfilled_long_reductions_only():
+    """1xTF32 / 16-bit kernels reduce a tile in one piece; when the grid has fewer tiles than
+    workers and K is long the policy cuts the tiles along K, otherwise it leaves them whole."""
+    dev = arch.B200()
+    def top(M, N, K, bits, mode):
+        return get_roller_hints(MatmulConfig(M, N, K, bits), dev, topk=1, mode=mode)[0]
+    h = top(4096, 64, 8192, 32, MODE_1XTF32)
+    assert h.split_k == 4 and h.chunk_k == 2048 and h.grid_size * h.split_k <= 148 // h.cta_group
+    h = top(8192, 16, 8192, 32, MODE_1XTF32)
+    assert h.split_k == 2 and h.chunk_k == 4096
+    assert top(8192, 16, 8192, 16, MODE_BF16).split_k == 2
+    # short reduction, full grid, 3xTF32 (the library splits that mode itself), skinny layout
+    assert top(2048, 2048, 2048, 32, MODE_1XTF32).split_k == 1
+    assert top(8192, 8192, 8192, 32, MODE_1XTF32).split_k == 1
+    assert top(8192, 16, 8192, 32, MODE_3XTF32).split_k == 1
+    assert top(16, 8192, 8192, 32, MODE_1XTF32).split_k == 1
+    for hint in get_roller_hints(MatmulConfig(4096, 64, 8192, 32), dev, topk=8, mode=MODE_1XTF32):
+        if hint.split_k > 1:
+            assert hint.chunk_k % hint.rstep == 0 and hint.chunk_k * hint.split_k >= 8192

@@ -115,3 +115,25 @@ def test_calibrate_measures_per_kblock_times():
     for mode in (1, 3):
         top = roller.get_roller_hints(roller.MatmulConfig(8192, 8192, 8192, 32), model, topk=1, mode=mode)[0]
         assert (top.block_tile, top.cta_group) == ([256, 256], 2)
+
+
+def test_split_k_hint_is_applied_and_pays():
+    """4096 x 64 x 8192 in 1xTF32: 32 tiles for 148 SMs. The hint asks for a cut along K,
+    `Compiler` applies it, the result stays within the 1xTF32 band and the launch gets faster."""
+    M, N, K = 4096, 64, 8192
+    cfg = MatmulConfig(M, N, K, 32)
+    hint = get_roller_hints(cfg, B200(), topk=1, mode=1)[0]
+    assert hint.split_k > 1
+    A, Bm = g.make_inputs(M, N, K, "uniform", seed=3)
+    dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(Bm).cuda()
+    dC = torch.empty(M, N, device="cuda")
+    split = roller.Compiler(cfg, hint, mode=1).compile()
+    whole = roller.Compiler(cfg, hint, mode=1, stream_k=0).compile()
+    split((1, 1), (1, 1), (dA.data_ptr(), dB.data_ptr(), dC.data_ptr()))
+    torch.cuda.synchronize()
+    split.plan.check_status()
+    rows = [0, 127, 128, 2047, 4095]
+    assert g.err_norm(dC.cpu().numpy()[rows], g.sample_rows_fp64(A, Bm, rows)) <= 2e-3
+    t_split = min(split.time(dA, dB, dC, warmup=3, iters=20) for _ in range(3))
+    t_whole = min(whole.time(dA, dB, dC, warmup=3, iters=20) for _ in range(3))
+    assert t_split < t_whole / 1.15, (t_split, t_whole)
