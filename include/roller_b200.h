@@ -170,7 +170,8 @@ int roller_b200_gemm_set_chunk(roller_plan* plan, int k_elems);
 int roller_b200_gemm_set_grid(roller_plan* plan, int ctas);
 
 /* Stream-K scheduling of the leftover tiles (those that do not fill a last wave of the persistent
- * grid): -1 = use it when it shortens the schedule by 3 % or more (default), 0 = never (every
+ * grid; they are dealt out along K in pieces of one accumulation chunk in 3xTF32, of 8 k-blocks
+ * in the other modes): -1 = use it when it shortens the schedule by 3 % or more (default), 0 = never (every
  * tile is reduced by one worker; results are then bit-identical for every rTile and every
  * sharding), 1 = whenever there are leftover tiles. May allocate the scratch area for the
  * partial tiles. The reference's grid is always one block per tile (src/roller.py:536). */

@@ -130,10 +130,6 @@ class TileDict:
         self.est_us: Optional[float] = None
         self.kernel: Optional[str] = None
         self.layout: int = 0   # 0 general tile, 2 skinny tile (tensor core works on C^T)
-        # 1xTF32 / 16-bit kernels on a grid with fewer tiles than workers: cut every tile's
-        # reduction in `split_k` pieces of `chunk_k` elements so that idle SMs take a share
-        self.split_k: int = 1
-        self.chunk_k: Optional[int] = None
 
     def __hash__(self) -> int:
         return hash(tuple(self.block_tile + self.thread_tile))
@@ -398,14 +394,17 @@ class BlackwellPolicy:
             smem_clk = (raw + split_rw + mma_reads) / dev.smem_bytes_per_clk_sm
             l2_clk = raw / dev.l2_bytes_per_clk_sm
             kb_us = max(tensor_clk, smem_clk, l2_clk) / dev.sm_clock_mhz
-        # Whole tiles go round-robin; leftover tiles are dealt out in k-chunks (stream-K) when
-        # that shortens the schedule by 3 % or more after charging the partial-tile exchange --
-        # the same rule the library applies (3xTF32 only: 1xTF32 reduces a tile in one chunk).
+        # Whole tiles go round-robin; leftover tiles are dealt out in pieces along K (stream-K)
+        # when that shortens the schedule by 3 % or more after charging the partial-tile
+        # exchange -- the same rule the library applies. 3xTF32 schedules in its 4-k-block
+        # accumulation chunks and pays one of them (three when no whole tile follows); the
+        # other modes schedule in units of 8 k-blocks and pay 24 k-blocks (72).
         full, left = divmod(td.grid_size, workers)
         waves = float(td.num_wave)
-        if mode == MODE_3XTF32 and left:
-            cpt = -(-num_kb // 4)                      # 128-deep chunks per tile
-            exchange = 1 if full >= 1 else 3           # partial-tile exchange, in chunks
+        if left:
+            unit = 4 if mode == MODE_3XTF32 else min(8, num_kb)
+            cpt = -(-num_kb // unit)
+            exchange = (1 if mode == MODE_3XTF32 else -(-24 // unit)) * (1 if full >= 1 else 3)
             split = full * cpt + -(-left * cpt // workers) + exchange
             if cpt > 1 and (full + 1) * cpt - split >= 0.03 * (full + 1) * cpt:
                 waves = split / cpt
@@ -414,21 +413,6 @@ class BlackwellPolicy:
         # launch, pipeline fill, last drain and the C stores of the final tile
         fixed_us = 8.0 + rows_cta * block_n * 4 / 32768.0
         worker_us = waves * num_kb * kb_us + fixed_us
-        # An under-filled grid of a mode that reduces a tile in one piece (1xTF32, 16-bit): a
-        # cut of every tile along K lets the idle workers take a share. The partial tiles go
-        # through global memory; measured cost of that exchange 12 us for a 128 x 64 tile,
-        # 18 us for a 128 x 256 one. Worth it for long reductions only (8192 x 16 x 8192 in
-        # 1xTF32: 76 -> 55 us; 2048^3 would go from 35 to 40 us and is left alone).
-        if mode != MODE_3XTF32 and layout != 2 and td.grid_size < workers and num_kb >= 32:
-            exchange_us = 10.0 + 0.06 * rows_cta * block_n * 4 / 1024.0
-            for s in (2, 3, 4, 6, 8):
-                if td.grid_size * s > workers or num_kb // s < 8:
-                    break
-                cand = -(-num_kb // s) * kb_us + exchange_us + fixed_us
-                if cand < 0.9 * worker_us:
-                    worker_us = cand
-                    td.split_k = s
-                    td.chunk_k = -(-num_kb // s) * rstep
         hbm_bytes = float(eb) * (cfg.M * cfg.K + cfg.K * cfg.N) + 4.0 * cfg.M * cfg.N
         hbm_us = hbm_bytes / (dev.hbm_gbs * 1e3) + 4.0
         td.est_us = max(worker_us, hbm_us)

@@ -118,6 +118,7 @@ void pad_rows(const void* src, long long ld_src, void* dst, long long ld_dst, in
 
 struct roller_plan;
 static int plan_configure(roller_plan* p);
+static int default_unit_kb(const roller_plan* p);
 
 struct roller_plan {
   const KernelVariant* kv;
@@ -131,6 +132,7 @@ struct roller_plan {
   int layout;             // 0 plain, 1 B given transposed, 2 skinny (roles swapped)
   int tiles_m, tiles_n, grid;
   int chunk_kb;           // accumulation chunk, in k-blocks (one reduce step each)
+  int unit_kb;            // unit of the stream-K schedule, in k-blocks (<= chunk_kb)
   int max_clusters;       // co-resident CTA pairs the device reports (cta_group 2 only)
   int max_workers;        // persistent workers (CTAs or CTA pairs) that may run at once
   bool grid_forced;       // grid fixed by roller_b200_gemm_set_grid
@@ -289,6 +291,7 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
   // A skinny problem streams B once and is HBM-bound: it needs every SM pulling data, which
   // only a split along K provides, so 1xTF32 gets chunks too (512 k).
   if (layout == 2 && mode != ROLLER_MODE_3XTF32 && num_kb > 16) p->chunk_kb = 16;
+  p->unit_kb = default_unit_kb(p);
   p->stage_a = (static_cast<long long>(lda) * elem % 16) != 0;
   p->stage_b = (static_cast<long long>(ldb) * elem % 16) != 0;
 
@@ -412,7 +415,8 @@ int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, void* C, 
   args.ldc = p->ldc;
   args.tiles_m = p->tiles_m;
   args.tiles_n = p->tiles_n;
-  args.chunk_kb = p->chunk_kb;
+  args.chunk_kb = p->unit_kb;
+  args.acc_kb = p->chunk_kb;
   args.flags = (p->flags & ROLLER_FLAG_ACCUMULATE) ? kFlagAccumulate : 0;
   if ((p->ldc * p->c_elem % 16) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0)
     args.flags |= kFlagVecStore;
@@ -520,6 +524,7 @@ int roller_b200_gemm_set_chunk(roller_plan* p, int k_elems) {
   if (kb < 1) kb = 1;
   if (kb > num_kb) kb = num_kb;
   p->chunk_kb = kb;
+  p->unit_kb = default_unit_kb(p);
   return plan_configure(p);
 }
 
@@ -596,11 +601,19 @@ const char* roller_b200_last_cuda_error(void) { return g_cuda_err; }
 // K = 4096 and 8192, -5 % at K = 16384; 48 tiles at K = 8192: -22 %). So the split schedule is
 // charged one chunk (whole tiles follow) or three (they do not) and used when it is still at
 // least 3 % shorter.
+// 3xTF32 drains every chunk for accuracy and deals leftover tiles out in the same pieces. The
+// other modes drain rarely (or never), so their schedule gets a unit of its own: 8 k-blocks,
+// fine enough to even out a last wave, and never longer than the accumulation chunk.
+static int default_unit_kb(const roller_plan* p) {
+  if (p->mode == ROLLER_MODE_3XTF32 || p->layout == 2) return p->chunk_kb;
+  return p->chunk_kb < 8 ? p->chunk_kb : 8;
+}
+
 static int plan_configure(roller_plan* p) {
   const KernelVariant* kv = p->kv;
   const long long tiles = static_cast<long long>(p->tiles_m) * p->tiles_n;
   const int num_kb = (p->K + kv->rstep - 1) / kv->rstep;
-  const int cpt = (num_kb + p->chunk_kb - 1) / p->chunk_kb;
+  const int cpt = (num_kb + p->unit_kb - 1) / p->unit_kb;
   int workers = p->grid_forced ? p->grid / kv->cta_group : p->max_workers;
   if (workers < 1) workers = 1;
 
@@ -609,8 +622,13 @@ static int plan_configure(roller_plan* p) {
   if (p->sk_mode != 0 && r != 0 && cpt > 1 && !(p->flags & ROLLER_FLAG_ACCUMULATE)) {
     const long long full = tiles / workers;
     const long long dp_time = (full + 1) * cpt;
-    const long long sk_time =
-        full * cpt + (r * cpt + workers - 1) / workers + (full >= 1 ? 1 : 3);
+    // Cost of handing partial tiles from worker to worker through global memory, in units:
+    // one unit, three when no whole tile follows to hide the wait, for 3xTF32 (4.4 us per
+    // unit); 24 k-blocks, or 72, for the faster modes (fitted to measurements: 4096^3 and
+    // 2048 x 4096 x 4096 gain 7-10 % in 1xTF32, 2048^3 would lose 9 %).
+    const long long per_exchange = (p->mode == ROLLER_MODE_3XTF32) ? 1 : (24 + p->unit_kb - 1) / p->unit_kb;
+    const long long exchange = per_exchange * (full >= 1 ? 1 : 3);
+    const long long sk_time = full * cpt + (r * cpt + workers - 1) / workers + exchange;
     // (the skinny layout is HBM-bound: it always splits, to put every SM to work on the stream)
     if (p->sk_mode == 1 || p->layout == 2 || (dp_time - sk_time) * 100 >= 3 * dp_time)
       sk_tiles = static_cast<int>(r);

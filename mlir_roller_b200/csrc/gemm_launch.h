@@ -19,7 +19,8 @@ struct GemmArgs {
   int M, N, K;
   long long ldc;
   int tiles_m, tiles_n;
-  int chunk_kb;  // k-blocks accumulated in TMEM before a drain into registers
+  int chunk_kb;  // unit of the stream-K schedule, in k-blocks
+  int acc_kb;    // k-blocks accumulated in TMEM before a drain into registers
   int flags;
   uint32_t* status;
   int sk_tiles;         // tiles dealt out in k-chunks (stream-K); 0 = whole tiles only

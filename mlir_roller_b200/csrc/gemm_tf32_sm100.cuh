@@ -284,8 +284,12 @@ template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  float* __restrict__ C, int M, int N, int K, long long ldc, int tiles_m,
-                 int tiles_n, int chunk_kb, int flags, uint32_t* status, int sk_tiles,
+                 int tiles_n, int chunk_kb, int acc_kb, int flags, uint32_t* status, int sk_tiles,
                  float* sk_ws, uint32_t* sk_flags, uint32_t epoch) {
+  // chunk_kb: the unit of the stream-K schedule (a tile's reduction is dealt out in pieces of
+  // that many k-blocks); acc_kb: how many k-blocks accumulate in TMEM before the accumulate
+  // warps drain them into registers. 3xTF32 uses the same value for both; the modes whose
+  // accuracy does not ask for frequent drains schedule in small units and drain rarely.
   constexpr int BN = Cfg::BN, BK = Cfg::BK, CG = Cfg::CG, STAGES = Cfg::STAGES;
 
   extern __shared__ uint8_t smem_dyn[];
@@ -386,8 +390,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t acc_ph = 0;
       bool ok = true;
       while (ok && sched.next(sg)) {
-        for (int kb0 = sg.kb0; kb0 < sg.kb1 && ok; kb0 += chunk_kb) {
-          const int kb1 = min(kb0 + chunk_kb, sg.kb1);
+        for (int kb0 = sg.kb0; kb0 < sg.kb1 && ok; kb0 += acc_kb) {
+          const int kb1 = min(kb0 + acc_kb, sg.kb1);
           if (!mbar_wait(tmem_empty_bar(acc), acc_ph ^ 1u, status, kDevTimeoutTmemEmpty)) {
             ok = false;
             break;
@@ -460,7 +464,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int n0 = nb * BN + half * COLS;
 #pragma unroll
       for (int j = 0; j < COLS; ++j) sum[j] = 0.0f;
-      for (int kb0 = sg.kb0; kb0 < sg.kb1; kb0 += chunk_kb) {
+      for (int kb0 = sg.kb0; kb0 < sg.kb1; kb0 += acc_kb) {
         if (!mbar_wait(tmem_full_bar(acc), acc_ph, status, kDevTimeoutTmemFull)) { ok = false; break; }
         tcgen05_fence_after_sync();
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +

@@ -21,7 +21,7 @@ static cudaError_t launch_variant(const GemmArgs& a, int grid, cudaStream_t stre
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, gemm_tf32_kernel<Cfg>, a.tmA, a.tmB, a.C, a.M, a.N, a.K, a.ldc,
-                            a.tiles_m, a.tiles_n, a.chunk_kb, a.flags, a.status, a.sk_tiles, a.sk_ws,
+                            a.tiles_m, a.tiles_n, a.chunk_kb, a.acc_kb, a.flags, a.status, a.sk_tiles, a.sk_ws,
                             a.sk_flags, a.epoch);
 }
 

@@ -182,6 +182,7 @@ extern "C" int roller_b200_gemm_static_scratch(const roller_ktile* tile, int mod
   args.tiles_n = (N + kv->block_n - 1) / kv->block_n;
   const int num_kb = (K + kv->rstep - 1) / kv->rstep;
   args.chunk_kb = (mode == ROLLER_MODE_3XTF32) ? 4 : num_kb;
+  args.acc_kb = args.chunk_kb;
   args.flags = 0;
   if ((ldc % 4) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) args.flags |= kFlagVecStore;
   args.status = status;

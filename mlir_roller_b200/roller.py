@@ -115,10 +115,6 @@ class Compiler:
                              | (_lib.FLAG_C_16BIT if self.out_16bit else 0))
         if self.stream_k != -1:
             plan.set_stream_k(self.stream_k)
-        elif (getattr(self.hint, "split_k", 1) or 1) > 1 and not self.accumulate:
-            # the search found the grid under-filled and the reduction long: cut the tiles along K
-            plan.set_chunk(self.hint.chunk_k)
-            plan.set_stream_k(1)
         return CompiledGemm(plan, self.hint)
 
 

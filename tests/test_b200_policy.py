@@ -121,22 +121,20 @@ def test_tune_cache_roundtrip(tmp_path):
     assert roller.TuneCache(tmp_path / "broken.json").table == {}
 
 
-def test_split_k_is_suggested_for_underfilled_long_reductions_only():
-    """1xTF32 / 16-bit kernels reduce a tile in one piece; when the grid has fewer tiles than
-    workers and K is long the policy cuts the tiles along K, otherwise it leaves them whole."""
+def test_estimate_counts_the_cut_along_k_of_leftover_tiles():
+    """The library deals leftover tiles out along K when that pays (in units of 8 k-blocks for
+    the modes that do not drain often); the estimate follows the same rule, so an under-filled
+    grid with a long reduction is not charged a whole wave."""
     dev = arch.B200()
     def top(M, N, K, bits, mode):
         return get_roller_hints(MatmulConfig(M, N, K, bits), dev, topk=1, mode=mode)[0]
-    h = top(4096, 64, 8192, 32, MODE_1XTF32)
-    assert h.split_k == 4 and h.chunk_k == 2048 and h.grid_size * h.split_k <= 148 // h.cta_group
-    h = top(8192, 16, 8192, 32, MODE_1XTF32)
-    assert h.split_k == 2 and h.chunk_k == 4096
-    assert top(8192, 16, 8192, 16, MODE_BF16).split_k == 2
-    # short reduction, full grid, 3xTF32 (the library splits that mode itself), skinny layout
-    assert top(2048, 2048, 2048, 32, MODE_1XTF32).split_k == 1
-    assert top(8192, 8192, 8192, 32, MODE_1XTF32).split_k == 1
-    assert top(8192, 16, 8192, 32, MODE_3XTF32).split_k == 1
-    assert top(16, 8192, 8192, 32, MODE_1XTF32).split_k == 1
-    for hint in get_roller_hints(MatmulConfig(4096, 64, 8192, 32), dev, topk=8, mode=MODE_1XTF32):
-        if hint.split_k > 1:
-            assert hint.chunk_k % hint.rstep == 0 and hint.chunk_k * hint.split_k >= 8192
+    h = top(4096, 64, 8192, 32, MODE_1XTF32)       # 16 or 32 tiles for 74 / 148 workers
+    kb_us = dev.kblock_us[(h.block_tile[0], h.block_tile[1], h.cta_group)][0]
+    assert h.est_us < 0.75 * (8192 // 32) * kb_us
+    h = top(2048, 2048, 2048, 32, MODE_1XTF32)     # short reduction: whole tiles
+    kb_us = dev.kblock_us[(h.block_tile[0], h.block_tile[1], h.cta_group)][0]
+    assert h.est_us >= (2048 // 32) * kb_us
+    # a ragged last wave of a long reduction: 256 tiles on 74 CTA pairs
+    h = top(4096, 4096, 8192, 32, MODE_1XTF32)
+    assert (h.block_tile, h.cta_group) == ([256, 256], 2)
+    assert h.est_us < 3.8 * (8192 // 32) * dev.kblock_us[(256, 256, 2)][0]

@@ -107,7 +107,8 @@ def test_chunk_length_trades_accuracy():
     """Longer TMEM chunks = more truncating adds in a row: the error grows with the chunk."""
     Ab, Bb, Av, Bv = g.make_inputs_16(256, 256, 8192, "bf16", "uniform", seed=6)
     C64 = g.matmul_fp64(Av, Bv)
-    e = {c: g.err_norm(gpu_gemm16(Ab, Bb, "bf16", (256, 256, 2), chunk=c), C64)
+    # whole-tile schedule: a cut along K would shorten the chains by itself
+    e = {c: g.err_norm(gpu_gemm16(Ab, Bb, "bf16", (256, 256, 2), chunk=c, stream_k=0), C64)
          for c in (256, 2048, 0)}
     assert e[256] < e[2048] < e[0]
     assert e[256] <= 1e-6 and e[2048] <= TIGHT and e[0] <= 5e-5

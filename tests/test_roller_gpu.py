@@ -117,13 +117,13 @@ def test_calibrate_measures_per_kblock_times():
         assert (top.block_tile, top.cta_group) == ([256, 256], 2)
 
 
-def test_split_k_hint_is_applied_and_pays():
-    """4096 x 64 x 8192 in 1xTF32: 32 tiles for 148 SMs. The hint asks for a cut along K,
-    `Compiler` applies it, the result stays within the 1xTF32 band and the launch gets faster."""
+def test_cut_along_k_pays_on_an_underfilled_grid():
+    """4096 x 64 x 8192 in 1xTF32: 32 tiles for 148 SMs. By default the library deals the
+    tiles out along K; the result stays within the 1xTF32 band and the launch gets faster than
+    with whole tiles."""
     M, N, K = 4096, 64, 8192
     cfg = MatmulConfig(M, N, K, 32)
     hint = get_roller_hints(cfg, B200(), topk=1, mode=1)[0]
-    assert hint.split_k > 1
     A, Bm = g.make_inputs(M, N, K, "uniform", seed=3)
     dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(Bm).cuda()
     dC = torch.empty(M, N, device="cuda")
