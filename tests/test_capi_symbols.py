@@ -71,3 +71,50 @@ def test_product_does_not_import_the_oracle():
     for src in list(pkg.glob("*.py")) + list((pkg / "csrc").glob("*")):
         text = src.read_text()
         assert "oracle" not in text, f"{src} mentions the oracle"
+
+
+C_CALLER = r"""
+#include <stdio.h>
+#include "roller_b200.h"
+int main(void) {
+  int n = roller_b200_kernel_count();
+  int i;
+  printf("%d\n", n);
+  for (i = 0; i < n; ++i) {
+    roller_ktile t;
+    if (roller_b200_kernel_desc(i, &t) != ROLLER_OK) return 2;
+    printf("%d %d %d %d\n", t.block_m, t.block_n, t.cta_group, t.layout);
+  }
+  {
+    roller_plan* plan = 0;
+    if (roller_b200_gemm_create(0, 1, 1, 1, 1, 1, 1, ROLLER_MODE_3XTF32, 0, &plan) != ROLLER_ERR_INVALID)
+      return 3;
+  }
+  printf("%s\n", roller_b200_strerror(ROLLER_ERR_TIMEOUT));
+  return 0;
+}
+"""
+
+
+def test_header_is_plain_c_and_links_from_a_c_program(tmp_path):
+    """The boundary is a C ABI: the header compiles as strict C99 and a C program that links
+    the library enumerates the same rTiles as the Python binding."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        import pytest
+        pytest.skip("no C compiler")
+    src = tmp_path / "caller.c"
+    src.write_text(C_CALLER)
+    exe = tmp_path / "caller"
+    libdir = str(_lib.LIB_PATH.parent)
+    subprocess.run([gcc, "-std=c99", "-pedantic", "-Wall", "-Werror", f"-I{HEADER.parent}", str(src),
+                    "-o", str(exe), f"-L{libdir}", "-lroller_b200", f"-Wl,-rpath,{libdir}"],
+                   check=True, capture_output=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split("\n")
+    tiles = _lib.kernel_tiles()
+    assert int(out[0]) == len(tiles)
+    for line, kt in zip(out[1:], tiles):
+        assert [int(x) for x in line.split()] == [kt.block_m, kt.block_n, kt.cta_group, kt.layout]
+    assert out[1 + len(tiles)].startswith("a bounded")
