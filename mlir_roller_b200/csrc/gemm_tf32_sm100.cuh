@@ -161,7 +161,7 @@ struct GemmCfg {
   static_assert(BN % (32 * CG) == 0, "each CTA stages whole 32-column boxes of B");
   static_assert(DT == 0 || MODE == 1, "split precision exists for fp32 operands only");
   static_assert(EPI_COLS % 16 == 0, "epilogue threads read whole 16-column slabs");
-  static_assert(TRANSPOSE_C || EPI_COLS % 32 == 0, "row-major C is stored in 32-column pieces");
+  static_assert(EPI_COLS % 32 == 0 || EPI_COLS == 16, "C is stored in pieces of 32 (or 16) columns");
   static_assert(TMEM_COLS == 64 || TMEM_COLS == 128 || TMEM_COLS == 256 || TMEM_COLS == 512,
                 "power of two");
   static_assert(LAYOUT != 2 || CG == 1, "the skinny layout runs on single CTAs");
@@ -444,6 +444,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------------------------------------ accumulate + epilogue
     if constexpr (Cfg::REBALANCE) setmaxnreg_inc<Cfg::REGS_EPI>();
     constexpr int COLS = Cfg::EPI_COLS;
+    constexpr int PIECE = COLS < 32 ? COLS : 32;   // columns of row-major C stored at a time
     const int quarter = warp & 3;  // TMEM lanes a warp may read: 32 * (warp id mod 4)
     const int half = (warp - Cfg::FIRST_EPI_WARP) >> 2;
     const int et = static_cast<int>(threadIdx.x) - Cfg::FIRST_EPI_WARP * 32;  // 0..255
@@ -563,17 +564,17 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           unsigned short* crow =
               reinterpret_cast<unsigned short*>(C) + static_cast<size_t>(row) * static_cast<size_t>(ldc);
 #pragma unroll
-          for (int c = 0; c < COLS / 32; ++c) {
-            const int col0 = n0 + c * 32;
+          for (int c = 0; c < COLS / PIECE; ++c) {
+            const int col0 = n0 + c * PIECE;
             if (col0 >= N) break;
             unsigned short* dst = crow + col0;
-            if (vec_store && col0 + 32 <= N) {
+            if (vec_store && col0 + PIECE <= N) {
               uint4* dst4 = reinterpret_cast<uint4*>(dst);   // 8 elements per 128-bit store
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
+              for (int j = 0; j < PIECE / 8; ++j) {
                 float v[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] = sum[c * 32 + 8 * j + e];
+                for (int e = 0; e < 8; ++e) v[e] = sum[c * PIECE + 8 * j + e];
                 if (accumulate) {
                   const uint4 old = dst4[j];
                   const uint32_t w[4] = {old.x, old.y, old.z, old.w};
@@ -588,9 +589,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               }
             } else {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
+              for (int j = 0; j < PIECE; ++j) {
                 if (col0 + j < N) {
-                  float o = sum[c * 32 + j];
+                  float o = sum[c * PIECE + j];
                   if (accumulate) o += from_16bit<Cfg::DT>(dst[j]);
                   dst[j] = static_cast<unsigned short>(to_16bit<Cfg::DT>(o));
                 }
@@ -601,16 +602,16 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       } else if (row < M) {
         float* crow = C + static_cast<size_t>(row) * static_cast<size_t>(ldc);
 #pragma unroll
-        for (int c = 0; c < COLS / 32; ++c) {
-          const int col0 = n0 + c * 32;
+        for (int c = 0; c < COLS / PIECE; ++c) {
+          const int col0 = n0 + c * PIECE;
           if (col0 >= N) break;
           float* dst = crow + col0;
-          if (vec_store && col0 + 32 <= N) {
+          if (vec_store && col0 + PIECE <= N) {
             float4* dst4 = reinterpret_cast<float4*>(dst);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float4 o = make_float4(sum[c * 32 + 4 * j], sum[c * 32 + 4 * j + 1],
-                                     sum[c * 32 + 4 * j + 2], sum[c * 32 + 4 * j + 3]);
+            for (int j = 0; j < PIECE / 4; ++j) {
+              float4 o = make_float4(sum[c * PIECE + 4 * j], sum[c * PIECE + 4 * j + 1],
+                                     sum[c * PIECE + 4 * j + 2], sum[c * PIECE + 4 * j + 3]);
               if (accumulate) {
                 const float4 old = dst4[j];
                 o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
@@ -619,9 +620,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
           } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
+            for (int j = 0; j < PIECE; ++j) {
               if (col0 + j < N) {
-                float o = sum[c * 32 + j];
+                float o = sum[c * PIECE + j];
                 if (accumulate) o += dst[j];
                 dst[j] = o;
               }
