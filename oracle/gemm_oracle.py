@@ -226,5 +226,17 @@ def gemm_3xtf32_c(A: np.ndarray, B: np.ndarray, chunk: int = 128) -> np.ndarray:
     return C
 
 
+def gemm_16bit_c(Ab: np.ndarray, Bb: np.ndarray, kind: str, chunk: int = 2048) -> np.ndarray:
+    """The C restatement of the 16-bit kernels' arithmetic on bf16 / fp16 bit patterns."""
+    lib = _c()
+    Ab = np.ascontiguousarray(Ab, dtype=np.uint16)
+    Bb = np.ascontiguousarray(Bb, dtype=np.uint16)
+    M, K = Ab.shape
+    N = Bb.shape[1]
+    C = np.empty((M, N), dtype=np.float32)
+    lib.oracle_gemm_16bit(_ptr(Ab), _ptr(Bb), _ptr(C), M, N, K, {"bf16": 0, "f16": 1}[kind], chunk)
+    return C
+
+
 def host_threads() -> int:
     return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)

@@ -144,3 +144,31 @@ def test_bf16_and_f16_conversions():
     assert f[9] == 65504.0 and f[10] == np.inf and f[11] == 0.0
     with pytest.raises(ValueError):
         g.make_inputs_16(2, 2, 2, "fp8")
+
+
+@pytest.mark.parametrize("name", CASES16)
+def test_c_restatement_of_the_16_bit_arithmetic(name):
+    kind = "bf16" if name.startswith("bf16") else "f16"
+    Ab, Bb = GOLDEN16[f"{name}/A"], GOLDEN16[f"{name}/B"]
+    Av, Bv = _values16(name)
+    C64 = GOLDEN16[f"{name}/C64"]
+    for chunk in (16, 64, 4096):
+        Cc = g.gemm_16bit_c(Ab, Bb, kind, chunk=chunk)
+        assert g.err_norm(Cc, C64) < 5e-7
+        # same model as the numpy one (the fp64 partial sums may differ in their last bit)
+        assert np.abs(Cc - g.emulate_16bit(Av, Bv, chunk=chunk)).max() <= 1e-6 * np.abs(C64).max()
+
+
+def test_c_decoding_of_16_bit_patterns():
+    """Every fp16 and a sweep of bf16 bit patterns through a 1 x 1 x 1 product with 1.0."""
+    one16 = {"bf16": np.uint16(0x3F80), "f16": np.uint16(0x3C00)}
+    for kind, conv in (("f16", g.from_f16_bits), ("bf16", g.from_bf16_bits)):
+        pats = np.arange(0, 65536, 1 if kind == "f16" else 7, dtype=np.uint32).astype(np.uint16)
+        A = pats.reshape(-1, 1)
+        B = np.array([[one16[kind]]], dtype=np.uint16)
+        with np.errstate(invalid="ignore"):
+            got = g.gemm_16bit_c(A, B, kind)[:, 0]
+        want = conv(pats)
+        assert np.array_equal(np.isnan(got), np.isnan(want))
+        ok = ~np.isnan(want)
+        assert np.array_equal(got[ok], want[ok])
