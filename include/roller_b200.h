@@ -124,7 +124,9 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
 
 /* Replaces cuda_func(grid, block, (A, B, C), shared_mem=...) (src/roller.py:545-550): enqueue one
  * GEMM on `stream`. No allocation, no synchronisation. A and B point to elements of the type
- * the plan's mode names; C is fp32 unless the plan was made with ROLLER_FLAG_C_16BIT. */
+ * the plan's mode names; C is fp32 unless the plan was made with ROLLER_FLAG_C_16BIT. Because
+ * it only enqueues, the call may be made on a capturing stream; replays of the captured graph
+ * run the same launch on the same pointers (tested with the stream-K schedule active). */
 int roller_b200_gemm_run(roller_plan* plan, const void* A, const void* B, void* C, void* stream);
 
 /* Replaces the timed loop of run_eval (src/roller.py:564-584): `warmup` untimed launches, then

@@ -531,6 +531,11 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const float4 q = __ldcg(slot + j * 256 + et);
             sum[4 * j] += q.x; sum[4 * j + 1] += q.y; sum[4 * j + 2] += q.z; sum[4 * j + 3] += q.w;
           }
+          // Hand the slot back (each slot has exactly one reader per launch): with the flag at
+          // zero again, a replay of this very launch -- a captured CUDA graph re-issues the
+          // same epoch -- cannot take the old contents for new ones.
+          epi_bar_sync();
+          if (et == 0) st_release_gpu(sk_flags + p * CG + cta_rank, 0u);
           if (sched.unit_begin(p) <= tile_u0) break;  // worker p started the tile
         }
         if (!ok) break;

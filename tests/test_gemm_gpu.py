@@ -398,3 +398,32 @@ def test_linearity_in_scale():
     A, B = g.make_inputs(256, 256, 512, "normal", seed=17)
     base = gpu_gemm(A, B, (256, 256, 2), 3)
     assert np.array_equal(gpu_gemm(A * np.float32(4), B, (256, 256, 2), 3), base * np.float32(4))
+
+
+@pytest.mark.parametrize("mode", [1, 3])
+def test_launches_can_be_replayed_from_a_cuda_graph(mode):
+    """`roller_b200_gemm_run` only enqueues (no allocation, no synchronisation), so a launch can
+    be captured into a CUDA graph; replays see new operand contents, also with the stream-K
+    schedule, whose hand-over flags are returned to zero by their readers."""
+    M, N, K = 2304, 2304, 1024          # 81 pair tiles on 74 CTA pairs: leftover tiles
+    A, B = g.make_inputs(M, N, K, "uniform", seed=21)
+    dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    dC = torch.empty(M, N, device="cuda")
+    plan = _lib.GemmPlan(_lib.find_tile(256, 256, 2), M, N, K, mode=mode)
+    if mode == 1:
+        plan.set_chunk(256)
+    plan.set_stream_k(1)
+    plan.run(dA, dB, dC)                # first call outside the capture: tensor maps, warm-up
+    torch.cuda.synchronize()
+    eager = dC.clone()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        plan.run(dA, dB, dC)
+    for scale in (1.0, 2.0, 4.0):       # powers of two: results scale exactly
+        dA.copy_(torch.from_numpy(A).cuda() * scale)
+        dC.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        plan.check_status()
+        assert torch.equal(dC, eager * scale)
+    plan.destroy()
