@@ -113,6 +113,9 @@ class ClockSampler:
         sm, mx, power, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         inside = [r for r in self.rows if r and self._inside(r[0])]
+        fallback = not inside and bool(self.rows)
+        if fallback:            # no stamp could be matched to the region: report every sample
+            inside = list(self.rows)
         for r in inside:
             try:
                 sm.append(float(r[1]))
@@ -127,7 +130,9 @@ class ClockSampler:
                 "sm_max_mhz": max(mx) if mx else None,
                 "samples": len(sm), "samples_outside_timed_region": len(self.rows) - len(inside),
                 "power_w_median": statistics.median(power) if power else None,
-                "reasons": sorted(reasons)}
+                "reasons": sorted(reasons),
+                **({"note": "no sample stamped inside the timed region; all samples used"}
+                   if fallback else {})}
 
 
 # ------------------------------------------------------------------ CPU baseline / reference arm

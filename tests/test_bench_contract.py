@@ -65,3 +65,32 @@ SHAPES = [(2048, 2048, 2048), (2048, 2048, 8192), (2048, 4096, 2048), (2048, 409
           (2048, 8192, 2048), (2048, 8192, 4096), (2048, 8192, 8192), (4096, 2048, 2048),
           (4096, 4096, 8192), (4096, 8192, 2048), (4096, 8192, 4096), (8192, 2048, 8192),
           (8192, 4096, 2048), (8192, 4096, 4096)]
+
+
+def test_clock_sampler_keeps_only_samples_of_the_timed_region():
+    import datetime
+    sys.path.insert(0, str(ROOT))
+    import bench
+
+    class Done:
+        def terminate(self):
+            pass
+
+        def wait(self, timeout=None):
+            pass
+
+    fmt = "%Y/%m/%d %H:%M:%S.%f"
+    now = datetime.datetime.now()
+    s = bench.ClockSampler(0)
+    s.proc = Done()
+    s.rows = [[(now + datetime.timedelta(milliseconds=20 * i)).strftime(fmt)[:-3], str(1500 + i), "1965",
+               "800.0", "0x4", "Not Active", "Not Active", "Not Active", "Active"] for i in range(10)]
+    s.t_begin = now + datetime.timedelta(milliseconds=50)
+    s.t_end = now + datetime.timedelta(milliseconds=130)
+    rec = s.stop()
+    assert rec["samples"] == 4 and rec["samples_outside_timed_region"] == 6
+    assert rec["sm_mhz"] == 1504.5 and rec["sm_max_mhz"] == 1965.0 and rec["reasons"] == ["sw_power_cap"]
+    s.rows = [["not a stamp", "1700", "1965", "800.0", "0x4", "Not Active", "Not Active", "Not Active",
+               "Not Active"]]
+    rec = s.stop()
+    assert rec["samples"] == 1 and "note" in rec and rec["reasons"] == []
