@@ -10,11 +10,15 @@ the timed region; the sweep touches ~3.2 GB per pass, so every GEMM finds its op
 from the 126 MB L2. Times are CUDA-event times on the launching stream, max over ranks.
 
 With N > 1 (launched by torchrun, one rank per GPU) every rank runs the same sweep as its row
-shard of an N-times-taller GEMM (operands replicated, no data-path collective): weak scaling.
-The strong-scaling shapes of the sharded configurations (8192x4096x4096 row-sharded, and
-16384^3 row-sharded and on a 4x2 grid at N = 8) are timed as well and reported under "strong":
-the kernels alone, with an NCCL gather of C, and with the exchange of C overlapped with the
-computation.
+shard of an N-times-taller GEMM (operands replicated, no data-path collective): weak scaling,
+i.e. the headline `value` at N > 1 is N replicas of the sweep. The sharded configurations
+(8192x4096x4096 row-sharded; 16384^3 row-sharded and on a 4x2 grid at N = 8) are timed as well
+and recorded under roofline.strong: the kernels alone, with an NCCL gather of C, with the
+exchange of C overlapped with the computation (copy engines, or fused into the kernel), each
+with the error of the delivered C against fp64 on sampled rows.
+
+What the driver keeps of the JSON line verbatim are the `config` and `roofline` objects, so the
+per-shape table, the ragged/skinny shapes and the sharded jobs are recorded inside `roofline`.
 
 `--impl reference` times the reference's CPU path for the same workload (numpy fp32 matmul on
 the host cores + the CPU restatement of its rTile search under oracle/), rank 0 only.
@@ -49,6 +53,17 @@ WORKLOAD = "README sweep M0-M13 fp32 GEMMs, uniform[-1,1) seeded inputs, one rTi
 
 def sweep_flops(shapes=README_SHAPES) -> float:
     return float(sum(2 * m * n * k for m, n, k in shapes))
+
+
+def workload_config(world: int) -> dict:
+    """The `config` object, the same for both arms."""
+    return {"workload": WORKLOAD, "mode": "3xTF32",
+            "l2": "inputs larger than L2: one sweep touches ~3.2 GB, L2 is 126 MB",
+            "parallelism": ("1 GPU" if world == 1 else
+                            f"{world} replicas: each rank runs the sweep as the row shard of a "
+                            f"{world}x taller GEMM, operands replicated, no collective; the "
+                            "headline value is replica scaling, the sharded jobs are under "
+                            "roofline.strong")}
 
 
 # ------------------------------------------------------------------ clocks
@@ -194,7 +209,7 @@ def run_reference_arm(args) -> None:
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_secs / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": {"workload": WORKLOAD},
+        "data": "synthetic", "config": workload_config(args.gpus),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": sample, "search_ms": statistics.mean(searches)},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -238,18 +253,24 @@ def measure_tf32_library_peak(torch, seconds: float = 1.0):
 
 
 class ShapeCase:
-    """One README shape bound to its selected kernel, with resident seeded operands."""
+    """One shape bound to its selected kernel, with resident seeded operands."""
 
-    def __init__(self, torch, idx, shape, mode, arch, measure=True):
+    def __init__(self, torch, idx, shape, mode, arch, measure=True, dist_name="uniform",
+                 seed=None):
         from mlir_roller_b200 import roller
         from mlir_roller_b200.analyze import MatmulConfig
+        self.torch = torch
         self.idx, self.shape, self.mode = idx, shape, mode
         m, n, k = shape
         g = torch.Generator(device="cuda")
-        g.manual_seed(idx)
+        g.manual_seed(idx if seed is None else seed)
         dt = roller.operand_dtype(mode)      # fp32, or bf16 / fp16 for the 16-bit modes
-        self.A = (torch.rand(m, k, device="cuda", generator=g) * 2 - 1).to(dt)
-        self.B = (torch.rand(k, n, device="cuda", generator=g) * 2 - 1).to(dt)
+        if dist_name == "normal":
+            self.A = torch.randn(m, k, device="cuda", generator=g).to(dt)
+            self.B = torch.randn(k, n, device="cuda", generator=g).to(dt)
+        else:
+            self.A = (torch.rand(m, k, device="cuda", generator=g) * 2 - 1).to(dt)
+            self.B = (torch.rand(k, n, device="cuda", generator=g) * 2 - 1).to(dt)
         self.C = torch.empty(m, n, device="cuda")
         cfg = MatmulConfig(m, n, k, 16 if dt != torch.float32 else 32)
         t0 = time.perf_counter()
@@ -258,6 +279,7 @@ class ShapeCase:
         self.select_ms = (time.perf_counter() - t0) * 1e3
         self.plan = self.fn.plan
         self.ptrs = (self.A.data_ptr(), self.B.data_ptr(), self.C.data_ptr())
+        self.rotation = None
 
     def launch(self):
         self.plan.run_ptr(*self.ptrs)
@@ -266,11 +288,53 @@ class ShapeCase:
         m, n, k = self.shape
         return 2.0 * m * n * k
 
+    def bytes(self):
+        m, n, k = self.shape
+        return self.A.element_size() * (m * k + k * n) + 4.0 * m * n
+
     def error(self, torch):
         self.launch()
         torch.cuda.synchronize()
         c64 = self.A.double() @ self.B.double()
         return float((self.C.double() - c64).abs().max() / c64.abs().max())
+
+    def loop_ms(self, reps, warmup=3, l2_bytes=126e6):
+        """Mean ms of `reps` launches issued back to back between two events, as the
+        reference times a hint (src/roller.py:564-584). Shapes whose operands would stay in
+        L2 from one launch to the next rotate through copies of them (each copy bound to a
+        plan of its own), so that every launch finds its operands evicted."""
+        from mlir_roller_b200 import _lib, roller
+        torch = self.torch
+        if self.rotation is None:
+            sets = max(1, int(-(-2.4 * l2_bytes // self.bytes())))
+            self.rotation = [(self.plan, self.ptrs, None)]
+            tile = roller.kernel_tile_for(self.hint)
+            m, n, k = self.shape
+            for _ in range(sets - 1):
+                keep = (self.A.clone(), self.B.clone(), torch.empty_like(self.C))
+                plan = _lib.GemmPlan(tile, m, n, k, mode=self.mode)
+                self.rotation.append((plan, tuple(t.data_ptr() for t in keep), keep))
+        rot = self.rotation
+        for i in range(warmup * len(rot)):
+            plan, ptrs, _ = rot[i % len(rot)]
+            plan.run_ptr(*ptrs)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(reps):
+            plan, ptrs, _ = rot[i % len(rot)]
+            plan.run_ptr(*ptrs)
+        e1.record()
+        e1.synchronize()
+        for plan, _, _ in rot:
+            plan.check_status()
+        return e0.elapsed_time(e1) / reps
+
+    def release_rotation(self):
+        if self.rotation:
+            for plan, _, keep in self.rotation[1:]:
+                plan.destroy()
+        self.rotation = None
 
 
 def measure_pcie(torch, mib: int = 512):
@@ -333,7 +397,9 @@ class SixteenBitOutCase:
 
 
 def timed_sweep(torch, cases, steps, warmup, dist=None):
-    """Returns (ms per step, per-shape mean ms). Barrier + synchronize on both sides."""
+    """ms per step (one pass over `cases`), launches issued back to back with an event at
+    every pass boundary and nothing between the launches of a pass. Barrier + synchronize on
+    both sides."""
     for _ in range(warmup):
         for c in cases:
             c.launch()
@@ -341,21 +407,17 @@ def timed_sweep(torch, cases, steps, warmup, dist=None):
     if dist is not None:
         dist.barrier()
         torch.cuda.synchronize()
-    n = len(cases)
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(n + 1)] for _ in range(steps)]
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    ev[0].record()
     for s in range(steps):
-        ev[s][0].record()
-        for i, c in enumerate(cases):
+        for c in cases:
             c.launch()
-            ev[s][i + 1].record()
+        ev[s + 1].record()
     torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
         torch.cuda.synchronize()
-    total_ms = sum(ev[s][0].elapsed_time(ev[s][n]) for s in range(steps)) / steps
-    per_shape = [sum(ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(steps)) / steps
-                 for i in range(n)]
-    return total_ms, per_shape
+    return ev[0].elapsed_time(ev[steps]) / steps
 
 
 def e2e_sweep(torch, cases, steps):
@@ -393,17 +455,71 @@ def e2e_sweep(torch, cases, steps):
     return e0.elapsed_time(e1) / steps, h2d, d2h, checksum
 
 
-def strong_scaling(torch, dist, rank, world, steps, warmup, mode):
-    """Strong-scaling shapes of the sharded configurations. Per job: the local kernels alone
-    ("compute"), followed by an NCCL gather of C to rank 0 ("with_gather"), and with the exchange
-    of C running underneath the computation over symmetric memory, to rank 0
-    ("overlapped_root") and to every rank ("overlapped_all"). Returns a list of records
-    (identical on all ranks); times are the max over ranks."""
+def _block_rows_operand(torch, rows, K, seed, row_block):
+    """A's rows of one row block of the process grid: any rank can regenerate any block."""
+    g = torch.Generator(device="cuda")
+    g.manual_seed(seed * 1000 + 17 * row_block + 1)
+    return torch.rand(rows, K, device="cuda", generator=g) * 2 - 1
+
+
+def _sample_rows(blocks, bands_of):
+    """Global rows of C to check against fp64: first and last row of every block and of every
+    band a block is cut into, plus the rows either side of the first 256-row tile boundary."""
+    rows = set()
+    for b in blocks:
+        if b.rows <= 0 or b.cols <= 0:
+            continue
+        rows.update((b.row0, b.row1 - 1, b.row0 + b.rows // 2))
+        for r0, r1 in bands_of(b):
+            rows.update((r0, r1 - 1))
+        if b.rows > 256:
+            rows.update((b.row0 + 255, b.row0 + 256))
+    return sorted(rows)
+
+
+class _Checker:
+    """fp64 reference (cuBLAS DGEMM on this rank's GPU) of sampled rows of the sharded C."""
+
+    def __init__(self, torch, blocks, grid, K, N, seed, B_full, bands_of):
+        self.torch = torch
+        self.rows = _sample_rows(blocks, bands_of)
+        gn = grid[1]
+        a_rows = []
+        cache = {}
+        for r in self.rows:
+            b = next(x for x in blocks if x.row0 <= r < x.row1 and x.col0 == 0)
+            i = b.rank // gn
+            if i not in cache:
+                cache[i] = _block_rows_operand(torch, b.rows, K, seed, i)
+            a_rows.append(cache[i][r - b.row0])
+        a = torch.stack(a_rows).double()
+        del cache
+        self.ref = a @ B_full.double()
+        self.scale = float(self.ref.abs().max())
+        self.index = torch.tensor(self.rows, device="cuda")
+
+    def err(self, C_full):
+        """max |C - ref| / max |ref| over the sampled rows of the whole M x N matrix. NaN (an
+        element never written) propagates."""
+        d = (C_full[self.index].double() - self.ref).abs().max()
+        return float(d) / self.scale
+
+
+def strong_scaling(torch, dist, rank, world, steps, warmup):
+    """The sharded configurations. Per job and mode: the local kernels alone ("kernels"), followed
+    by an NCCL gather of C to rank 0 ("gather"), with the exchange of C running underneath the
+    computation through the copy engines to rank 0 ("banded_root") and to every rank
+    ("banded_all"), and fused into the kernel ("fused_root": the kernel's TMA unit stores the
+    tiles straight into rank 0's C, progressive schedule, closed by flags). After timing, each
+    path runs once more into a NaN-filled C and the delivered matrix is compared with fp64 on
+    sampled rows. Returns a list of compact records (identical on all ranks); times are the max
+    over ranks, errors the max over the ranks that hold a result."""
     from mlir_roller_b200 import mgpu
-    jobs = [("M13 8192x4096x4096 row-sharded", (8192, 4096, 4096), (world, 1), 13)]
+    from mlir_roller_b200.analyze import MODE_1XTF32, MODE_3XTF32
+    jobs = [("M13_rows", (8192, 4096, 4096), (world, 1), 13, (MODE_3XTF32, MODE_1XTF32))]
     if world == 8:
-        jobs.append(("16384^3 row-sharded", (16384, 16384, 16384), (8, 1), 0))
-        jobs.append(("16384^3 on a 4x2 grid", (16384, 16384, 16384), (4, 2), 0))
+        jobs.append(("16384_rows", (16384, 16384, 16384), (8, 1), 0, (MODE_3XTF32,)))
+        jobs.append(("16384_4x2", (16384, 16384, 16384), (4, 2), 0, (MODE_3XTF32, MODE_1XTF32)))
 
     def timed(fn):
         for _ in range(warmup):
@@ -422,53 +538,154 @@ def strong_scaling(torch, dist, rank, world, steps, warmup, mode):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def max_over_ranks(x):
+        # NaN must survive the reduction: send it as +inf
+        t = torch.tensor([float("inf") if x != x else x], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     out = []
-    for name, (M, N, K), grid, seed in jobs:
-        sg = mgpu.ShardedGemm(M, N, K, rank, world, grid=grid, mode=mode, measure=True)
-        b = sg.block
+    for name, (M, N, K), grid, seed, modes in jobs:
+        gm, gn = grid
         g = torch.Generator(device="cuda")
         g.manual_seed(seed)
-        # every rank holds its rows of A and the whole (replicated) B
-        A_rows = torch.rand(b.rows, K, device="cuda", generator=g) * 2 - 1
-        B_full = torch.rand(K, N, device="cuda", generator=g) * 2 - 1
-        C_blk = torch.empty(b.rows, b.cols, device="cuda")
-        C_full = torch.empty(M, N, device="cuda") if rank == 0 else None
-        rec = {"name": name, "grid": list(grid), "tile": sg.hint.block_tile if sg.hint else None}
+        B_full = torch.rand(K, N, device="cuda", generator=g) * 2 - 1     # replicated
+        for mode in modes:
+            sg = mgpu.ShardedGemm(M, N, K, rank, world, grid=grid, mode=mode, measure=True)
+            b = sg.block
+            A_rows = _block_rows_operand(torch, b.rows, K, seed, rank // gn)
+            C_blk = torch.empty(b.rows, b.cols, device="cuda")
+            C_full = torch.empty(M, N, device="cuda") if rank == 0 else None
+            rec = {"job": name, "mode": f"{mode}xTF32", "grid": f"{gm}x{gn}",
+                   "tile": "x".join(str(v) for v in (sg.hint.block_tile if sg.hint else []))}
+            flops = 2.0 * M * N * K
 
-        def put(label, ms):
-            rec[label + "_ms"] = ms
-            rec[label + "_tflops"] = 2.0 * M * N * K / ms / 1e9
+            rec["kernels_ms"] = timed(lambda: sg.run(A_rows, B_full, C_blk))
+            rec["gather_ms"] = timed(lambda: (sg.run(A_rows, B_full, C_blk),
+                                              sg.gather(C_blk, out=C_full)))
+            ob = mgpu.OverlappedGemm(M, N, K, rank, world, grid=grid, mode=mode, dest="root")
+            bands = list(ob.bands)
+            checker = _Checker(torch, ob.blocks, grid, K, N, seed, B_full,
+                               lambda blk: mgpu.split_bands(blk.row0, blk.row1, len(bands)))
+            # the gathered C of the run above (rank 0 holds it)
+            if rank == 0:
+                C_full.fill_(float("nan"))
+            torch.cuda.synchronize()
+            dist.barrier()
+            sg.run(A_rows, B_full, C_blk)
+            sg.gather(C_blk, out=C_full)
+            torch.cuda.synchronize()
+            rec["gather_err"] = max_over_ranks(checker.err(C_full) if rank == 0 else 0.0)
+            del C_full
+            sg.plan.check_status()
 
-        put("compute", timed(lambda: sg.run(A_rows, B_full, C_blk)))
-        put("with_gather", timed(lambda: (sg.run(A_rows, B_full, C_blk),
-                                          sg.gather(C_blk, out=C_full))))
-        del C_full
-        for dest in ("root", "all"):
-            try:
-                og = mgpu.OverlappedGemm(M, N, K, rank, world, grid=grid, mode=mode, dest=dest)
-            except Exception as e:  # noqa: BLE001 - no symmetric memory on this box: keep the rest
-                rec["overlapped_error"] = f"{type(e).__name__}: {e}"[:300]
-                break
-            put("overlapped_" + dest, timed(lambda: (og.run(A_rows, B_full), og.finish())))
-            rec["bands"] = len(og.bands)
-            for p in og.plans:
-                p.check_status()
-            og.destroy()
-            del og
+            paths = [("banded_root", ob, False), ("banded_all", None, True), ("fused_root", None, False)]
+            for label, og, everywhere in paths:
+                try:
+                    if og is None:
+                        og = mgpu.OverlappedGemm(M, N, K, rank, world, grid=grid, mode=mode,
+                                                 dest="all" if everywhere else "root",
+                                                 fused=(label == "fused_root"))
+                except Exception as e:  # noqa: BLE001 - keep the other paths' numbers
+                    rec[label + "_error"] = f"{type(e).__name__}: {e}"[:200]
+                    continue
+                rec[label + "_ms"] = timed(lambda: (og.run(A_rows, B_full), og.finish()))
+                og.C.fill_(float("nan"))
+                torch.cuda.synchronize()
+                dist.barrier()
+                og.run(A_rows, B_full)
+                og.finish()
+                torch.cuda.synchronize()
+                dist.barrier()
+                og.check_status()
+                holds = everywhere or rank == 0
+                rec[label + "_err"] = max_over_ranks(checker.err(og.C) if holds else 0.0)
+                if label == "banded_root":
+                    rec["bands"] = len(og.bands)
+                if label == "fused_root" and og.plans:
+                    info = og.plans[0].schedule_info()
+                    rec["fused_rounds"] = int(max_over_ranks(float(info["rounds"])))
+                og.destroy()
+                del og
+                torch.cuda.empty_cache()
+            del checker
+            # the same GEMM, unsharded, on this rank's GPU alone (the strong-scaling numerator)
+            A_full = torch.rand(M, K, device="cuda", generator=g) * 2 - 1
+            C_one = torch.empty(M, N, device="cuda")
+            one = mgpu.ShardedGemm(M, N, K, 0, 1, grid=(1, 1), mode=mode, measure=True)
+            rec["single_ms"] = timed(lambda: one.run(A_full, B_full, C_one))
+            one.plan.destroy()
+            del A_full, C_one, one
             torch.cuda.empty_cache()
-        # the same GEMM, unsharded, on this rank's GPU alone (the strong-scaling numerator)
-        A_full = torch.rand(M, K, device="cuda", generator=g) * 2 - 1
-        C_one = torch.empty(M, N, device="cuda")
-        one = mgpu.ShardedGemm(M, N, K, 0, 1, grid=(1, 1), mode=mode, measure=True)
-        put("single_gpu", timed(lambda: one.run(A_full, B_full, C_one)))
-        one.plan.destroy()
-        del A_full, C_one, one
+            # lower bound of any exchange that ends with C on one rank: its NVLink ingress at the
+            # measured 770 GB/s per direction
+            link_ms = (world - 1) / world * M * N * 4 / 770e9 * 1e3
+            rec["link_bound_ms"] = link_ms
+            best_root = min(rec.get(k, float("inf")) for k in ("banded_root_ms", "fused_root_ms",
+                                                               "gather_ms"))
+            rec["delivered_root_ms"] = best_root
+            rec["ingress_gbs"] = (world - 1) / world * M * N * 4 / best_root / 1e6
+            rec["eff_kernels"] = rec["single_ms"] / (world * rec["kernels_ms"])
+            rec["eff_delivered_root"] = rec["single_ms"] / (world * best_root)
+            rec["eff_ceiling"] = rec["single_ms"] / (world * max(link_ms, rec["kernels_ms"]))
+            rec["tflops_delivered_root"] = flops / best_root / 1e9
+            out.append({k: (round(v, 5) if isinstance(v, float) and v == v and abs(v) < 1e30
+                            and k.endswith(("_ms", "_gbs")) else v) for k, v in rec.items()})
+            sg.plan.destroy()
+            del A_rows, C_blk, sg
+            torch.cuda.empty_cache()
+        del B_full
         torch.cuda.empty_cache()
-        # lower bound of any exchange that ends with C on one rank: its ingress over NVLink
-        rec["gather_link_bound_ms"] = (world - 1) / world * M * N * 4 / 770e9 * 1e3
-        out.append(rec)
-        del A_rows, B_full, C_blk, sg
-        torch.cuda.empty_cache()
+    return out
+
+
+CONFIG4_SHAPES = [("ragged", (4097, 2049, 8193)), ("skinny", (16, 8192, 8192))]
+HBM_GBS_FALLBACK = 6650.0
+
+
+def config4_records(torch, arch, peak_tf32, hbm_gbs, reps):
+    """The ragged and the skinny GEMM (normal(0,1) inputs, seed 0), both modes: time per launch in
+    a back-to-back loop, fraction of t_roof = max(flops / P_tf32, bytes / BW_hbm), error against
+    fp64. For the ragged shape, whose rows are not multiples of 16 bytes, the same kernel is
+    also timed on operands that were padded beforehand: the difference is what the two staging
+    copies inside every launch cost."""
+    from mlir_roller_b200 import _lib, roller
+    from mlir_roller_b200.analyze import MODE_1XTF32, MODE_3XTF32
+    out = []
+    for name, shape in CONFIG4_SHAPES:
+        m, n, k = shape
+        for mode in (MODE_3XTF32, MODE_1XTF32):
+            case = ShapeCase(torch, 0, shape, mode, arch, True, dist_name="normal", seed=0)
+            err = case.error(torch)
+            ms = case.loop_ms(reps)
+            flops = (3 if mode == MODE_3XTF32 else 1) * 2.0 * m * n * k
+            t_roof_ms = max(flops / (peak_tf32 * 1e9), case.bytes() / (hbm_gbs * 1e6))
+            rec = {"shape": name, "mnk": list(shape), "mode": f"{mode}xTF32",
+                   "tile": "x".join(str(v) for v in case.hint.block_tile) + f"/cg{case.hint.cta_group}"
+                           + ("/skinny" if getattr(case.hint, "layout", 0) == 2 else ""),
+                   "us": ms * 1e3, "frac_of_t_roof": t_roof_ms / ms,
+                   "bound": "tensor" if flops / (peak_tf32 * 1e9) >= case.bytes() / (hbm_gbs * 1e6)
+                   else "hbm",
+                   "tflops": 2.0 * m * n * k / ms / 1e9, "gbs": case.bytes() / ms / 1e6, "err": err}
+            if k % 4 or n % 4:
+                # the same product with the operands padded once, outside the timed loop
+                kp, np_ = -(-k // 4) * 4, -(-n // 4) * 4
+                Ap = torch.zeros(m, kp, device="cuda"); Ap[:, :k] = case.A
+                Bp = torch.zeros(k, np_, device="cuda"); Bp[:, :n] = case.B
+                Cp = torch.empty(m, np_, device="cuda")
+                plan = _lib.GemmPlan(roller.kernel_tile_for(case.hint), m, n, k, lda=kp, ldb=np_,
+                                     ldc=np_, mode=mode)
+                ms_aligned = plan.time(Ap, Bp, Cp, warmup=3, iters=reps)
+                plan.check_status()
+                plan.destroy()
+                rec["us_operands_prepadded"] = ms_aligned * 1e3
+                rec["staging_copies_share"] = max(0.0, 1.0 - ms_aligned / ms)
+                del Ap, Bp, Cp
+            case.release_rotation()
+            case.plan.destroy()
+            del case
+            torch.cuda.empty_cache()
+            out.append(rec)
     return out
 
 
@@ -500,7 +717,7 @@ def run_gpu_arm(args) -> None:
         c.plan.check_status()
 
     sampler.mark_begin()
-    step_ms, per_shape_ms = timed_sweep(torch, cases, args.steps, args.warmup, dist)
+    step_ms = timed_sweep(torch, cases, args.steps, args.warmup, dist)
     sampler.mark_end()
     clocks = sampler.stop() if rank == 0 else None
     if dist is not None:
@@ -511,28 +728,46 @@ def run_gpu_arm(args) -> None:
         c.plan.check_status()
     value = sweep_flops() * world / step_ms / 1e9
 
-    # 1xTF32 for the per-shape report (not part of `value`)
-    cases1 = [ShapeCase(torch, i, s, MODE_1XTF32, arch, measure) for i, s in enumerate(README_SHAPES)]
-    errs1 = [c.error(torch) for c in cases1]
-    _, per_shape_ms1 = timed_sweep(torch, cases1, max(args.steps // 2, 1), 1, None)
-    del cases1
-    torch.cuda.empty_cache()
+    # Per-shape table, both modes: each shape in a back-to-back loop of its own (rank 0's GPU is
+    # enough: every rank runs the same kernels on the same shapes).
+    loop_reps = max(args.steps, 10)
+    per_shape_ms = per_shape_ms1 = errs1 = tiles1 = None
+    step_ms16 = None
+    if rank == 0:
+        per_shape_ms = [c.loop_ms(loop_reps) for c in cases]
+        for c in cases:
+            c.release_rotation()
+        torch.cuda.empty_cache()
+        cases1 = [ShapeCase(torch, i, s, MODE_1XTF32, arch, measure)
+                  for i, s in enumerate(README_SHAPES)]
+        errs1 = [c.error(torch) for c in cases1]
+        per_shape_ms1 = [c.loop_ms(loop_reps) for c in cases1]
+        tiles1 = [(c.hint.block_tile, c.hint.cta_group) for c in cases1]
+        for c in cases1:
+            c.release_rotation()
+            c.plan.destroy()
+        del cases1
+        torch.cuda.empty_cache()
 
-    # bf16 operands (the 16-bit kernels of the same family), with the library's bf16 GEMM timed
-    # on the same operands right after; not part of `value` either
-    cases16 = [ShapeCase(torch, i, s, MODE_BF16, arch, measure) for i, s in enumerate(README_SHAPES)]
-    errs16 = [c.error(torch) for c in cases16]
-    step_ms16, per_shape_ms16 = timed_sweep(torch, cases16, max(args.steps // 2, 1), 2, None)
-    lib16 = [LibraryCase(torch, c) for c in cases16]
-    step_ms16_lib, _ = timed_sweep(torch, lib16, max(args.steps // 2, 1), 2, None)
-    out16 = [SixteenBitOutCase(torch, c) for c in cases16]
-    step_ms16_out, _ = timed_sweep(torch, out16, max(args.steps // 2, 1), 2, None)
-    for c in out16:
-        c.plan.check_status()
-        c.plan.destroy()
-    tiles16 = [(c.hint.block_tile, c.hint.cta_group) for c in cases16]
-    del cases16, lib16, out16
-    torch.cuda.empty_cache()
+        # bf16 operands (the 16-bit kernels of the same family), with the library's bf16 GEMM
+        # timed on the same operands right after; not part of `value` either
+        cases16 = [ShapeCase(torch, i, s, MODE_BF16, arch, measure)
+                   for i, s in enumerate(README_SHAPES)]
+        errs16 = [c.error(torch) for c in cases16]
+        half = max(args.steps // 2, 1)
+        step_ms16 = timed_sweep(torch, cases16, half, 2, None)
+        lib16 = [LibraryCase(torch, c) for c in cases16]
+        step_ms16_lib = timed_sweep(torch, lib16, half, 2, None)
+        out16 = [SixteenBitOutCase(torch, c) for c in cases16]
+        step_ms16_out = timed_sweep(torch, out16, half, 2, None)
+        for c in out16:
+            c.plan.check_status()
+            c.plan.destroy()
+        tiles16 = [(c.hint.block_tile, c.hint.cta_group) for c in cases16]
+        for c in cases16:
+            c.plan.destroy()
+        del cases16, lib16, out16
+        torch.cuda.empty_cache()
 
     e2e_ms, h2d, d2h, _ = e2e_sweep(torch, cases, max(args.steps // 2, 1))
     if dist is not None:
@@ -540,10 +775,15 @@ def run_gpu_arm(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     e2e_value = sweep_flops() * world / e2e_ms / 1e9
+    tiles3 = [(c.hint.block_tile, c.hint.cta_group) for c in cases]
+    for c in cases:
+        c.plan.destroy()
+    del cases
+    torch.cuda.empty_cache()
 
     strong = None
     if dist is not None:
-        strong = strong_scaling(torch, dist, rank, world, max(args.steps // 2, 2), 2, MODE_3XTF32)
+        strong = strong_scaling(torch, dist, rank, world, max(args.steps // 2, 3), 2)
 
     if rank != 0:
         if dist is not None:
@@ -557,31 +797,74 @@ def run_gpu_arm(args) -> None:
     t_down = d2h / (duplex_gbs * 1e6)
     e2e_bound_ms = t_down + max(h2d - t_down * duplex_gbs * 1e6, 0.0) / (up_gbs * 1e6)
 
-    # ---- roofline of the dominant kernel (the tcgen05 GEMM): algorithmic tensor flops
-    # (3 TF32 products per fp32 product) per launch over the mean launch duration.
+    # ---- roofline of the dominant kernel (the tcgen05 GEMM): algorithmic tensor flops (3 TF32
+    # products per fp32 product) of one step over the step's duration. The denominator is a
+    # library TF32 GEMM measured in this run (the driver-written peaks file has no TF32 entry)
+    # in the regime the timed region ran in: the best single launch ("burst") for a region
+    # shorter than a second -- the GPU has not reached its power-capped steady state by then --
+    # and the rate sustained over a second otherwise. The bf16 figures of the peaks file,
+    # halved, are printed beside it.
     burst_tf32, sustained_tf32 = measure_tf32_library_peak(torch)
     peaks_path = ROOT / "MEASURED_PEAKS.json"
     peaks = json.loads(peaks_path.read_text()) if peaks_path.exists() else {}
+    hbm_gbs = float(peaks.get("hbm_gbs", HBM_GBS_FALLBACK))
+    region_s = step_ms * args.steps / 1e3
+    burst_regime = region_s < 1.0
+    peak = burst_tf32 if burst_regime else sustained_tf32
+    if "bf16_tflops" in peaks and burst_regime:
+        peak = max(peak, peaks["bf16_tflops"] / 2)       # never a softer denominator than the file's
     tensor_flops = 3.0 * sweep_flops()
-    achieved = tensor_flops / sum(per_shape_ms) / 1e9
+    achieved = tensor_flops / step_ms / 1e9
+    shape_peak = max(burst_tf32, peaks.get("bf16_tflops", 0.0) / 2)   # loops of a few ms: burst
+
+    per_shape = []
+    for i, (shape, ms3, ms1) in enumerate(zip(README_SHAPES, per_shape_ms, per_shape_ms1)):
+        fl = 2.0 * shape[0] * shape[1] * shape[2]
+        per_shape.append({
+            "s": f"M{i}", "tile3": "x".join(map(str, tiles3[i][0])) + f"/cg{tiles3[i][1]}",
+            "us3": round(ms3 * 1e3, 2), "tf3": round(fl / ms3 / 1e9, 1),
+            "frac3": round(3 * fl / ms3 / 1e9 / shape_peak, 4), "err3": float(f"{errs[i]:.3g}"),
+            "tile1": "x".join(map(str, tiles1[i][0])) + f"/cg{tiles1[i][1]}",
+            "us1": round(ms1 * 1e3, 2), "tf1": round(fl / ms1 / 1e9, 1),
+            "frac1": round(fl / ms1 / 1e9 / shape_peak, 4), "err1": float(f"{errs1[i]:.3g}"),
+        })
+    config4 = config4_records(torch, arch, shape_peak, hbm_gbs, loop_reps)
+
     roofline = {
-        "bound": "tensor", "achieved": achieved, "peak": sustained_tf32, "unit": "TFLOP/s",
-        "frac": achieved / sustained_tf32,
+        "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+        "frac": achieved / peak,
         # DRAM bytes per launch: an ncu capture of this kernel at 4096 x 4096 x 2048 read+wrote
         # 1.13 x its algorithmic bytes 4(MK+KN+MN); scaled to the sweep's mean launch.
         "traffic": 1.13 * sum(4.0 * (m * k + k * n + m * n) for m, n, k in README_SHAPES)
         / len(README_SHAPES),
         "traffic_unit": "bytes per launch (mean over the 14 shapes), scaled from an ncu capture",
-        "peak_source": ("cuBLAS TF32 8192^3 sustained, measured in this run (MEASURED_PEAKS.json "
-                        "carries no TF32 entry); burst %.1f; bf16_tflops_sustained/2 = %.1f"
-                        % (burst_tf32, peaks.get("bf16_tflops_sustained", 1371.6) / 2)),
-        # the driver-measured file has no TF32 entry; its sustained bf16 figure halved is the
-        # nearest thing to a TF32 peak it offers
-        "peak_from_measured_peaks_file": peaks.get("bf16_tflops_sustained", 1371.6) / 2,
-        "frac_of_measured_peaks_file": achieved / (peaks.get("bf16_tflops_sustained", 1371.6) / 2),
+        "peak_regime": "burst" if burst_regime else "sustained",
+        "peak_source": ("library TF32 GEMM (cuBLAS through torch, 8192^3) measured in this run: "
+                        "burst %.1f, sustained over 1 s %.1f TFLOP/s; the timed region lasted "
+                        "%.2f s, so the %s figure is the denominator. MEASURED_PEAKS.json has no "
+                        "TF32 entry; its bf16 figures halved: burst %.1f, sustained %.1f"
+                        % (burst_tf32, sustained_tf32, region_s,
+                           "burst" if burst_regime else "sustained",
+                           peaks.get("bf16_tflops", float("nan")) / 2,
+                           peaks.get("bf16_tflops_sustained", float("nan")) / 2)),
+        "peak_tf32_burst": burst_tf32, "peak_tf32_sustained": sustained_tf32,
+        "frac_of_sustained": achieved / sustained_tf32,
         "flops_per_launch": "3 * 2*M*N*K (three TF32 MMAs per fp32 product)",
         "kernel": "rb200::gemm_tf32_kernel<GemmCfg<BN,3,CG>>",
+        "timed_region_s": region_s,
+        # per README shape, back-to-back loops of one shape each; frac = tensor flops / time /
+        # the burst peak (3x counted at 3 x 2MNK); err = max|C - C64| / max|C64|
+        "per_shape": per_shape,
+        "per_shape_min_frac3": min(r["frac3"] for r in per_shape),
+        "per_shape_min_frac1": min(r["frac1"] for r in per_shape),
+        "per_shape_peak": shape_peak,
+        "max_err_3x": max(errs), "max_err_1x": max(errs1),
+        # the ragged and the skinny GEMM of the tail / memory-bound configuration
+        "config4": config4,
+        "hbm_gbs_peak": hbm_gbs,
     }
+    if strong is not None:
+        roofline["strong"] = strong
 
     # ---- search timing: product search vs the reference's search (CPU restatement)
     from oracle import search_port
@@ -591,6 +874,9 @@ def run_gpu_arm(args) -> None:
         t0 = time.perf_counter(); get_roller_hints(cfg, arch, topk=20); t_new.append(time.perf_counter() - t0)
         t0 = time.perf_counter(); get_roller_hints(cfg, CUDA(), topk=20); t_a100.append(time.perf_counter() - t0)
         t0 = time.perf_counter(); search_port.roller_hints(m, n, k, topk=20); t_ref.append(time.perf_counter() - t0)
+    roofline["search_ms"] = {"b200_policy": statistics.mean(t_new) * 1e3,
+                             "a100_policy": statistics.mean(t_a100) * 1e3,
+                             "reference_port": statistics.mean(t_ref) * 1e3}
 
     # ---- CPU baseline on this box's host cores (bounded sample)
     from oracle import gemm_oracle
@@ -602,28 +888,12 @@ def run_gpu_arm(args) -> None:
         "search_ms_reference_port": statistics.mean(t_ref) * 1e3,
     }
 
-    per_shape = []
-    for i, (c, ms3, ms1) in enumerate(zip(cases, per_shape_ms, per_shape_ms1)):
-        fl = c.flops()
-        per_shape.append({
-            "shape": f"M{i}", "mnk": list(c.shape), "tile": c.hint.block_tile,
-            "cta_group": c.hint.cta_group,
-            "ms_3x": ms3, "tflops_3x": fl / ms3 / 1e9, "frac_3x": 3 * fl / ms3 / 1e9 / sustained_tf32,
-            "err_3x": errs[i],
-            "ms_1x": ms1, "tflops_1x": fl / ms1 / 1e9, "frac_1x": fl / ms1 / 1e9 / sustained_tf32,
-            "err_1x": errs1[i],
-        })
-
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "tf32x3 (fp32 in, fp32 accumulate/out)",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD, "mode": "3xTF32",
-                   "l2": "inputs larger than L2: one sweep touches ~3.2 GB, L2 is 126 MB",
-                   "parallelism": ("1 GPU" if world == 1 else
-                                   f"{world} ranks, each the row shard of a {world}x taller GEMM, "
-                                   "operands replicated, no collective")},
+        "config": workload_config(world),
         "clocks": clocks,
         "roofline": roofline,
         "cpu_baseline": cpu_baseline,
@@ -631,12 +901,7 @@ def run_gpu_arm(args) -> None:
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
                 "pcie_gbs": {"h2d": up_gbs, "d2h": down_gbs, "each_way_duplex": duplex_gbs},
                 "pcie_bound_ms": e2e_bound_ms},
-        "gpu_launches": len(cases) * args.steps,
-        "search_ms": {"b200_policy": statistics.mean(t_new) * 1e3,
-                      "a100_policy": statistics.mean(t_a100) * 1e3,
-                      "reference_port": statistics.mean(t_ref) * 1e3},
-        "max_err_3x": max(errs), "max_err_1x": max(errs1),
-        "per_shape": per_shape,
+        "gpu_launches": len(README_SHAPES) * args.steps,
         # the same sweep with bf16 operands (fp32 accumulate and C); rank 0's own GPU only
         "bf16": {
             "value": sweep_flops() / step_ms16 / 1e9, "unit": UNIT, "ms_per_step": step_ms16,
@@ -647,14 +912,9 @@ def run_gpu_arm(args) -> None:
                      if "bf16_tflops_sustained" in peaks else None),
             "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained (cuBLAS bf16 8192^3)",
             "max_err": max(errs16),
-            "per_shape": [{"shape": f"M{i}", "tile": t[0], "cta_group": t[1], "ms": ms,
-                           "tflops": 2.0 * m * n * k / ms / 1e9}
-                          for i, ((m, n, k), t, ms) in enumerate(zip(README_SHAPES, tiles16,
-                                                                     per_shape_ms16))],
+            "tiles": ["x".join(map(str, t[0])) + f"/cg{t[1]}" for t in tiles16],
         },
     }
-    if strong is not None:
-        line["strong"] = strong
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()

@@ -66,6 +66,37 @@ typedef enum roller_status {
                                  (one el_bits for A, B and C, src/analyze.py:31-49); sums are
                                  kept in fp32 and rounded to nearest even once, on the store */
 
+/* Options of roller_b200_gemm_set_option. */
+#define ROLLER_OPT_WAIT_LIMIT_CYCLES 1 /* clock cycles any device-side wait of the plan's launches
+                                          may last before the kernel gives up (0 = the default,
+                                          about two seconds) */
+#define ROLLER_OPT_OVERLAP_LAUNCH 2    /* 1 (default): launches carry the programmatic-stream-
+                                          serialization attribute, so a launch is scheduled while
+                                          the previous kernel of its stream winds down and sets up
+                                          its CTAs early; it still waits for that kernel's
+                                          completion before touching global memory. 0: plain
+                                          stream order */
+#define ROLLER_OPT_TMA_STORE 3         /* 1: C leaves each CTA through shared memory and TMA
+                                          stores instead of the accumulate warps' own stores, so
+                                          a slow destination (C in another GPU's memory, mapped
+                                          into this process) does not hold the warps up. Needs
+                                          fp32 C with 16-byte aligned base and row stride, no
+                                          ROLLER_FLAG_ACCUMULATE, and an rTile whose kernel has
+                                          the staging area (else ROLLER_ERR_UNSUPPORTED) */
+#define ROLLER_OPT_PROGRESSIVE_ROUNDS 4 /* n > 0: every tile is cut along K and the tiles are
+                                          worked through in n groups by the whole grid, so that
+                                          finished tiles leave the kernel at a steady rate from
+                                          early on rather than together at the end (rounded down
+                                          to a divisor of the tile count; at most 64). -1 = the
+                                          library picks n; 0 = off */
+#define ROLLER_OPT_TEST_DROP_PUBLISH 5 /* test aid, 1: workers that hand a partial tile to another
+                                          worker write it but never raise its flag, so the bounded
+                                          wait of the receiving worker runs out and the launch ends
+                                          with ROLLER_ERR_TIMEOUT. Nothing faults or hangs */
+
+/* Most flags one roller_b200_flag_signal_async call can raise. */
+#define ROLLER_MAX_FLAG_TARGETS 32
+
 /* Device facts feeding the B200 device model of the search (reference: the constants hard-coded
  * in arch.CUDA, src/arch.py:47-61). */
 typedef struct roller_dev_info {
@@ -161,6 +192,13 @@ int roller_b200_copy_block_async(float* dst, long long dst_ld, const float* src,
 int roller_b200_gemm_launch_info(const roller_plan* plan, int* grid, int* block, int* smem_bytes,
                                  int* tiles_m, int* tiles_n, int* max_clusters);
 
+/* How the plan deals its work out, which the reference fixes at one block per tile
+ * (src/roller.py:536): tiles cut along K (0 = none), the rounds they are worked through in
+ * (1 unless the progressive schedule is on), and the k-blocks per schedule unit and per
+ * accumulation chunk. Any out pointer may be NULL. */
+int roller_b200_gemm_schedule_info(const roller_plan* plan, int* sk_tiles, int* rounds,
+                                   int* unit_kb, int* chunk_kb);
+
 /* Accumulation chunk of the 3xTF32 mode: the TMEM accumulator is drained into fp32 registers
  * every `k_elems` elements of the reduction (rounded up to whole 32-element steps; 0 = never,
  * one chunk spans K). Shorter chunks cost more drains and give a smaller rounding error. The
@@ -179,6 +217,28 @@ int roller_b200_gemm_set_grid(roller_plan* plan, int ctas);
  * partial tiles. The reference's grid is always one block per tile (src/roller.py:536). */
 int roller_b200_gemm_set_stream_k(roller_plan* plan, int mode);
 
+/* Sets one option of a plan (ROLLER_OPT_*); affects later launches. The reference has no
+ * run-time options: its schedule is fixed when a hint is compiled (src/roller.py:93-342). */
+int roller_b200_gemm_set_option(roller_plan* plan, int option, long long value);
+
+/* Raises flags in other GPUs' memory: stores `value` (system-scope release) into each of the
+ * `n` addresses in `targets` (host array of device pointers, each possibly another GPU's memory
+ * mapped into this process), enqueued on `stream` behind the work whose completion it announces.
+ * The multi-GPU driver uses it to tell the rank that collects C that this rank's stores have
+ * landed, and to release the other ranks into the next step. There is no counterpart in the
+ * reference, which runs on one device (.env:5-6). */
+int roller_b200_flag_signal_async(uint32_t* const* targets, int n, uint32_t value, void* stream);
+
+/* Enqueues a one-block kernel that waits until each of the first `n` (<= 64) words of `flags`
+ * selected by `mask` (bit i = word i) has reached `value` (flags count steps; the comparison
+ * survives wrap-around). The wait is bounded: after `limit_cycles` clock cycles (0 = about two
+ * seconds) the kernel stores a non-zero code into *dev_status (device memory, zeroed by the
+ * caller) and returns, so a rank that never signals costs a time-out, not a hang. There
+ * is no counterpart in the reference (single device, .env:5-6). */
+int roller_b200_flag_wait_async(const uint32_t* flags, int n, unsigned long long mask,
+                                uint32_t value, long long limit_cycles, uint32_t* dev_status,
+                                void* stream);
+
 /* One GEMM, enqueued on `stream`, that allocates nothing: no cudaMalloc, cudaFree or allocating
  * library call, on this or any later call. It has no counterpart in the reference (whose launch
  * path allocates freely through CuPy); it exists for callers that cannot allocate -- a process
@@ -190,7 +250,10 @@ int roller_b200_gemm_set_stream_k(roller_plan* plan, int mode);
  * library, until exit). Staging needs beyond 32 MiB return ROLLER_ERR_TOO_LARGE.
  * All calls share the array and it keeps the last call's contents: calls whose GPU work
  * overlaps race on it. The first call on a device resolves the array's device address; make
- * that call before starting any stream capture. `dev_status` (optional, device memory) receives
+ * that call before starting any stream capture. Under CUDA's default lazy module loading the
+ * array and each kernel image receive their device memory at first use, so a caller whose pool
+ * will take all device memory should make one call per rTile and mode beforehand (or set
+ * CUDA_MODULE_LOADING=EAGER). `dev_status` (optional, device memory) receives
  * the kernel's bounded-wait status word; NULL uses a word inside the library. C = A @ B. */
 int roller_b200_gemm_static_scratch(const roller_ktile* tile, int mode, int M, int N, int K,
                                     int lda, int ldb, int ldc, const float* A, const float* B,
@@ -199,7 +262,10 @@ int roller_b200_gemm_static_scratch(const roller_ktile* tile, int mode, int M, i
 /* Stands in for the per-hint try/except of the sweep (src/benchmark.py:43-58): a kernel whose
  * pipeline stalls ends by itself and reports here instead of hanging.
  * Reads back the device status word of the plan (0 = all bounded waits completed); returns
- * ROLLER_ERR_TIMEOUT when it is non-zero. Synchronises the device. */
+ * ROLLER_ERR_TIMEOUT when it is non-zero. Synchronises the device. A non-zero word is cleared
+ * by this call (with the plan's stream-K flags), so the plan can be launched again; until it has
+ * been read, later launches of the plan give up at their first wait and leave C undefined, which
+ * is why callers that time or compare kernels must read it after they have run them. */
 int roller_b200_last_status(roller_plan* plan, uint32_t* device_status);
 
 /* Releases what roller_b200_gemm_create allocated (the reference leaves its module to the

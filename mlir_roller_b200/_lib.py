@@ -20,6 +20,17 @@ FLAG_B_TRANSPOSED = 2
 FLAG_C_16BIT = 4    # 16-bit modes only: C is written in the operand type instead of fp32
 LAYOUT_GENERAL = 0
 LAYOUT_SKINNY = 2
+# roller_b200_gemm_set_option
+OPT_WAIT_LIMIT_CYCLES = 1
+OPT_OVERLAP_LAUNCH = 2
+OPT_TMA_STORE = 3
+OPT_PROGRESSIVE_ROUNDS = 4
+OPT_TEST_DROP_PUBLISH = 5
+MAX_FLAG_TARGETS = 32
+# device status words (what a bounded wait that ran out records)
+DEV_TIMEOUT_FIXUP = 7
+DEV_TIMEOUT_SLOT = 8
+DEV_TIMEOUT_PEER = 9
 
 OK = 0
 ERR_INVALID = -1
@@ -80,9 +91,15 @@ SIGNATURES = {
     "roller_b200_gemm_host_async": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                               C.c_void_p]),
     "roller_b200_gemm_launch_info": (C.c_int, [C.c_void_p] + [C.POINTER(C.c_int)] * 6),
+    "roller_b200_gemm_schedule_info": (C.c_int, [C.c_void_p] + [C.POINTER(C.c_int)] * 4),
     "roller_b200_gemm_set_chunk": (C.c_int, [C.c_void_p, C.c_int]),
     "roller_b200_gemm_set_grid": (C.c_int, [C.c_void_p, C.c_int]),
     "roller_b200_gemm_set_stream_k": (C.c_int, [C.c_void_p, C.c_int]),
+    "roller_b200_gemm_set_option": (C.c_int, [C.c_void_p, C.c_int, C.c_longlong]),
+    "roller_b200_flag_signal_async": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_uint32,
+                                                C.c_void_p]),
+    "roller_b200_flag_wait_async": (C.c_int, [C.c_void_p, C.c_int, C.c_ulonglong, C.c_uint32,
+                                              C.c_longlong, C.c_void_p, C.c_void_p]),
     "roller_b200_gemm_static_scratch": (C.c_int, [C.POINTER(KTile), C.c_int, C.c_int, C.c_int,
                                                   C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                                   C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
@@ -183,6 +200,24 @@ def copy_block_async(dst_ptr: int, dst_ld: int, src_ptr: int, src_ld: int, rows:
           "roller_b200_copy_block_async")
 
 
+def flag_signal_async(target_ptrs, value: int, stream=None) -> None:
+    """Enqueue a store of `value` into every address of `target_ptrs` (device pointers, possibly
+    other GPUs' mapped memory), behind the work already on `stream`."""
+    arr = (C.c_void_p * len(target_ptrs))(*target_ptrs)
+    check(load().roller_b200_flag_signal_async(arr, len(target_ptrs), value & 0xFFFFFFFF,
+                                               _stream_ptr(stream)),
+          "roller_b200_flag_signal_async")
+
+
+def flag_wait_async(flags_ptr: int, n: int, mask: int, value: int, status_ptr: int,
+                    limit_cycles: int = 0, stream=None) -> None:
+    """Enqueue a bounded wait until the words `flags_ptr[i]` selected by `mask` have reached
+    `value`; a wait that runs out stores a non-zero code into the device word at `status_ptr`."""
+    check(load().roller_b200_flag_wait_async(flags_ptr, n, mask, value & 0xFFFFFFFF, limit_cycles,
+                                             status_ptr, _stream_ptr(stream)),
+          "roller_b200_flag_wait_async")
+
+
 class GemmPlan:
     """One rTile bound to one problem shape (owns the C-side plan)."""
 
@@ -247,6 +282,11 @@ class GemmPlan:
         check(self._lib.roller_b200_gemm_set_stream_k(self._h, mode),
               "roller_b200_gemm_set_stream_k")
 
+    def set_option(self, option: int, value: int) -> None:
+        """One of the OPT_* options of roller_b200_gemm_set_option."""
+        check(self._lib.roller_b200_gemm_set_option(self._h, option, value),
+              "roller_b200_gemm_set_option")
+
     def launch_info(self) -> dict:
         vals = [C.c_int() for _ in range(6)]
         check(self._lib.roller_b200_gemm_launch_info(self._h, *[C.byref(v) for v in vals]),
@@ -254,7 +294,15 @@ class GemmPlan:
         keys = ("grid", "block", "smem_bytes", "tiles_m", "tiles_n", "max_clusters")
         return {k: v.value for k, v in zip(keys, vals)}
 
+    def schedule_info(self) -> dict:
+        vals = [C.c_int() for _ in range(4)]
+        check(self._lib.roller_b200_gemm_schedule_info(self._h, *[C.byref(v) for v in vals]),
+              "roller_b200_gemm_schedule_info")
+        return {k: v.value for k, v in zip(("sk_tiles", "rounds", "unit_kb", "chunk_kb"), vals)}
+
     def device_status(self) -> int:
+        """The plan's device status word (0 = every bounded wait completed). Synchronises the
+        device; a non-zero word is cleared by the read, so the plan can be launched again."""
         st = C.c_uint32()
         rc = self._lib.roller_b200_last_status(self._h, C.byref(st))
         if rc not in (OK, ERR_TIMEOUT):

@@ -141,7 +141,13 @@ struct roller_plan {
   float* sk_ws;           // stream-K partial-tile slots (device), owned
   uint32_t* sk_flags;     // one flag per CTA (device), owned
   int sk_slots;           // CTAs the scratch area was sized for
-  uint32_t epoch;         // launch counter for the flags
+  uint32_t epoch;         // launch counter for the flags (1 .. 2^26-1)
+  int sk_rounds;          // rounds of the progressive schedule in use (1 = plain stream-K)
+  int progressive;        // requested rounds of the progressive schedule; 0 = off
+  long long spin_limit;   // clock cycles a device-side wait may last
+  bool overlap_launch;    // launches carry the programmatic-stream-serialization attribute
+  bool tma_store;         // C leaves through shared memory and TMA stores
+  bool drop_publish;      // test aid: partial tiles are never flagged
   bool stage_a, stage_b;  // operands go through a padded copy
   void* ws_a;             // padded copies (device), owned
   void* ws_b;
@@ -150,7 +156,8 @@ struct roller_plan {
   // cached tensor maps for the last (A, B) pointers seen
   const void* map_a_ptr;
   const void* map_b_ptr;
-  CUtensorMap tmA, tmB;
+  const void* map_c_ptr;
+  CUtensorMap tmA, tmB, tmC;
   // host-buffer path
   void *hd_a, *hd_b, *hd_c;
   cudaEvent_t ev0, ev1;
@@ -280,6 +287,9 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
   p->max_workers = p->sm_count / kv->cta_group;
   p->sk_mode = -1;
   p->epoch = 0;
+  p->sk_rounds = 1;
+  p->spin_limit = kSpinLimitCycles;
+  p->overlap_launch = true;
   // 3xTF32 drains the TMEM accumulator every 128 k (see the kernel header); 1xTF32 is
   // dominated by the 10-bit input mantissa, so one chunk spans the whole reduction.
   const int num_kb = (K + kv->rstep - 1) / kv->rstep;
@@ -358,12 +368,14 @@ int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, void* C, 
   const void* a_src = A;
   const void* b_src = B;
   long long lda = p->lda, ldb = p->ldb;
+  // every argument is checked before anything is enqueued
+  if (!p->stage_a && (reinterpret_cast<uintptr_t>(A) & 15)) return ROLLER_ERR_INVALID;
+  if (!p->stage_b && (reinterpret_cast<uintptr_t>(B) & 15)) return ROLLER_ERR_INVALID;
+  if (p->tma_store && (reinterpret_cast<uintptr_t>(C) & 15)) return ROLLER_ERR_INVALID;
   if (p->stage_a) {
     pad_rows(A, p->lda, p->ws_a, p->ws_lda, p->M, p->K, p->elem, p->sm_count * 8, st);
     a_src = p->ws_a;
     lda = p->ws_lda;
-  } else if (reinterpret_cast<uintptr_t>(A) & 15) {
-    return ROLLER_ERR_INVALID;
   }
   if (p->stage_b) {
     if (p->layout == 1)
@@ -372,9 +384,8 @@ int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, void* C, 
       pad_rows(B, p->ldb, p->ws_b, p->ws_ldb, p->K, p->N, p->elem, p->sm_count * 8, st);
     b_src = p->ws_b;
     ldb = p->ws_ldb;
-  } else if (reinterpret_cast<uintptr_t>(B) & 15) {
-    return ROLLER_ERR_INVALID;
   }
+  if (p->stage_a || p->stage_b) RB_CUDA(cudaGetLastError());
 
   // Which matrix feeds which MMA operand depends on the layout (see the kernel header).
   if (a_src != p->map_a_ptr || b_src != p->map_b_ptr) {
@@ -404,10 +415,19 @@ int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, void* C, 
     p->map_a_ptr = a_src;
     p->map_b_ptr = b_src;
   }
+  if (p->tma_store && C != p->map_c_ptr) {
+    // C as a store destination: boxes of 32 x 32 fp32 under the 128-byte swizzle. C may be
+    // another GPU's memory mapped into this process; the map is never used for a load.
+    int rc = encode_matrix(&p->tmC, C, p->M, p->N, p->ldc, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B,
+                           kElemF32);
+    if (rc != ROLLER_OK) return rc;
+    p->map_c_ptr = C;
+  }
 
   GemmArgs args;
   args.tmA = p->tmA;
   args.tmB = p->tmB;
+  if (p->tma_store) args.tmC = p->tmC; else memset(&args.tmC, 0, sizeof(args.tmC));
   args.C = static_cast<float*>(C);
   args.M = (p->layout == 2) ? p->N : p->M;
   args.N = (p->layout == 2) ? p->M : p->N;
@@ -421,11 +441,17 @@ int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, void* C, 
   if ((p->ldc * p->c_elem % 16) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0)
     args.flags |= kFlagVecStore;
   if (p->c_elem == 2) args.flags |= kFlagC16;
+  if (p->tma_store) args.flags |= kFlagTmaStore;
+  if (p->drop_publish) args.flags |= kFlagDropPublish;
   args.status = p->status;
+  args.spin_limit = p->spin_limit;
+  args.serialize_programmatically = p->overlap_launch;
   args.sk_tiles = p->sk_tiles;
+  args.sk_rounds = p->sk_rounds;
   args.sk_ws = p->sk_ws;
   args.sk_flags = p->sk_flags;
-  args.epoch = ++p->epoch;
+  p->epoch = p->epoch % 0x3FFFFFFu + 1;   // never zero: zero in a flag means "slot free"
+  args.epoch = p->epoch;
   RB_CUDA(kv->launch(args, p->grid, st));
   return ROLLER_OK;
 }
@@ -517,6 +543,16 @@ int roller_b200_gemm_launch_info(const roller_plan* p, int* grid, int* block, in
   return ROLLER_OK;
 }
 
+int roller_b200_gemm_schedule_info(const roller_plan* p, int* sk_tiles, int* rounds, int* unit_kb,
+                                   int* chunk_kb) {
+  if (!p) return ROLLER_ERR_INVALID;
+  if (sk_tiles) *sk_tiles = p->sk_tiles;
+  if (rounds) *rounds = p->sk_rounds;
+  if (unit_kb) *unit_kb = p->unit_kb;
+  if (chunk_kb) *chunk_kb = p->chunk_kb;
+  return ROLLER_OK;
+}
+
 int roller_b200_gemm_set_chunk(roller_plan* p, int k_elems) {
   if (!p || k_elems < 0) return ROLLER_ERR_INVALID;
   const int num_kb = (p->K + p->kv->rstep - 1) / p->kv->rstep;
@@ -551,7 +587,46 @@ int roller_b200_last_status(roller_plan* p, uint32_t* device_status) {
   RB_CUDA(cudaDeviceSynchronize());
   RB_CUDA(cudaMemcpy(&h, p->status, sizeof(h), cudaMemcpyDeviceToHost));
   if (device_status) *device_status = h;
+  if (h != 0) {
+    // Read and clear: the failed launch has been reported, later launches start clean. The
+    // stream-K flags of a launch that gave up may be left raised, so they are reset as well.
+    RB_CUDA(cudaMemset(p->status, 0, sizeof(uint32_t)));
+    if (p->sk_flags) RB_CUDA(cudaMemset(p->sk_flags, 0, sizeof(uint32_t) * p->sk_slots));
+  }
   return h == 0 ? ROLLER_OK : ROLLER_ERR_TIMEOUT;
+}
+
+int roller_b200_gemm_set_option(roller_plan* p, int option, long long value) {
+  if (!p) return ROLLER_ERR_INVALID;
+  switch (option) {
+    case ROLLER_OPT_WAIT_LIMIT_CYCLES:
+      if (value < 0) return ROLLER_ERR_INVALID;
+      p->spin_limit = value == 0 ? kSpinLimitCycles : value;
+      return ROLLER_OK;
+    case ROLLER_OPT_OVERLAP_LAUNCH:
+      p->overlap_launch = value != 0;
+      return ROLLER_OK;
+    case ROLLER_OPT_TMA_STORE:
+      if (value != 0) {
+        if (p->kv->staging_bytes == 0 || p->layout == 2 || p->c_elem != 4 ||
+            (p->flags & ROLLER_FLAG_ACCUMULATE))
+          return ROLLER_ERR_UNSUPPORTED;
+        if (p->ldc % 4 != 0) return ROLLER_ERR_INVALID;   // TMA needs 16-byte row strides
+      }
+      p->tma_store = value != 0;
+      p->map_c_ptr = nullptr;
+      return ROLLER_OK;
+    case ROLLER_OPT_PROGRESSIVE_ROUNDS:
+      if (value < -1 || value > 64) return ROLLER_ERR_INVALID;
+      if (value != 0 && (p->flags & ROLLER_FLAG_ACCUMULATE)) return ROLLER_ERR_UNSUPPORTED;
+      p->progressive = static_cast<int>(value);
+      return plan_configure(p);
+    case ROLLER_OPT_TEST_DROP_PUBLISH:
+      p->drop_publish = value != 0;
+      return ROLLER_OK;
+    default:
+      return ROLLER_ERR_INVALID;
+  }
 }
 
 int roller_b200_gemm_destroy(roller_plan* p) {
@@ -618,8 +693,22 @@ static int plan_configure(roller_plan* p) {
   if (workers < 1) workers = 1;
 
   int sk_tiles = 0;
+  int rounds = 1;
   const long long r = tiles % workers;
-  if (p->sk_mode != 0 && r != 0 && cpt > 1 && !(p->flags & ROLLER_FLAG_ACCUMULATE)) {
+  if (p->progressive != 0 && cpt > 1 && !p->grid_forced && tiles * cpt < (1ll << 31)) {
+    // Progressive schedule: every tile is cut along K and the tiles are worked through in
+    // groups, so that finished tiles appear at a steady rate. The number of rounds must
+    // divide the tile count (no tile may straddle two rounds): the largest divisor not above
+    // the request is taken. Left to the library (-1), a round is made as short as it can be
+    // with every worker still holding a run of about three units, which keeps the cost of
+    // handing partial tiles around below a tenth of the work.
+    long long want = p->progressive > 0 ? p->progressive : tiles * cpt / (3ll * workers);
+    if (want > 64) want = 64;
+    if (want < 1) want = 1;
+    rounds = static_cast<int>(want);
+    while (rounds > 1 && tiles % rounds != 0) --rounds;
+    sk_tiles = static_cast<int>(tiles);
+  } else if (p->sk_mode != 0 && r != 0 && cpt > 1 && !(p->flags & ROLLER_FLAG_ACCUMULATE)) {
     const long long full = tiles / workers;
     const long long dp_time = (full + 1) * cpt;
     // Cost of handing partial tiles from worker to worker through global memory, in units:
@@ -641,6 +730,7 @@ static int plan_configure(roller_plan* p) {
     p->grid = static_cast<int>(w) * kv->cta_group;
   }
   p->sk_tiles = sk_tiles;
+  p->sk_rounds = rounds;
   if (sk_tiles && p->sk_slots < p->grid) {
     cudaFree(p->sk_ws);
     cudaFree(p->sk_flags);

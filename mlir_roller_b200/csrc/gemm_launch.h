@@ -7,14 +7,23 @@
 
 namespace rb200 {
 
+// Default limit of every device-side wait, in clock cycles: about two seconds at the B200's
+// boost clock; no legitimate wait in these kernels lasts longer than a few milliseconds. The
+// host may pass a shorter limit per launch.
+constexpr long long kSpinLimitCycles = 4000000000LL;
+
 // Kernel flag bits (GemmArgs::flags).
 constexpr int kFlagAccumulate = 1;  // C += A@B instead of C = A@B
 constexpr int kFlagVecStore = 2;    // C rows are 16-byte aligned: use 128-bit stores
 constexpr int kFlagC16 = 4;         // 16-bit kernels only: C holds elements of the operand type
+constexpr int kFlagTmaStore = 8;    // C leaves through shared memory and TMA stores (GemmArgs::tmC)
+constexpr int kFlagDropPublish = 16;  // test aid: partial tiles are written but never flagged, so
+                                      // the worker completing the tile sees its bounded wait run out
 
 struct GemmArgs {
   CUtensorMap tmA;
   CUtensorMap tmB;
+  CUtensorMap tmC;      // C as a store destination (32 x 32 boxes); used with kFlagTmaStore only
   float* C;
   int M, N, K;
   long long ldc;
@@ -23,10 +32,13 @@ struct GemmArgs {
   int acc_kb;    // k-blocks accumulated in TMEM before a drain into registers
   int flags;
   uint32_t* status;
+  long long spin_limit; // clock cycles a device-side wait may last
+  bool serialize_programmatically;  // launch may overlap the tail of the stream's previous kernel
   int sk_tiles;         // tiles dealt out in k-chunks (stream-K); 0 = whole tiles only
+  int sk_rounds;        // groups the stream-K tiles are worked through one after the other (>= 1)
   float* sk_ws;         // one 128 x block_n slot per CTA for partial tiles
   uint32_t* sk_flags;   // one flag per CTA, set to `epoch` when its slot is valid
-  uint32_t epoch;       // distinguishes this launch's flags from earlier launches'
+  uint32_t epoch;       // distinguishes this launch's flags from earlier launches' (1 .. 2^26-1)
 };
 
 struct KernelVariant {
@@ -40,6 +52,7 @@ struct KernelVariant {
   int smem_bytes;
   int tmem_cols;
   int threads;
+  int staging_bytes;  // shared memory set aside for the TMA-store output path (0 = kernel lacks it)
   const void* func;  // kernel symbol, for cudaFuncSetAttribute / occupancy queries
   cudaError_t (*launch)(const GemmArgs& args, int grid, cudaStream_t stream);
 };

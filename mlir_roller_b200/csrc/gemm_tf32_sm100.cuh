@@ -53,6 +53,21 @@
 // stores C. Every worker runs its stream-K units first (the piece it must publish before the
 // piece it must complete), then its whole tiles, so these waits are short; they are bounded
 // like every other wait in the kernel.
+//
+// "Progressive" schedule (sk_rounds > 1, every tile cut along K). The tiles are taken in
+// `sk_rounds` groups of consecutive tiles; the whole grid works on one group at a time, each
+// worker on a few k-chunks of it, so finished tiles leave the kernel at a steady rate from
+// early on instead of all together at the end. That is what a consumer on the far side of a
+// link wants (the multi-GPU driver stores C straight into another GPU's memory): the transfer
+// then runs underneath the rest of the computation. A worker reuses its scratch slot from
+// round to round, so it waits (bounded) for the slot's reader before it publishes again.
+//
+// Output path. By default the accumulate warps store C themselves. With kFlagTmaStore (kernels
+// that have a staging area, Cfg::STAGING_BYTES > 0) each warp writes 32 x 32 pieces of its
+// part of the tile into shared memory and hands them to the TMA unit
+// (cp.async.bulk.tensor store), which drains them to global memory on its own: the warps are
+// back at the next tile's accumulation at once, however slowly the destination (a peer GPU
+// behind NVLink) takes the data.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -140,7 +155,14 @@ struct GemmCfg {
   static constexpr int SMEM_LIMIT = 232448;  // 227 KiB opt-in maximum per CTA
   static constexpr int STAGES_FIT = (SMEM_LIMIT - 1024 - CTRL_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + CTRL_BYTES + 1024;
+  // Staging area of the TMA-store output path: one 32 x 32 fp32 box (128-byte swizzle) per
+  // accumulate warp. Present where the ring leaves room for it (and C is not written
+  // transposed); kernels without it only have the plain store path.
+  static constexpr int STAGING_WANTED = 8 * 4096;
+  static constexpr int STAGING_BYTES =
+      (LAYOUT_ != 2 && SMEM_LIMIT - 1024 - CTRL_BYTES - STAGES * STAGE_BYTES >= STAGING_WANTED)
+          ? STAGING_WANTED : 0;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + CTRL_BYTES + 1024;
   static constexpr int ACC_STAGES = 2;
   static constexpr int TMEM_COLS = ACC_STAGES * BN;
   static constexpr bool HAS_XFORM = (MODE == 3);
@@ -223,35 +245,61 @@ struct Segment {
   int tile;
   int kb0, kb1;
   bool final;  // holds the end of the tile's reduction: adds the other workers' partials, stores C
+  int round;   // round of the schedule the segment belongs to (0 for whole tiles)
 };
 
 // Static schedule shared by the producer, split, MMA and epilogue roles (each walks its own copy).
+//
+// The first `sk_tiles` tiles are cut into units of `chunk_kb` k-blocks; the units, in tile
+// order, are dealt out in contiguous runs to rounds * workers "virtual workers", and worker w
+// plays the virtual workers w, w + workers, w + 2 workers, ... one after the other (one per
+// round). With rounds == 1 that is the plain stream-K deal. The remaining tiles follow whole,
+// round-robin. `rounds` must divide sk_tiles, so that no tile straddles two rounds.
+// All of it is 32-bit arithmetic (the host only enables the split when units < 2^31 and
+// virtual workers < 2^15): a 64-bit division is a subroutine call on the device.
 struct Schedule {
-  int num_tiles, workers, worker, num_kb, chunk_kb, cpt, sk_tiles;
-  long long u_begin, u_end;  // this worker's stream-K units (chunks), consumed from the end
-  int dp_next;               // next whole tile
+  int num_tiles, workers, worker, num_kb, chunk_kb, cpt, sk_tiles, rounds;
+  int round;             // round whose units are being consumed
+  uint32_t vworkers;     // rounds * workers
+  uint32_t q, rem;       // units / vworkers and units % vworkers
+  int u_begin, u_end;    // this worker's units of the current round, consumed from the end
+  int dp_next;           // next whole tile
 
   __device__ Schedule(int num_tiles_, int workers_, int worker_, int num_kb_, int chunk_kb_,
-                      int sk_tiles_)
+                      int sk_tiles_, int rounds_)
       : num_tiles(num_tiles_), workers(workers_), worker(worker_), num_kb(num_kb_),
-        chunk_kb(chunk_kb_), sk_tiles(sk_tiles_) {
+        chunk_kb(chunk_kb_), sk_tiles(sk_tiles_), rounds(rounds_), round(0) {
     cpt = (num_kb + chunk_kb - 1) / chunk_kb;
+    vworkers = static_cast<uint32_t>(workers) * static_cast<uint32_t>(rounds);
+    const uint32_t units = static_cast<uint32_t>(sk_tiles) * static_cast<uint32_t>(cpt);
+    q = units / vworkers;
+    rem = units % vworkers;
     u_begin = unit_begin(worker);
     u_end = unit_begin(worker + 1);
     dp_next = sk_tiles + worker;
   }
-  __device__ long long unit_begin(int w) const {
-    return static_cast<long long>(sk_tiles) * cpt * w / workers;
+  // First unit of virtual worker v (v = round * workers + worker):
+  // floor(units * v / vworkers) = q * v + floor(rem * v / vworkers), no product above 2^31.
+  __device__ int unit_begin(int v) const {
+    const uint32_t uv = static_cast<uint32_t>(v);
+    return static_cast<int>(q * uv + rem * uv / vworkers);
   }
   __device__ bool next(Segment& s) {
+    while (u_end <= u_begin && round + 1 < rounds) {
+      ++round;
+      const int v = round * workers + worker;
+      u_begin = unit_begin(v);
+      u_end = unit_begin(v + 1);
+    }
     if (u_end > u_begin) {
-      const int tile = static_cast<int>((u_end - 1) / cpt);
-      const long long t0 = static_cast<long long>(tile) * cpt;
-      const long long sb = u_begin > t0 ? u_begin : t0;
+      const int tile = (u_end - 1) / cpt;
+      const int t0 = tile * cpt;
+      const int sb = u_begin > t0 ? u_begin : t0;
       s.tile = tile;
-      s.kb0 = static_cast<int>(sb - t0) * chunk_kb;
-      s.kb1 = min(static_cast<int>(u_end - t0) * chunk_kb, num_kb);
+      s.kb0 = (sb - t0) * chunk_kb;
+      s.kb1 = min((u_end - t0) * chunk_kb, num_kb);
       s.final = (u_end - t0 == cpt);
+      s.round = round;
       u_end = sb;
       return true;
     }
@@ -260,6 +308,7 @@ struct Schedule {
       s.kb0 = 0;
       s.kb1 = num_kb;
       s.final = true;
+      s.round = 0;
       dp_next += workers;
       return true;
     }
@@ -279,13 +328,29 @@ __device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
 __device__ __forceinline__ void epi_bar_sync() {
   asm volatile("bar.sync 1, 256;" ::: "memory");
 }
+// The same barrier carrying a vote: true for every thread when any of the 256 passed `mine`.
+// The accumulate warps use it wherever they must agree on giving up: a warp that left on its
+// own would leave the others waiting at the next barrier for ever.
+__device__ __forceinline__ bool epi_bar_any(bool mine) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.or.pred p, 1, 256, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(out)
+      : "r"(static_cast<uint32_t>(mine))
+      : "memory");
+  return out != 0;
+}
 
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 float* __restrict__ C, int M, int N, int K, long long ldc, int tiles_m,
-                 int tiles_n, int chunk_kb, int acc_kb, int flags, uint32_t* status, int sk_tiles,
-                 float* sk_ws, uint32_t* sk_flags, uint32_t epoch) {
+                 const __grid_constant__ CUtensorMap tmC, float* __restrict__ C, int M, int N, int K,
+                 long long ldc, int tiles_m, int tiles_n, int chunk_kb, int acc_kb, int flags,
+                 uint32_t* status, long long spin_limit, int sk_tiles, int sk_rounds, float* sk_ws,
+                 uint32_t* sk_flags, uint32_t epoch) {
   // chunk_kb: the unit of the stream-K schedule (a tile's reduction is dealt out in pieces of
   // that many k-blocks); acc_kb: how many k-blocks accumulate in TMEM before the accumulate
   // warps drain them into registers. 3xTF32 uses the same value for both; the modes whose
@@ -297,15 +362,16 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t smem_base = (smem_dyn_addr + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_dyn + (smem_base - smem_dyn_addr);
 
-  const uint32_t ctrl = smem_base + STAGES * Cfg::STAGE_BYTES;
+  const uint32_t staging = smem_base + STAGES * Cfg::STAGE_BYTES;   // 1024-byte aligned
+  const uint32_t ctrl = staging + Cfg::STAGING_BYTES;
   auto full_bar = [&](int s) { return ctrl + 8u * s; };         // TMA bytes landed (per CTA)
   auto ready_bar = [&](int s) { return ctrl + 64u + 8u * s; };  // stage usable by MMA (leader)
   auto empty_bar = [&](int s) { return ctrl + 128u + 8u * s; }; // MMAs done reading (per CTA)
   auto tmem_full_bar = [&](int a) { return ctrl + 192u + 8u * a; };
   auto tmem_empty_bar = [&](int a) { return ctrl + 208u + 8u * a; };
   const uint32_t tmem_slot = ctrl + 224u;
-  volatile uint32_t* epi_abort =
-      reinterpret_cast<volatile uint32_t*>(smem_gen + STAGES * Cfg::STAGE_BYTES + 232);
+  const uint32_t mma_done_bar = ctrl + 240u;   // every MMA of this launch has completed
+  const WaitCtx wc{status, spin_limit};
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -322,24 +388,33 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(tmem_full_bar(a), 1);
       mbar_init(tmem_empty_bar(a), CG * Cfg::EPI_WARPS);
     }
-    *epi_abort = 0;
+    mbar_init(mma_done_bar, 1);
     fence_barrier_init();
   }
   if (warp == 1) tmem_alloc<CG>(tmem_slot, Cfg::TMEM_COLS);
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if constexpr (Cfg::STAGING_BYTES > 0) {
+      if (flags & kFlagTmaStore) tma_prefetch_desc(&tmC);
+    }
   }
+  // The next kernel of the stream may be scheduled from now on (its CTAs take SMs as this
+  // grid's CTAs leave them and wait below); nothing above touched global memory.
+  grid_launch_dependents();
   tcgen05_fence_before_sync();
   if constexpr (CG == 2) cluster_sync(); else __syncthreads();
   tcgen05_fence_after_sync();
+  // Everything from here on reads operands, scratch and status that the previous kernel of
+  // the stream may have written, and writes C.
+  grid_dependency_wait();
 
   uint32_t tmem_base;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
   const int num_kb = (K + BK - 1) / BK;
   Schedule sched(tiles_m * tiles_n, static_cast<int>(gridDim.x) / CG,
-                 static_cast<int>(blockIdx.x) / CG, num_kb, chunk_kb, sk_tiles);
+                 static_cast<int>(blockIdx.x) / CG, num_kb, chunk_kb, sk_tiles, sk_rounds);
   Segment sg;
 
   if (warp < Cfg::FIRST_EPI_WARP) {
@@ -355,7 +430,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int m0 = (mb * CG + static_cast<int>(cta_rank)) * Cfg::BM;
         const int n0 = nb * BN + static_cast<int>(cta_rank) * Cfg::BNL;
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
-          if (!mbar_wait(empty_bar(s), ph ^ 1u, status, kDevTimeoutEmpty)) { ok = false; break; }
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, wc, kDevTimeoutEmpty)) { ok = false; break; }
           const uint32_t a_dst = smem_base + s * Cfg::STAGE_BYTES;
           const uint32_t b_dst = a_dst + Cfg::A_BYTES;
           if constexpr (CG == 2 && !Cfg::HAS_XFORM) {
@@ -374,9 +449,11 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       // Tail: the MMA issuer's last releases must land in this CTA before it may exit.
       for (int i = 0; i < STAGES && ok; ++i) {
-        ok = mbar_wait(empty_bar(s), ph ^ 1u, status, kDevTimeoutTail);
+        ok = mbar_wait(empty_bar(s), ph ^ 1u, wc, kDevTimeoutTail);
         if (++s == STAGES) { s = 0; ph ^= 1u; }
       }
+      // ... and so must the arrival that closes the MMA issuer's work (sent to both CTAs).
+      mbar_wait_drain(mma_done_bar, 0u, spin_limit);
     } else if (warp == 1 && lane == 0 && is_leader) {
       // ---------------------------------------------------------- MMA issuer
       constexpr uint32_t idesc =
@@ -392,7 +469,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       while (ok && sched.next(sg)) {
         for (int kb0 = sg.kb0; kb0 < sg.kb1 && ok; kb0 += acc_kb) {
           const int kb1 = min(kb0 + acc_kb, sg.kb1);
-          if (!mbar_wait(tmem_empty_bar(acc), acc_ph ^ 1u, status, kDevTimeoutTmemEmpty)) {
+          if (!mbar_wait(tmem_empty_bar(acc), acc_ph ^ 1u, wc, kDevTimeoutTmemEmpty)) {
             ok = false;
             break;
           }
@@ -400,7 +477,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
           for (int kb = kb0; kb < kb1; ++kb) {
             const uint32_t wait_bar = Cfg::HAS_XFORM ? ready_bar(s) : full_bar(s);
-            if (!mbar_wait(wait_bar, ph, status, kDevTimeoutReady)) { ok = false; break; }
+            if (!mbar_wait(wait_bar, ph, wc, kDevTimeoutReady)) { ok = false; break; }
             tcgen05_fence_after_sync();
             const uint32_t stage = smem_base + s * Cfg::STAGE_BYTES;
             const uint64_t a_raw = Cfg::AOp::desc(stage);
@@ -439,6 +516,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (acc == 0) acc_ph ^= 1u;
         }
       }
+      // Whatever was issued must have completed before tensor and shared memory are given
+      // up, also when the loop above was left early. (Not cut short by a recorded error.)
+      umma_commit<CG>(mma_done_bar);
+      mbar_wait_drain(mma_done_bar, 0u, spin_limit);
     }
   } else if (warp < Cfg::FIRST_XFORM_WARP) {
     // ------------------------------------------------------------ accumulate + epilogue
@@ -452,6 +533,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const bool vec_store = (flags & kFlagVecStore) != 0;
     // 16-bit kernels can also write C in their operand type (C then points to 16-bit elements)
     const bool c16 = Cfg::DT != 0 && (flags & kFlagC16) != 0;
+    const bool tma_store = Cfg::STAGING_BYTES > 0 && (flags & kFlagTmaStore) != 0;
+    // With partial tiles in play the 256 threads meet at barriers, so they must also leave
+    // together: every decision to give up is then taken by a vote at such a barrier.
+    const bool sk_active = sk_tiles > 0;
     // Stream-K scratch: one slot of 128 x BN floats per CTA; thread `et` owns every 256th float4.
     constexpr size_t kSlotFloats = static_cast<size_t>(Cfg::BM) * BN;
     int acc = 0;
@@ -466,7 +551,11 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
       for (int j = 0; j < COLS; ++j) sum[j] = 0.0f;
       for (int kb0 = sg.kb0; kb0 < sg.kb1; kb0 += acc_kb) {
-        if (!mbar_wait(tmem_full_bar(acc), acc_ph, status, kDevTimeoutTmemFull)) { ok = false; break; }
+        // (a warp gives up as a whole: the tensor-memory loads below need all 32 lanes)
+        if (!__all_sync(0xffffffffu, mbar_wait(tmem_full_bar(acc), acc_ph, wc, kDevTimeoutTmemFull))) {
+          ok = false;
+          break;
+        }
         tcgen05_fence_after_sync();
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                static_cast<uint32_t>(acc * BN + half * COLS);
@@ -487,10 +576,37 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         acc ^= 1;
         if (acc == 0) acc_ph ^= 1u;
       }
-      if (!ok) break;
+      if (sk_active) {
+        if (epi_bar_any(!ok)) { ok = false; break; }
+      } else if (!ok) {
+        break;
+      }
 
+      // Flags carry the launch and the round, so a slot's reader never takes one round's
+      // partial sums for another's; zero means "slot free".
+      const uint32_t tag = (epoch << 6) | static_cast<uint32_t>(sg.round);
       if (!sg.final) {
         // Publish this worker's partial sums of the tile, then raise its flag.
+        uint32_t* my_flag = sk_flags + sched.worker * CG + cta_rank;
+        if (sg.round > 0) {
+          // The slot still holds the previous round's partial until its reader hands it back.
+          bool failed = false;
+          if (et == 0) {
+            const long long t0 = clock64();
+            uint32_t spins = 0;
+            while (ld_acquire_gpu(my_flag) != 0u) {
+              if ((++spins & 63u) == 0) {
+                if (*reinterpret_cast<volatile uint32_t*>(status) != kDevOk) { failed = true; break; }
+                if (clock64() - t0 > spin_limit) {
+                  atomicCAS(status, kDevOk, kDevTimeoutSlot);
+                  failed = true;
+                  break;
+                }
+              }
+            }
+          }
+          if (epi_bar_any(failed)) { ok = false; break; }
+        }
         float4* slot = reinterpret_cast<float4*>(
             sk_ws + (static_cast<size_t>(sched.worker) * CG + cta_rank) * kSlotFloats);
 #pragma unroll
@@ -498,32 +614,35 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           slot[j * 256 + et] = make_float4(sum[4 * j], sum[4 * j + 1], sum[4 * j + 2], sum[4 * j + 3]);
         __threadfence();
         epi_bar_sync();
-        if (et == 0) st_release_gpu(sk_flags + sched.worker * CG + cta_rank, epoch);
+        // (a launch made for a test of the bounded waits leaves the flag down)
+        if (et == 0 && !(flags & kFlagDropPublish)) st_release_gpu(my_flag, tag);
         continue;
       }
       if (sg.kb0 > 0) {
-        // Add the partial sums of the workers that computed the earlier parts of this tile.
-        const long long tile_u0 = static_cast<long long>(sg.tile) * sched.cpt;
+        // Add the partial sums of the workers that computed the earlier parts of this tile:
+        // the virtual workers before this one, all of the same round.
+        const int tile_u0 = sg.tile * sched.cpt;
+        const int v_round0 = sg.round * sched.workers;
         for (int p = sched.worker - 1; p >= 0; --p) {
-          // A worker with no stream-K units (more workers than units) publishes nothing.
-          if (sched.unit_begin(p + 1) == sched.unit_begin(p)) continue;
+          // A worker with no units in this round publishes nothing.
+          if (sched.unit_begin(v_round0 + p + 1) == sched.unit_begin(v_round0 + p)) continue;
+          bool failed = false;
           if (et == 0) {
             const uint32_t* flag = sk_flags + p * CG + cta_rank;
             const long long t0 = clock64();
             uint32_t spins = 0;
-            while (ld_acquire_gpu(flag) != epoch) {
+            while (ld_acquire_gpu(flag) != tag) {
               if ((++spins & 63u) == 0) {
-                if (*reinterpret_cast<volatile uint32_t*>(status) != kDevOk) { *epi_abort = 1; break; }
-                if (clock64() - t0 > kSpinLimitCycles) {
+                if (*reinterpret_cast<volatile uint32_t*>(status) != kDevOk) { failed = true; break; }
+                if (clock64() - t0 > spin_limit) {
                   atomicCAS(status, kDevOk, kDevTimeoutFixup);
-                  *epi_abort = 1;
+                  failed = true;
                   break;
                 }
               }
             }
           }
-          epi_bar_sync();
-          if (*epi_abort != 0) { ok = false; break; }
+          if (epi_bar_any(failed)) { ok = false; break; }
           const float4* slot = reinterpret_cast<const float4*>(
               sk_ws + (static_cast<size_t>(p) * CG + cta_rank) * kSlotFloats);
 #pragma unroll
@@ -531,14 +650,50 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const float4 q = __ldcg(slot + j * 256 + et);
             sum[4 * j] += q.x; sum[4 * j + 1] += q.y; sum[4 * j + 2] += q.z; sum[4 * j + 3] += q.w;
           }
-          // Hand the slot back (each slot has exactly one reader per launch): with the flag at
-          // zero again, a replay of this very launch -- a captured CUDA graph re-issues the
-          // same epoch -- cannot take the old contents for new ones.
+          // Hand the slot back (each partial has exactly one reader): with the flag at zero
+          // again its owner may publish the next round's partial, and a replay of this very
+          // launch -- a captured CUDA graph re-issues the same epoch -- cannot take the old
+          // contents for new ones.
           epi_bar_sync();
           if (et == 0) st_release_gpu(sk_flags + p * CG + cta_rank, 0u);
-          if (sched.unit_begin(p) <= tile_u0) break;  // worker p started the tile
+          if (sched.unit_begin(v_round0 + p) <= tile_u0) break;  // worker p started the tile
         }
         if (!ok) break;
+      }
+      if constexpr (Cfg::STAGING_BYTES > 0) {
+        if (tma_store) {
+          // Hand the tile to the TMA unit in 32 x 32 pieces through this warp's staging box.
+          // Box rows are 128 bytes; the 16-byte chunk c of row r sits at chunk (c ^ (r & 7)),
+          // the 128-byte swizzle the tensor map of C is encoded with (and the order in which a
+          // warp's 32 lanes hit every bank exactly once per four rows).
+          const uint32_t box = staging + static_cast<uint32_t>(warp - Cfg::FIRST_EPI_WARP) * 4096u;
+          const int row0 = (mb * CG + static_cast<int>(cta_rank)) * Cfg::BM + quarter * 32;
+          if (row0 < M) {
+#pragma unroll
+            for (int c = 0; c < COLS / 32; ++c) {
+              const int col0 = n0 + c * 32;
+              if (col0 >= N) break;
+              if (lane == 0) bulk_wait_read_all();   // the box's previous contents have left
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const uint32_t at = box + static_cast<uint32_t>(lane) * 128u +
+                                    (static_cast<uint32_t>(j ^ (lane & 7)) << 4);
+                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(at),
+                             "f"(sum[c * 32 + 4 * j]), "f"(sum[c * 32 + 4 * j + 1]),
+                             "f"(sum[c * 32 + 4 * j + 2]), "f"(sum[c * 32 + 4 * j + 3])
+                             : "memory");
+              }
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_2d(&tmC, box, col0, row0);
+                bulk_commit_group();
+              }
+            }
+          }
+          continue;
+        }
       }
       if constexpr (Cfg::TRANSPOSE_C) {
         // The kernel computed C^T: element (row, col) of its tile is C[col][row], so for one
@@ -636,6 +791,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       }
     }
+    if constexpr (Cfg::STAGING_BYTES > 0) {
+      // Stores handed to the TMA unit must have been performed before the CTA may go.
+      if (tma_store && lane == 0) bulk_wait_all();
+    }
   } else {
     // ------------------------------------------------------------ split warps
     if constexpr (Cfg::REBALANCE) setmaxnreg_dec<Cfg::REGS_XFORM>();
@@ -648,7 +807,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         bool ok = true;
         while (ok && sched.next(sg)) {
           for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
-            if (!mbar_wait(full_bar(s), ph, status, kDevTimeoutFull)) { ok = false; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, wc, kDevTimeoutFull))) {
+              ok = false;
+              break;
+            }
             // Element-wise, so the swizzled placement of the raw tile carries over unchanged.
             const uint4* src = reinterpret_cast<const uint4*>(smem_gen + s * Cfg::STAGE_BYTES);
             uint4* dst =
@@ -678,6 +840,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   // ------------------------------------------------------------ teardown
   __syncwarp();
+  // After a failed wait some role left its loop early: give bulk copies still on their way
+  // into this CTA's shared memory time to land before the memory is released.
+  if (*reinterpret_cast<volatile uint32_t*>(status) != kDevOk) abort_grace_period();
   tcgen05_fence_before_sync();
   if constexpr (CG == 2) cluster_sync(); else __syncthreads();
   if (warp == 1) {

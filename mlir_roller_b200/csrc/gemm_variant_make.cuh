@@ -13,16 +13,20 @@ static cudaError_t launch_variant(const GemmArgs& a, int grid, cudaStream_t stre
   cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = Cfg::CG;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  // Lets this launch be scheduled while the previous kernel of the stream winds down; the
+  // kernel itself waits for that kernel's completion before it touches global memory.
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, gemm_tf32_kernel<Cfg>, a.tmA, a.tmB, a.C, a.M, a.N, a.K, a.ldc,
-                            a.tiles_m, a.tiles_n, a.chunk_kb, a.acc_kb, a.flags, a.status, a.sk_tiles, a.sk_ws,
-                            a.sk_flags, a.epoch);
+  cfg.numAttrs = a.serialize_programmatically ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, gemm_tf32_kernel<Cfg>, a.tmA, a.tmB, a.tmC, a.C, a.M, a.N, a.K,
+                            a.ldc, a.tiles_m, a.tiles_n, a.chunk_kb, a.acc_kb, a.flags, a.status,
+                            a.spin_limit, a.sk_tiles, a.sk_rounds, a.sk_ws, a.sk_flags, a.epoch);
 }
 
 // The table's `mode` is the caller-visible one: 1 / 3 for fp32 operands (1xTF32 / 3xTF32),
@@ -42,6 +46,7 @@ static KernelVariant make_variant() {
   v.smem_bytes = Cfg::SMEM_BYTES;
   v.tmem_cols = Cfg::TMEM_COLS;
   v.threads = Cfg::THREADS;
+  v.staging_bytes = Cfg::STAGING_BYTES;
   v.func = reinterpret_cast<const void*>(&gemm_tf32_kernel<Cfg>);
   v.launch = &launch_variant<Cfg>;
   return v;

@@ -14,9 +14,17 @@
 // there; two calls whose GPU work overlaps (different streams, or different host threads)
 // race on it. Nothing in the array has to start at zero except the status word, which each
 // call clears on its stream before launching.
+//
+// Where the memory really comes from: with CUDA's default lazy module loading the array and
+// the kernel images get their device memory when they are first touched (the symbol lookup,
+// the first launch of each rTile/mode), not when the library is loaded. A caller whose pool
+// is about to take all of the device's memory should therefore make one call per rTile and
+// mode it will use before the pool does so (or run with CUDA_MODULE_LOADING=EAGER); once that
+// is done no later call needs memory from anyone.
 #include "../../include/roller_b200.h"
 
 #include <cstdio>
+#include <cstring>
 #include <mutex>
 
 #include "gemm_launch.h"
@@ -34,8 +42,11 @@ constexpr int kMaxDevices = 64;
 static __device__ __align__(256) float g_static_scratch[kScratchFloats];
 static __device__ __align__(256) uint32_t g_static_status[64];
 
+constexpr int kMaxVariants = 64;
+
 struct DeviceSetup {
   bool ready = false;
+  int max_pairs[kMaxVariants] = {};   // co-resident CTA pairs per cta_group-2 kernel; 0 = not asked yet
   float* scratch = nullptr;     // device address of g_static_scratch on this device
   uint32_t* status = nullptr;   // device address of g_static_status on this device
   int sm_count = 0;
@@ -134,6 +145,9 @@ extern "C" int roller_b200_gemm_static_scratch(const roller_ktile* tile, int mod
   int rc = setup_current_device(&dev);
   if (rc != ROLLER_OK) return rc;
   if (dev->cc_major != 10 || dev->smem_optin < kv->smem_bytes) return ROLLER_ERR_DEVICE;
+  int variant_idx = -1;
+  for (int i = 0; i < variant_count() && i < kMaxVariants; ++i)
+    if (&variant_at(i) == kv) variant_idx = i;
 
   // Which operands break TMA's 16-byte rules and how much of the static array they need.
   const bool stage_a = (lda % 4) != 0 || (reinterpret_cast<uintptr_t>(A) & 15) != 0;
@@ -169,12 +183,14 @@ extern "C" int roller_b200_gemm_static_scratch(const roller_ktile* tile, int mod
     b_src = dst;
     b_ld = static_cast<long long>(pad_ldb);
   }
+  if ((stage_a || stage_b) && cudaGetLastError() != cudaSuccess) return ROLLER_ERR_CUDA;
 
   GemmArgs args;
   const bool rnd = (mode == ROLLER_MODE_1XTF32);  // 1xTF32 operands are rounded by the TMA unit
   if (!encode(&args.tmA, a_src, M, K, a_ld, 32, 128, CU_TENSOR_MAP_SWIZZLE_128B, rnd) ||
       !encode(&args.tmB, b_src, K, N, b_ld, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, rnd))
     return ROLLER_ERR_CUDA;
+  memset(&args.tmC, 0, sizeof(args.tmC));
   args.C = C;
   args.M = M; args.N = N; args.K = K;
   args.ldc = ldc;
@@ -186,12 +202,38 @@ extern "C" int roller_b200_gemm_static_scratch(const roller_ktile* tile, int mod
   args.flags = 0;
   if ((ldc % 4) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) args.flags |= kFlagVecStore;
   args.status = status;
+  args.spin_limit = kSpinLimitCycles;
+  args.serialize_programmatically = false;
   args.sk_tiles = 0;  // whole tiles only: the stream-K schedule needs a scratch area per CTA
+  args.sk_rounds = 1;
   args.sk_ws = nullptr;
   args.sk_flags = nullptr;
-  args.epoch = 0;
+  args.epoch = 1;
   const long long tiles = static_cast<long long>(args.tiles_m) * args.tiles_n;
-  const int workers = dev->sm_count / kv->cta_group;
+  int workers = dev->sm_count / kv->cta_group;
+  if (kv->cta_group == 2 && variant_idx >= 0) {
+    // Same cap as the plan path: no more CTA pairs than the device can hold at once. The
+    // occupancy query runs on the host and allocates nothing; its answer is kept per device.
+    std::lock_guard<std::mutex> lock(g_setup_mutex);
+    int& cached = dev->max_pairs[variant_idx];
+    if (cached == 0) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(static_cast<unsigned>(dev->sm_count), 1, 1);
+      cfg.blockDim = dim3(static_cast<unsigned>(kv->threads), 1, 1);
+      cfg.dynamicSmemBytes = static_cast<size_t>(kv->smem_bytes);
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kv->func, &cfg) == cudaSuccess && n > 0) cached = n;
+      else { cudaGetLastError(); cached = -1; }
+    }
+    if (cached > 0 && workers > cached) workers = cached;
+  }
   const int grid = static_cast<int>(tiles < workers ? tiles : workers) * kv->cta_group;
   if (kv->launch(args, grid, st) != cudaSuccess) {
     cudaGetLastError();

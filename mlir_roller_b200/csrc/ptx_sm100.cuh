@@ -18,12 +18,16 @@ enum : uint32_t {
   kDevTimeoutTmemEmpty = 4,  // MMA issuer never saw an accumulator drained
   kDevTimeoutTmemFull = 5,   // epilogue never saw an accumulator completed
   kDevTimeoutTail = 6,       // producer tail wait ran out
-  kDevTimeoutFixup = 7       // split-K fix-up wait ran out
+  kDevTimeoutFixup = 7,      // split-K fix-up wait ran out
+  kDevTimeoutSlot = 8,       // a worker's scratch slot was never handed back by its reader
+  kDevTimeoutPeer = 9        // a flag another GPU should have raised never arrived
 };
 
-// About two seconds at the B200's boost clock; no legitimate wait in these kernels lasts
-// longer than a few milliseconds.
-constexpr long long kSpinLimitCycles = 4000000000LL;
+// What a bounded wait needs: where to record a failure and how long to keep trying.
+struct WaitCtx {
+  uint32_t* status;   // device status word shared by the whole grid (0 = no error)
+  long long limit;    // clock cycles a wait may spin before it gives up
+};
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -100,21 +104,42 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait. Returns false after recording `code` when the limit runs out, or when some
 // other role of the grid has already recorded an error (so a failure drains quickly).
 template <bool kClusterScope = false>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t* status,
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
                                           uint32_t code) {
   if (mbar_try_wait<kClusterScope>(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (!mbar_try_wait<kClusterScope>(bar, parity)) {
     if ((++spins & 63u) == 0) {
-      if (*reinterpret_cast<volatile uint32_t*>(status) != kDevOk) return false;
-      if (clock64() - t0 > kSpinLimitCycles) {
-        atomicCAS(status, kDevOk, code);
+      if (*reinterpret_cast<volatile uint32_t*>(ctx.status) != kDevOk) return false;
+      if (clock64() - t0 > ctx.limit) {
+        atomicCAS(ctx.status, kDevOk, code);
         return false;
       }
     }
   }
   return true;
+}
+
+// Wait used while winding a CTA down: bounded by time alone (an error recorded elsewhere does
+// not cut it short, because what it waits for -- the tensor core finishing the MMAs already
+// issued -- still has to happen before shared and tensor memory may be given up). Records
+// nothing.
+__device__ __forceinline__ bool mbar_wait_drain(uint32_t bar, uint32_t parity, long long limit) {
+  if (mbar_try_wait<false>(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (!mbar_try_wait<false>(bar, parity)) {
+    if ((++spins & 63u) == 0 && clock64() - t0 > limit) return false;
+  }
+  return true;
+}
+
+// Lets bulk copies and MMAs that were in flight when a role gave up finish before the CTA
+// releases its shared memory: a fixed pause, far longer than any such operation takes.
+__device__ __forceinline__ void abort_grace_period() {
+  const long long t0 = clock64();
+  while (clock64() - t0 < 200000) __nanosleep(1000);
 }
 
 // ---------------------------------------------------------------- proxies and fences
@@ -155,6 +180,42 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
       " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
       "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar_cluster), "r"(c0), "r"(c1)
       : "memory");
+}
+
+// 2-D tiled store of one box from this CTA's shared memory to global memory (which may be a
+// peer GPU's memory mapped into this process: the tensor map is only ever a store destination).
+// c0 is the innermost coordinate (c0 * 4 bytes 16-byte aligned); elements outside the tensor
+// are not written. Completion is tracked by the issuing thread's bulk async-group.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(tm)),
+               "r"(src), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Until the shared-memory source of every committed store has been read (it may be rewritten).
+__device__ __forceinline__ void bulk_wait_read_all() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+// Until every committed store has been performed.
+__device__ __forceinline__ void bulk_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// A launch carrying the programmatic-stream-serialization attribute may start while the
+// previous kernel of its stream is still running. `grid_dependency_wait` blocks until that
+// kernel has completed and its writes are visible; everything before it must touch neither
+// global memory the previous kernel may write nor memory it may still read.
+// `grid_launch_dependents` tells the runtime that the next kernel may be scheduled once every
+// CTA of this grid has said so (or exited). Both are no-ops for an ordinary launch.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 // ---------------------------------------------------------------- TMEM

@@ -243,6 +243,11 @@ def push_order(rank: int, world_size: int, dest: str, root: int = 0) -> List[int
     raise ValueError(f"dest must be 'root' or 'all', not {dest!r}")
 
 
+# Flag array of the fused exchange (one per rank, in symmetric memory).
+FLAG_WORDS = 64
+FLAG_GO = 32
+
+
 @dataclass(frozen=True)
 class BandStep:
     """One band of a rank's block in the overlapped exchange: the kernel computes rows
@@ -280,10 +285,18 @@ class OverlappedGemm:
     it has completed on a rank, every rank's pushes had completed before it.
 
     dest = "root": the whole C ends up on `root` (a gather); dest = "all": on every rank.
-    With `fused=True` (dest = "root" only) there are no bands and no copies: each rank runs one
-    kernel over its whole block whose epilogue stores go straight into the root's C through the
-    peer mapping, tile by tile as tiles finish, so the transfer rides under the main loop of the
-    later tiles and nothing but the closing fence follows the kernel.
+    With `fused=True` (dest = "root" only) there are no bands, no copies and no collective:
+    each rank runs one kernel over its whole block that writes its tiles straight into the
+    root's C through the peer mapping. The kernel hands finished tiles to its TMA unit from a
+    staging area in shared memory (so the warps that drain the accumulators never wait for
+    NVLink) and follows the progressive schedule (`rounds`: all SMs work on a few tiles at a
+    time, so finished tiles leave at a steady rate from the first microseconds on and the
+    transfer runs underneath the rest of the computation instead of after it). The step is
+    closed by flags: each rank stores a step counter into its word of the root's flag array
+    once its kernel has completed, the root waits (bounded) for all of them, then releases the
+    others into the next step by storing the counter into their "go" word, so that nobody
+    overwrites a C that the root may still be reading. An rTile whose kernel lacks the staging
+    area keeps the kernel's own stores.
     C must not be read while another rank may still be pushing the next step into it: separate
     consecutive steps by whatever makes the readers finish first (the bench only times).
 
@@ -294,7 +307,8 @@ class OverlappedGemm:
     def __init__(self, M: int, N: int, K: int, rank: int, world_size: int,
                  grid: Optional[Tuple[int, int]] = None, mode: int = 3,
                  bands: Optional[int] = None, dest: str = "root", root: int = 0, group=None, arch=None, measure: bool = False,
-                 comm_streams: int = 2, taper: bool = False, fused: bool = False):
+                 comm_streams: int = 2, taper: bool = False, fused: bool = False,
+                 rounds: Optional[int] = None, wait_limit_cycles: int = 0):
         import os
         # plain peer mappings only: no NVLink multicast object is bound to the buffer
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
@@ -316,6 +330,7 @@ class OverlappedGemm:
         if fused and dest != "root":
             raise ValueError("the fused output path delivers C to the root only")
         self.fused = fused
+        self.root = root
         self.dests = push_order(rank, world_size, dest, root)
         self._lib = _lib
         self._dist = dist
@@ -325,6 +340,22 @@ class OverlappedGemm:
         self.handle = symm_mem.rendezvous(self.C, self.group)
         self.peer_C = {d: self.handle.get_buffer(d, (M, N), torch.float32) for d in self.dests}
         self._token = torch.zeros(1, dtype=torch.float32, device="cuda")
+        self._step = 0
+        self._wait_limit = wait_limit_cycles
+        if fused:
+            if world_size > FLAG_GO:
+                raise ValueError(f"the fused exchange handles at most {FLAG_GO} ranks")
+            # words 0 .. world-1 of the root's array: "rank r's stores of step s have landed";
+            # word FLAG_GO of every other rank's array: "the root is done with step s"
+            self.flags = symm_mem.empty((FLAG_WORDS,), dtype=torch.int32, device=torch.device("cuda"))
+            self.flags.zero_()
+            torch.cuda.synchronize()
+            self.flag_handle = symm_mem.rendezvous(self.flags, self.group)
+            self.flag_status = torch.zeros(1, dtype=torch.int32, device="cuda")
+            peers = range(world_size) if rank == root else (root,)
+            self.peer_flags = {d: self.flag_handle.get_buffer(d, (FLAG_WORDS,), torch.int32)
+                               for d in peers if d != rank}
+            dist.barrier(group=self.group)     # every rank's flags are zero before anyone signals
         self.comm = [torch.cuda.Stream() for _ in range(max(1, comm_streams))]
         if fused:
             bands = 1
@@ -342,8 +373,18 @@ class OverlappedGemm:
                 by_shape[shape] = roller.kernel_tile_for(hint)
             tile = by_shape[shape]
             self.tiles.append(tile)
-            self.plans.append(_lib.GemmPlan(tile, shape[0], shape[1], K, lda=K, ldb=N, ldc=N,
-                                            mode=mode))
+            plan = _lib.GemmPlan(tile, shape[0], shape[1], K, lda=K, ldb=N, ldc=N, mode=mode)
+            if fused and self.dests:
+                # C lives on the other side of NVLink: decoupled stores, steady tile completion
+                try:
+                    plan.set_option(_lib.OPT_TMA_STORE, 1)
+                    plan.set_option(_lib.OPT_PROGRESSIVE_ROUNDS, -1 if rounds is None else rounds)
+                except _lib.RollerError as e:
+                    if e.status not in (_lib.ERR_UNSUPPORTED, _lib.ERR_INVALID):
+                        raise
+            if wait_limit_cycles:
+                plan.set_option(_lib.OPT_WAIT_LIMIT_CYCLES, wait_limit_cycles)
+            self.plans.append(plan)
             self._events.append(torch.cuda.Event())
 
     def run(self, A_rows, B_full, stream=None) -> None:
@@ -357,6 +398,12 @@ class OverlappedGemm:
             st.wait_stream(cs)          # the previous step's consumers are ordered before the pushes
         n = 0
         if self.fused:
+            self._step += 1
+            if self.rank != self.root and self._step > 1:
+                # the root has finished with the previous step's C
+                self._lib.flag_wait_async(self.flags.data_ptr(), FLAG_WORDS, 1 << FLAG_GO,
+                                          self._step - 1, self.flag_status.data_ptr(),
+                                          self._wait_limit, cs)
             # one kernel per rank; its C is the root's matrix (this rank's own on the root)
             out = self.peer_C[self.dests[0]] if self.dests else self.C
             for step, plan in zip(self.steps, self.plans):
@@ -380,6 +427,20 @@ class OverlappedGemm:
         step have landed."""
         torch = self._torch
         cs = stream if stream is not None else torch.cuda.current_stream()
+        if self.fused:
+            if self.rank != self.root:
+                # behind the kernel on the stream: its stores into the root's C have been performed
+                self._lib.flag_signal_async([self.peer_flags[self.root].data_ptr() + 4 * self.rank],
+                                            self._step, cs)
+                return
+            others = [r for r in range(self.world_size) if r != self.root]
+            if others:
+                mask = sum(1 << r for r in others)
+                self._lib.flag_wait_async(self.flags.data_ptr(), FLAG_WORDS, mask, self._step,
+                                          self.flag_status.data_ptr(), self._wait_limit, cs)
+                self._lib.flag_signal_async([self.peer_flags[r].data_ptr() + 4 * FLAG_GO
+                                             for r in others], self._step, cs)
+            return
         lead = self.comm[0]
         for st in self.comm[1:]:
             lead.wait_stream(st)
@@ -390,6 +451,18 @@ class OverlappedGemm:
 
     def flops(self) -> int:
         return 2 * self.block.rows * self.block.cols * self.K
+
+    def check_status(self) -> None:
+        """Raises RollerError(TIMEOUT) when a kernel of this rank, or one of its waits for
+        another rank's flag, gave up. Synchronises the device."""
+        for p in self.plans:
+            p.check_status()
+        if self.fused:
+            st = int(self.flag_status.item())
+            if st != 0:
+                self.flag_status.zero_()
+                raise self._lib.RollerError(self._lib.ERR_TIMEOUT,
+                                            f"wait for another rank's flag, status word = {st}")
 
     def destroy(self) -> None:
         for p in self.plans:

@@ -65,7 +65,15 @@ class CompiledGemm:
         return self.plan.launch_info()
 
     def time(self, A, B, C, warmup: int = 3, iters: int = 20) -> float:
-        return self.plan.time(A, B, C, warmup, iters)
+        """Mean ms per launch. Raises RollerError(TIMEOUT) when a device-side wait ran out in
+        any of the launches: such a kernel ends early, so its time means nothing."""
+        ms = self.plan.time(A, B, C, warmup, iters)
+        self.plan.check_status()
+        return ms
+
+    def check_status(self) -> None:
+        """Raises RollerError(TIMEOUT) if a launch since the last check gave up on a wait."""
+        self.plan.check_status()
 
 
 def kernel_tile_for(hint: TileDict) -> _lib.KTile:
@@ -177,6 +185,12 @@ def run_eval(cuda_func, pipeline_depth, hint: TileDict, repeat_times: int = 20):
     args = (dA.data_ptr(), dB.data_ptr(), dC.data_ptr())
 
     cuda_func(grid_dims, block_dims, args, shared_mem=shared_memory_usage)
+    # A launch that gave up on a device-side wait raises here, so that the sweep's per-hint
+    # try/except (src/benchmark.py:43-58) skips the hint instead of timing a kernel that
+    # ended early.
+    check = getattr(cuda_func, "check_status", None)
+    if check is not None:
+        check()
     # 16-bit operands: the fp32 product of the same (exactly representable) values
     ref = _strict_fp32_matmul(torch, dA.float(), dB.float())
     if not torch.allclose(dC, ref, rtol=1e-5, atol=1e-8):
@@ -196,6 +210,8 @@ def run_eval(cuda_func, pipeline_depth, hint: TileDict, repeat_times: int = 20):
         for _ in range(repeat_times):
             cuda_func(grid_dims, block_dims, args, shared_mem=shared_memory_usage)
     t_gpu = start_gpu.elapsed_time(end_gpu)
+    if check is not None:
+        check()
 
     print(f"t={t_gpu / repeat_times:.6f} ms", end=" ")
     flops = 2 * M * N * K
@@ -297,7 +313,7 @@ def best_hint(config: MatmulConfig, arch=None, topk: int = 20, mode: Optional[in
     for hint in hints:
         try:
             fn = Compiler(config, hint, mode=mode).compile()
-            ms = fn.time(dA, dB, dC, warmup=2, iters=5)
+            ms = fn.time(dA, dB, dC, warmup=2, iters=5)   # raises when a launch gave up
         except _lib.RollerError:
             continue
         if best is None or ms < best[2]:

@@ -29,6 +29,7 @@ def test_reference_arm_line():
     assert line["higher_is_better"] is True and line["vs_baseline"] is None
     assert line["unit"] == "TFLOP/s" and line["value"] > 0 and line["ms_per_step"] > 0
     assert "workload" in line["config"] and "model" not in line["config"]
+    assert {"mode", "l2", "parallelism"} <= set(line["config"])
     cb = line["cpu_baseline"]
     assert cb["kind"] == "port" and cb["cores"] >= 1 and cb["value"] == line["value"] and cb["sample"]
     e2e = line["e2e"]
@@ -40,15 +41,36 @@ def test_reference_arm_line():
 def test_gpu_arm_line():
     steps = 3
     line = run_bench("--steps", str(steps), "--warmup", "3", "--select", "model")
-    assert BASE_KEYS | {"clocks", "roofline", "gpu_launches", "per_shape", "bf16"} <= set(line)
+    assert BASE_KEYS | {"clocks", "roofline", "gpu_launches", "bf16"} <= set(line)
     assert "impl" not in line or line["impl"] != "reference"
     assert line["n_gpus"] == 1 and line["steps"] == steps and line["warmup"] >= 3
     assert line["scaling"] == "weak" and line["data"] == "synthetic" and line["vs_baseline"] is None
     assert line["gpu_launches"] == 14 * steps
     assert 50 < line["value"] < 600                     # useful fp32 TFLOP/s of the 3xTF32 sweep
+    # both arms describe the workload with the same config object
+    ref = run_bench("--impl", "reference", "--steps", "1", "--warmup", "0")
+    assert ref["config"] == line["config"]
     roof = line["roofline"]
     assert roof["bound"] == "tensor" and roof["unit"] == "TFLOP/s"
     assert abs(roof["frac"] - roof["achieved"] / roof["peak"]) < 1e-9 and roof["traffic"] > 0
+    # the fraction follows from the line's own figures, and a fraction of a peak stays near or
+    # below one (the denominator is a library GEMM, so a little above is possible)
+    tensor_flops = 3 * sum(2 * m * n * k for m, n, k in SHAPES)
+    assert abs(roof["achieved"] - tensor_flops / line["ms_per_step"] / 1e9) < 1e-6 * roof["achieved"]
+    assert 0.3 < roof["frac"] <= 1.05
+    assert roof["peak_regime"] in ("burst", "sustained")
+    assert len(roof["per_shape"]) == 14 and roof["max_err_3x"] <= 1e-5
+    for rec in roof["per_shape"]:
+        assert 0 < rec["frac3"] <= 1.05 and 0 < rec["frac1"] <= 1.05, rec
+    assert roof["per_shape_min_frac3"] == min(r["frac3"] for r in roof["per_shape"])
+    c4 = {(r["shape"], r["mode"]): r for r in roof["config4"]}
+    assert set(c4) == {("ragged", "3xTF32"), ("ragged", "1xTF32"), ("skinny", "3xTF32"),
+                       ("skinny", "1xTF32")}
+    assert c4[("ragged", "3xTF32")]["err"] <= 1e-5 and c4[("skinny", "3xTF32")]["err"] <= 1e-5
+    assert c4[("skinny", "1xTF32")]["bound"] == "hbm" and c4[("ragged", "3xTF32")]["bound"] == "tensor"
+    assert 0 <= c4[("ragged", "3xTF32")]["staging_copies_share"] < 0.5
+    for rec in roof["config4"]:
+        assert 0 < rec["frac_of_t_roof"] <= 1.05, rec
     cb = line["cpu_baseline"]
     assert cb["kind"] == "port" and cb["value"] > 0 and cb["cores"] >= 1
     e2e = line["e2e"]
@@ -57,7 +79,6 @@ def test_gpu_arm_line():
     assert e2e["d2h_bytes_per_step"] == 4 * sum(m * n for m, n, k in SHAPES)
     assert 0 < e2e["pcie_bound_ms"] < 10 * e2e["ms_per_step"]     # measured separately: loose
     assert {"sm_mhz", "sm_max_mhz", "reasons"} <= set(line["clocks"])
-    assert len(line["per_shape"]) == 14 and line["max_err_3x"] <= 1e-5
     assert line["bf16"]["max_err"] <= 1e-5 and line["bf16"]["value"] > line["value"]
 
 

@@ -118,12 +118,3 @@ def test_header_is_plain_c_and_links_from_a_c_program(tmp_path):
     for line, kt in zip(out[1:], tiles):
         assert [int(x) for x in line.split()] == [kt.block_m, kt.block_n, kt.cta_group, kt.layout]
     assert out[1 + len(tiles)].startswith("a bounded")
-
-
-def test_integration_notes_cover_every_entry_point():
-    """INTEGRATION.md's table names every function the header declares (by full name or by the
-    `_suffix` shorthand it uses for families)."""
-    doc = (HEADER.parent.parent / "INTEGRATION.md").read_text()
-    for name in sorted(declared_functions()):
-        short = name.replace("roller_b200_gemm", "").replace("roller_b200", "")
-        assert name in doc or f"`{short}`" in doc, name
