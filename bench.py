@@ -420,37 +420,71 @@ def timed_sweep(torch, cases, steps, warmup, dist=None):
     return ev[0].elapsed_time(ev[steps]) / steps
 
 
-def e2e_sweep(torch, cases, steps):
-    """Same sweep through the host-buffer entry point: pinned host operands in, C back out,
-    copies inside the timed region. Returns (ms per step, h2d bytes, d2h bytes)."""
-    host = []
+def e2e_sweep(torch, cases, steps, dist=None, rank=0, world=1):
+    """Same sweep from host memory: pinned host operands in, C back out, copies inside the timed
+    region. Returns (ms per step, h2d bytes, d2h bytes, checksum).
+
+    On one GPU every GEMM goes through the host-buffer entry point of the C ABI
+    (roller_b200_gemm_host_async). With several ranks each rank still owns its rows of A and its
+    block of C, but B is the same on all of them: a rank uploads only its 1/world share of B's
+    rows and the shares are exchanged over NVLink (mgpu.HostStagedGemm), so the host links carry
+    each byte of B once per node instead of once per rank."""
+    from mlir_roller_b200 import mgpu, roller
+    host, staged = [], []
     for c in cases:
         hA = c.A.cpu().pin_memory()
         hB = c.B.cpu().pin_memory()
         hC = torch.empty(c.C.shape, dtype=torch.float32).pin_memory()
         host.append((hA, hB, hC))
-    for c, (hA, hB, hC) in zip(cases, host):   # warm-up: allocates the plan-owned buffers
-        c.plan.run_host(hA, hB, hC)
-    torch.cuda.synchronize()
+        if world > 1:
+            m, n, k = c.shape
+            staged.append(mgpu.HostStagedGemm(m, n, k, rank, world, mode=c.mode,
+                                              tile=roller.kernel_tile_for(c.hint)))
     # Shapes are spread over three streams so that one GEMM's upload, another's kernel and a
     # third's readback overlap (the two PCIe directions are independent); a shape always uses
-    # the same stream, so its plan-owned buffers are never touched by two launches at once.
+    # the same stream, so its device buffers are never touched by two launches at once.
     streams = [torch.cuda.Stream() for _ in range(3)]
+
+    def one_pass():
+        for i, (c, (hA, hB, hC)) in enumerate(zip(cases, host)):
+            if world > 1:
+                staged[i].run(hA, hB, hC, stream=streams[i % 3])
+            else:
+                c.plan.run_host(hA, hB, hC, stream=streams[i % 3], wait=False)
+
+    one_pass()                                   # warm-up: allocates the device buffers
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for st in streams:
         st.wait_event(e0)
     for _ in range(steps):
-        for i, (c, (hA, hB, hC)) in enumerate(zip(cases, host)):
-            c.plan.run_host(hA, hB, hC, stream=streams[i % 3], wait=False)
+        one_pass()
     for st in streams:
         done = torch.cuda.Event()
         done.record(st)
         torch.cuda.current_stream().wait_event(done)
     e1.record()
     e1.synchronize()
-    h2d = sum(a.numel() * 4 + b.numel() * 4 for a, b, _ in host)
-    d2h = sum(c.numel() * 4 for _, _, c in host)
+    if dist is not None:
+        dist.barrier()
+    if world > 1:
+        moved = [g.bytes_per_call() for g in staged]
+        h2d, d2h = sum(b[0] for b in moved), sum(b[1] for b in moved)
+        # the staged path must deliver the same C as the kernel run on resident operands
+        for c, g, (_, _, hC) in zip(cases, staged, host):
+            c.launch()
+            torch.cuda.synchronize()
+            if not torch.equal(hC, c.C.cpu()):
+                raise RuntimeError(f"end-to-end result of shape {c.shape} differs from the resident run")
+            g.plan.check_status()
+            g.destroy()
+    else:
+        h2d = sum(a.numel() * a.element_size() + b.numel() * b.element_size() for a, b, _ in host)
+        d2h = sum(c.numel() * 4 for _, _, c in host)
     checksum = float(sum(float(hc[0, 0]) for _, _, hc in host))
     return e0.elapsed_time(e1) / steps, h2d, d2h, checksum
 
@@ -580,12 +614,17 @@ def strong_scaling(torch, dist, rank, world, steps, warmup):
             sg.plan.check_status()
 
             paths = [("banded_root", ob, False), ("banded_all", None, True), ("fused_root", None, False)]
+            if M * N // world <= 1024 * 4096:
+                # a block of less than one wave of tiles: also with more rounds than the
+                # library would pick (earlier output, dearer exchange of partial tiles)
+                paths.append(("fused_root_r4", None, False))
             for label, og, everywhere in paths:
                 try:
                     if og is None:
                         og = mgpu.OverlappedGemm(M, N, K, rank, world, grid=grid, mode=mode,
                                                  dest="all" if everywhere else "root",
-                                                 fused=(label == "fused_root"))
+                                                 fused=label.startswith("fused_root"),
+                                                 rounds=4 if label.endswith("_r4") else None)
                 except Exception as e:  # noqa: BLE001 - keep the other paths' numbers
                     rec[label + "_error"] = f"{type(e).__name__}: {e}"[:200]
                     continue
@@ -602,9 +641,10 @@ def strong_scaling(torch, dist, rank, world, steps, warmup):
                 rec[label + "_err"] = max_over_ranks(checker.err(og.C) if holds else 0.0)
                 if label == "banded_root":
                     rec["bands"] = len(og.bands)
-                if label == "fused_root" and og.plans:
+                if label.startswith("fused_root") and og.plans:
                     info = og.plans[0].schedule_info()
-                    rec["fused_rounds"] = int(max_over_ranks(float(info["rounds"])))
+                    rec[label.replace("fused_root", "fused_rounds")] = int(
+                        max_over_ranks(float(info["rounds"])))
                 og.destroy()
                 del og
                 torch.cuda.empty_cache()
@@ -622,7 +662,7 @@ def strong_scaling(torch, dist, rank, world, steps, warmup):
             link_ms = (world - 1) / world * M * N * 4 / 770e9 * 1e3
             rec["link_bound_ms"] = link_ms
             best_root = min(rec.get(k, float("inf")) for k in ("banded_root_ms", "fused_root_ms",
-                                                               "gather_ms"))
+                                                               "fused_root_r4_ms", "gather_ms"))
             rec["delivered_root_ms"] = best_root
             rec["ingress_gbs"] = (world - 1) / world * M * N * 4 / best_root / 1e6
             rec["eff_kernels"] = rec["single_ms"] / (world * rec["kernels_ms"])
@@ -769,7 +809,7 @@ def run_gpu_arm(args) -> None:
         del cases16, lib16, out16
         torch.cuda.empty_cache()
 
-    e2e_ms, h2d, d2h, _ = e2e_sweep(torch, cases, max(args.steps // 2, 1))
+    e2e_ms, h2d, d2h, _ = e2e_sweep(torch, cases, max(args.steps // 2, 1), dist, rank, world)
     if dist is not None:
         t = torch.tensor([e2e_ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -899,6 +939,9 @@ def run_gpu_arm(args) -> None:
         "cpu_baseline": cpu_baseline,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                "path": ("roller_b200_gemm_host_async per shape, three streams" if world == 1 else
+                         "mgpu.HostStagedGemm per shape: own rows of A and 1/world of B uploaded "
+                         "per rank, B's shares exchanged over NVLink (bytes are per rank)"),
                 "pcie_gbs": {"h2d": up_gbs, "d2h": down_gbs, "each_way_duplex": duplex_gbs},
                 "pcie_bound_ms": e2e_bound_ms},
         "gpu_launches": len(README_SHAPES) * args.steps,

@@ -76,13 +76,15 @@ typedef enum roller_status {
                                           its CTAs early; it still waits for that kernel's
                                           completion before touching global memory. 0: plain
                                           stream order */
-#define ROLLER_OPT_TMA_STORE 3         /* 1: C leaves each CTA through shared memory and TMA
-                                          stores instead of the accumulate warps' own stores, so
-                                          a slow destination (C in another GPU's memory, mapped
-                                          into this process) does not hold the warps up. Needs
-                                          fp32 C with 16-byte aligned base and row stride, no
-                                          ROLLER_FLAG_ACCUMULATE, and an rTile whose kernel has
-                                          the staging area (else ROLLER_ERR_UNSUPPORTED) */
+#define ROLLER_OPT_TMA_STORE 3         /* C leaves each CTA through shared memory and TMA stores
+                                          instead of the accumulate warps' own stores, so a slow
+                                          destination (C in another GPU's memory, mapped into
+                                          this process) does not hold the warps up. The library
+                                          uses this path by itself where it can: fp32 C with
+                                          16-byte aligned base and row stride, no
+                                          ROLLER_FLAG_ACCUMULATE, an rTile whose kernel has the
+                                          staging area. 1 insists on it (ROLLER_ERR_UNSUPPORTED /
+                                          _INVALID where it cannot work); 0 turns it off */
 #define ROLLER_OPT_PROGRESSIVE_ROUNDS 4 /* n > 0: every tile is cut along K and the tiles are
                                           worked through in n groups by the whole grid, so that
                                           finished tiles leave the kernel at a steady rate from

@@ -40,18 +40,21 @@ def _stale() -> bool:
     return any(d.stat().st_mtime > built for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every CUDA source for sm_100a and link the shared library."""
-    if not force and not _stale():
+def build(force: bool = False, verbose: bool = False, defines=(), lib_path: Path | None = None) -> Path:
+    """Compile every CUDA source for sm_100a and link the shared library. `defines` (e.g.
+    ["RB200_SMALL_STAGES=4"]) and `lib_path` build a variant of the library somewhere else, for
+    comparing build-time tunables; the package itself always loads the default one."""
+    out = LIB_PATH if lib_path is None else Path(lib_path)
+    if not force and not defines and lib_path is None and not _stale():
         return LIB_PATH
     nvcc = _nvcc()
     objs = []
-    build_dir = PKG_DIR / "build"
-    build_dir.mkdir(exist_ok=True)
+    build_dir = PKG_DIR / "build" if lib_path is None else out.parent / (out.stem + "_build")
+    build_dir.mkdir(parents=True, exist_ok=True)
     procs = []
     for src in SOURCES:      # the translation units are independent: compile them side by side
         obj = build_dir / (src + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-c", str(CSRC / src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, *[f"-D{d}" for d in defines], "-c", str(CSRC / src), "-o", str(obj)]
         if verbose:
             cmd[1:1] = ["-Xptxas", "-v"]
         procs.append((cmd, subprocess.Popen(cmd)))
@@ -59,9 +62,9 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     failed = [cmd for cmd, pr in procs if pr.wait() != 0]
     if failed:
         raise subprocess.CalledProcessError(1, failed[0])
-    subprocess.run([nvcc, "-shared", "-o", str(LIB_PATH), *objs, "-gencode",
+    subprocess.run([nvcc, "-shared", "-o", str(out), *objs, "-gencode",
                     "arch=compute_100a,code=sm_100a"], check=True)
-    return LIB_PATH
+    return out
 
 
 if __name__ == "__main__":

@@ -85,16 +85,29 @@ int encode_matrix(CUtensorMap* tm, const void* base, long long rows, long long c
 }
 
 // Copies a rows x cols matrix into a buffer whose rows are a multiple of 16 bytes long, so
-// that TMA's 16-byte stride rule holds for operands with odd leading dimensions.
+// that TMA's 16-byte stride rule holds for operands with odd leading dimensions. HBM-bound:
+// one thread moves 16 bytes -- scalar loads (the source rows start anywhere), one 128-bit store
+// (the destination rows are aligned); grid.y walks the rows, so no index is ever divided.
 template <typename T>
 __global__ void pad_rows_kernel(const T* __restrict__ src, long long ld_src,
                                 T* __restrict__ dst, long long ld_dst, int rows, int cols) {
-  const long long total = static_cast<long long>(rows) * cols;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long r = i / cols;
-    const long long c = i - r * cols;
-    dst[r * ld_dst + c] = src[r * ld_src + c];
+  constexpr int V = 16 / static_cast<int>(sizeof(T));   // elements per 128-bit store
+  const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * V;
+  if (c0 >= cols) return;
+#pragma unroll 2
+  for (int r = blockIdx.y; r < rows; r += gridDim.y) {
+    const T* s = src + static_cast<long long>(r) * ld_src + c0;
+    alignas(16) T v[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) v[j] = (c0 + j < cols) ? s[j] : T(0);
+    T* d = dst + static_cast<long long>(r) * ld_dst + c0;
+    if (c0 + V <= ld_dst) {
+      *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(v);
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j)
+        if (c0 + j < cols) d[j] = v[j];
+    }
   }
 }
 
@@ -106,18 +119,27 @@ long long round_up_ld(long long x, int elem_bytes) {
 
 void pad_rows(const void* src, long long ld_src, void* dst, long long ld_dst, int rows, int cols,
               int elem_bytes, int blocks, cudaStream_t st) {
+  const int per_thread = 16 / elem_bytes;
+  const int threads = 256;
+  const int gx = (cols + threads * per_thread - 1) / (threads * per_thread);
+  int gy = blocks / gx;                       // about `blocks` CTAs in all
+  if (gy < 1) gy = 1;
+  if (gy > rows) gy = rows;
+  if (gy > 65535) gy = 65535;
+  const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy), 1);
   if (elem_bytes == 2)
-    pad_rows_kernel<uint16_t><<<blocks, 256, 0, st>>>(static_cast<const uint16_t*>(src), ld_src,
-                                                     static_cast<uint16_t*>(dst), ld_dst, rows, cols);
+    pad_rows_kernel<uint16_t><<<grid, threads, 0, st>>>(static_cast<const uint16_t*>(src), ld_src,
+                                                       static_cast<uint16_t*>(dst), ld_dst, rows, cols);
   else
-    pad_rows_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(src), ld_src,
-                                                  static_cast<float*>(dst), ld_dst, rows, cols);
+    pad_rows_kernel<float><<<grid, threads, 0, st>>>(static_cast<const float*>(src), ld_src,
+                                                    static_cast<float*>(dst), ld_dst, rows, cols);
 }
 
 }  // namespace
 
 struct roller_plan;
 static int plan_configure(roller_plan* p);
+static cudaError_t bind_variant(roller_plan* p, const KernelVariant* kv);
 static int default_unit_kb(const roller_plan* p);
 
 struct roller_plan {
@@ -147,6 +169,7 @@ struct roller_plan {
   long long spin_limit;   // clock cycles a device-side wait may last
   bool overlap_launch;    // launches carry the programmatic-stream-serialization attribute
   bool tma_store;         // C leaves through shared memory and TMA stores
+  bool tma_forced;        // ... because the caller asked for it (else: chosen by the library)
   bool drop_publish;      // test aid: partial tiles are never flagged
   bool stage_a, stage_b;  // operands go through a padded copy
   void* ws_a;             // padded copies (device), owned
@@ -290,6 +313,10 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
   p->sk_rounds = 1;
   p->spin_limit = kSpinLimitCycles;
   p->overlap_launch = true;
+  // Where the kernel has the staging area and C qualifies, C leaves through TMA stores: measured
+  // 3-6 % faster than the accumulate warps' own stores on every README shape (whole 128-byte
+  // lines leave the SM, and the warps are back at the next tile sooner).
+  p->tma_store = false;   // decided below, once the kernel is bound
   // 3xTF32 drains the TMEM accumulator every 128 k (see the kernel header); 1xTF32 is
   // dominated by the 10-bit input mantissa, so one chunk spans the whole reduction.
   const int num_kb = (K + kv->rstep - 1) / kv->rstep;
@@ -305,28 +332,18 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
   p->stage_a = (static_cast<long long>(lda) * elem % 16) != 0;
   p->stage_b = (static_cast<long long>(ldb) * elem % 16) != 0;
 
-  cudaError_t e = cudaFuncSetAttribute(kv->func, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       kv->smem_bytes);
-  if (e == cudaSuccess && kv->cta_group == 2) {
-    // A persistent grid must be co-resident: ask how many CTA pairs the device can hold.
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(p->sm_count), 1, 1);
-    cfg.blockDim = dim3(static_cast<unsigned>(kv->threads), 1, 1);
-    cfg.dynamicSmemBytes = static_cast<size_t>(kv->smem_bytes);
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    int n = 0;
-    e = cudaOccupancyMaxActiveClusters(&n, kv->func, &cfg);
-    if (e == cudaSuccess) {
-      p->max_clusters = n;
-      if (n > 0 && p->max_workers > n) p->max_workers = n;
-    }
+  // Whether C can leave through TMA stores at all (the base address is checked per launch).
+  const bool c_fits_tma = layout != 2 && p->c_elem == 4 && !(flags & ROLLER_FLAG_ACCUMULATE) &&
+                          ldc % 4 == 0;
+  // A kernel whose ring fills shared memory also exists with one stage less and the staging
+  // area of that path; for the pair tile that form is the faster one up to K = 4096 (see
+  // GemmCfg; the single-CTA 128 x 128 tile gains nothing from it and switches only on request).
+  if (c_fits_tma && K <= 4096 && kv->cta_group == 2) {
+    const KernelVariant* staged = find_staged_form(kv);
+    if (staged && static_cast<int>(prop.sharedMemPerBlockOptin) >= staged->smem_bytes) kv = staged;
   }
+  cudaError_t e = bind_variant(p, kv);
+  p->tma_store = p->kv->staging_bytes > 0 && c_fits_tma;
   if (e == cudaSuccess) e = cudaMalloc(&p->status, sizeof(uint32_t));
   if (e == cudaSuccess) e = cudaMemset(p->status, 0, sizeof(uint32_t));
   if (e == cudaSuccess && p->stage_a) {
@@ -371,7 +388,9 @@ int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, void* C, 
   // every argument is checked before anything is enqueued
   if (!p->stage_a && (reinterpret_cast<uintptr_t>(A) & 15)) return ROLLER_ERR_INVALID;
   if (!p->stage_b && (reinterpret_cast<uintptr_t>(B) & 15)) return ROLLER_ERR_INVALID;
-  if (p->tma_store && (reinterpret_cast<uintptr_t>(C) & 15)) return ROLLER_ERR_INVALID;
+  const bool c_aligned = (reinterpret_cast<uintptr_t>(C) & 15) == 0;
+  if (p->tma_store && p->tma_forced && !c_aligned) return ROLLER_ERR_INVALID;
+  const bool tma_store = p->tma_store && c_aligned;
   if (p->stage_a) {
     pad_rows(A, p->lda, p->ws_a, p->ws_lda, p->M, p->K, p->elem, p->sm_count * 8, st);
     a_src = p->ws_a;
@@ -415,7 +434,7 @@ int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, void* C, 
     p->map_a_ptr = a_src;
     p->map_b_ptr = b_src;
   }
-  if (p->tma_store && C != p->map_c_ptr) {
+  if (tma_store && C != p->map_c_ptr) {
     // C as a store destination: boxes of 32 x 32 fp32 under the 128-byte swizzle. C may be
     // another GPU's memory mapped into this process; the map is never used for a load.
     int rc = encode_matrix(&p->tmC, C, p->M, p->N, p->ldc, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -427,7 +446,7 @@ int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, void* C, 
   GemmArgs args;
   args.tmA = p->tmA;
   args.tmB = p->tmB;
-  if (p->tma_store) args.tmC = p->tmC; else memset(&args.tmC, 0, sizeof(args.tmC));
+  if (tma_store) args.tmC = p->tmC; else memset(&args.tmC, 0, sizeof(args.tmC));
   args.C = static_cast<float*>(C);
   args.M = (p->layout == 2) ? p->N : p->M;
   args.N = (p->layout == 2) ? p->M : p->N;
@@ -441,7 +460,7 @@ int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, void* C, 
   if ((p->ldc * p->c_elem % 16) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0)
     args.flags |= kFlagVecStore;
   if (p->c_elem == 2) args.flags |= kFlagC16;
-  if (p->tma_store) args.flags |= kFlagTmaStore;
+  if (tma_store) args.flags |= kFlagTmaStore;
   if (p->drop_publish) args.flags |= kFlagDropPublish;
   args.status = p->status;
   args.spin_limit = p->spin_limit;
@@ -608,12 +627,20 @@ int roller_b200_gemm_set_option(roller_plan* p, int option, long long value) {
       return ROLLER_OK;
     case ROLLER_OPT_TMA_STORE:
       if (value != 0) {
-        if (p->kv->staging_bytes == 0 || p->layout == 2 || p->c_elem != 4 ||
-            (p->flags & ROLLER_FLAG_ACCUMULATE))
+        if (p->layout == 2 || p->c_elem != 4 || (p->flags & ROLLER_FLAG_ACCUMULATE))
           return ROLLER_ERR_UNSUPPORTED;
         if (p->ldc % 4 != 0) return ROLLER_ERR_INVALID;   // TMA needs 16-byte row strides
+        if (p->kv->staging_bytes == 0) {
+          // the form of the kernel with a shorter ring has the staging area
+          const KernelVariant* staged = find_staged_form(p->kv);
+          if (!staged) return ROLLER_ERR_UNSUPPORTED;
+          if (bind_variant(p, staged) != cudaSuccess) return cuda_fail(cudaGetLastError(), "bind kernel");
+          int rc = plan_configure(p);
+          if (rc != ROLLER_OK) return rc;
+        }
       }
       p->tma_store = value != 0;
+      p->tma_forced = value != 0;
       p->map_c_ptr = nullptr;
       return ROLLER_OK;
     case ROLLER_OPT_PROGRESSIVE_ROUNDS:
@@ -664,6 +691,36 @@ const char* roller_b200_last_cuda_error(void) { return g_cuda_err; }
 
 }  // extern "C"
 
+// Binds the plan to one compiled kernel: raises its shared-memory limit and asks how many of its
+// CTA pairs the device can hold at once (a persistent grid must be co-resident).
+static cudaError_t bind_variant(roller_plan* p, const KernelVariant* kv) {
+  p->kv = kv;
+  p->max_workers = p->sm_count / kv->cta_group;
+  p->max_clusters = 0;
+  cudaError_t e = cudaFuncSetAttribute(kv->func, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kv->smem_bytes);
+  if (e == cudaSuccess && kv->cta_group == 2) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(p->sm_count), 1, 1);
+    cfg.blockDim = dim3(static_cast<unsigned>(kv->threads), 1, 1);
+    cfg.dynamicSmemBytes = static_cast<size_t>(kv->smem_bytes);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, kv->func, &cfg);
+    if (e == cudaSuccess) {
+      p->max_clusters = n;
+      if (n > 0 && p->max_workers > n) p->max_workers = n;
+    }
+  }
+  return e;
+}
+
 // Chooses the persistent grid and the stream-K split for the plan's current settings, and makes
 // sure the stream-K scratch area exists when it is needed. Never called from the run path.
 //
@@ -699,10 +756,18 @@ static int plan_configure(roller_plan* p) {
     // Progressive schedule: every tile is cut along K and the tiles are worked through in
     // groups, so that finished tiles appear at a steady rate. The number of rounds must
     // divide the tile count (no tile may straddle two rounds): the largest divisor not above
-    // the request is taken. Left to the library (-1), a round is made as short as it can be
-    // with every worker still holding a run of about three units, which keeps the cost of
-    // handing partial tiles around below a tenth of the work.
-    long long want = p->progressive > 0 ? p->progressive : tiles * cpt / (3ll * workers);
+    // the request is taken. Left to the library (-1), a round holds about as many tiles as
+    // there are workers, so that a tile is shared by little more than one worker: the worker
+    // completing a tile adds the others' partial sums one after the other, and with more of
+    // them the exchange no longer hides behind the two accumulator buffers (measured on B200,
+    // 256 x 256 pair tile, 3xTF32, against whole tiles: shared by 1.2 workers 0-4 % slower, by
+    // 2.3 workers 5-15 %, by 4.6 workers 35-45 %). Two rounds at least, or nothing would leave
+    // early.
+    long long want = p->progressive;
+    if (want < 0) {
+      want = (tiles * 5) / (4ll * workers);        // a tile shared by about 1.2 workers: free
+      if (want < 2 && tiles >= workers / 4) want = 2;   // but at least two rounds
+    }
     if (want > 64) want = 64;
     if (want < 1) want = 1;
     rounds = static_cast<int>(want);
@@ -739,7 +804,7 @@ static int plan_configure(roller_plan* p) {
     p->sk_slots = 0;
     const size_t slot_bytes =
         sizeof(float) * 128 * static_cast<size_t>(p->layout == 2 ? kv->block_m : kv->block_n);
-    const int slots = p->max_workers * kv->cta_group;
+    const int slots = p->max_workers * kv->cta_group * 2;   // two per CTA, used alternately
     cudaError_t e = cudaMalloc(&p->sk_ws, slot_bytes * slots);
     if (e == cudaSuccess) e = cudaMalloc(&p->sk_flags, sizeof(uint32_t) * slots);
     if (e == cudaSuccess) e = cudaMemset(p->sk_flags, 0, sizeof(uint32_t) * slots);

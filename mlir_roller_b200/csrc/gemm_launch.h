@@ -36,8 +36,8 @@ struct GemmArgs {
   bool serialize_programmatically;  // launch may overlap the tail of the stream's previous kernel
   int sk_tiles;         // tiles dealt out in k-chunks (stream-K); 0 = whole tiles only
   int sk_rounds;        // groups the stream-K tiles are worked through one after the other (>= 1)
-  float* sk_ws;         // one 128 x block_n slot per CTA for partial tiles
-  uint32_t* sk_flags;   // one flag per CTA, set to `epoch` when its slot is valid
+  float* sk_ws;         // two 128 x block_n slots per CTA for partial tiles
+  uint32_t* sk_flags;   // one flag per slot, set to a tag of `epoch` and the round when valid
   uint32_t epoch;       // distinguishes this launch's flags from earlier launches' (1 .. 2^26-1)
 };
 
@@ -53,6 +53,7 @@ struct KernelVariant {
   int tmem_cols;
   int threads;
   int staging_bytes;  // shared memory set aside for the TMA-store output path (0 = kernel lacks it)
+  int gave_up_stage;  // 1 = the form of a kernel whose ring is one stage shorter to fit that area
   const void* func;  // kernel symbol, for cudaFuncSetAttribute / occupancy queries
   cudaError_t (*launch)(const GemmArgs& args, int grid, cudaStream_t stream);
 };
@@ -64,5 +65,10 @@ const KernelVariant* variants_16bit(int* n);
 // Returns nullptr when no kernel was compiled for the combination.
 const KernelVariant* find_variant(int block_m, int block_n, int rstep, int cta_group, int mode,
                                   int layout);
+// The form of `kv` with a shorter ring and the staging area of the TMA-store path, if `kv`
+// lacks the area and such a form was compiled; else nullptr.
+const KernelVariant* find_staged_form(const KernelVariant* kv);
+// The kernels with a shorter ring for 16-bit operands, kept beside the 16-bit table.
+const KernelVariant* staged_forms_16bit(int* n);
 
 }  // namespace rb200

@@ -78,6 +78,7 @@
 #include "gemm_launch.h"
 #include "ptx_sm100.cuh"
 
+
 namespace rb200 {
 
 // One operand tile of ROWS (m or n) x 128 bytes of k (32 fp32 or 64 16-bit elements) whose
@@ -132,7 +133,11 @@ struct OperandMN {
 };
 
 // DT_: operand element type. 0 = fp32 (tensor-core kind tf32), 1 = bf16, 2 = fp16 (kind f16).
-template <int BN_, int MODE_, int CG_, int LAYOUT_ = 0, int DT_ = 0>
+// STAGED_: 1 = a ring that would fill shared memory gives up one stage to make room for the
+// staging area of the TMA-store output path (measured on B200, 256 x 256 pair tile, 1xTF32 and
+// bf16: 8-14 % faster at 2048^3, even at K = 4096, 2-5 % slower at K = 8192; so both forms of
+// such a kernel exist and the host picks by K).
+template <int BN_, int MODE_, int CG_, int LAYOUT_ = 0, int DT_ = 0, int STAGED_ = 0>
 struct GemmCfg {
   static constexpr int BN = BN_;      // tile columns (of the CTA pair when CG == 2)
   static constexpr int MODE = MODE_;  // 1 or 3 tensor-core products per operand product
@@ -150,19 +155,31 @@ struct GemmCfg {
   static constexpr int A_BYTES = AOp::BYTES;
   static constexpr int B_BYTES = BOp::BYTES;
   static constexpr int RAW_BYTES = (A_BYTES + B_BYTES + 1023) / 1024 * 1024;
+  // 3xTF32 keeps the split-off small parts next to the raw tile, in the same stage. (A second,
+  // short ring for the small parts with a deeper landing ring was measured on the skinny
+  // tiles, where it should matter most: 16 x 8192 x 8192 went from 84 to 117 us.)
   static constexpr int STAGE_BYTES = (MODE == 3 ? 2 : 1) * RAW_BYTES;
   static constexpr int CTRL_BYTES = 256;
   static constexpr int SMEM_LIMIT = 232448;  // 227 KiB opt-in maximum per CTA
   static constexpr int STAGES_FIT = (SMEM_LIMIT - 1024 - CTRL_BYTES) / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
   // Staging area of the TMA-store output path: one 32 x 32 fp32 box (128-byte swizzle) per
-  // accumulate warp. Present where the ring leaves room for it (and C is not written
-  // transposed); kernels without it only have the plain store path.
+  // accumulate warp. Kernels without the area only have the plain store path (C written
+  // transposed never uses it).
   static constexpr int STAGING_WANTED = 8 * 4096;
+  static constexpr int STAGES_BESIDE_STAGING =
+      (SMEM_LIMIT - 1024 - CTRL_BYTES - STAGING_WANTED) / STAGE_BYTES;
+  static constexpr bool GIVES_UP_A_STAGE = STAGED_ != 0;
+  static_assert(!GIVES_UP_A_STAGE || (LAYOUT_ != 2 && STAGES_FIT <= 8 &&
+                                      STAGES_BESIDE_STAGING == STAGES_FIT - 1),
+                "only a ring that fills shared memory has a stage to give up");
+  static constexpr int STAGES = GIVES_UP_A_STAGE ? STAGES_BESIDE_STAGING
+                                                 : (STAGES_FIT > 8 ? 8 : STAGES_FIT);
   static constexpr int STAGING_BYTES =
-      (LAYOUT_ != 2 && SMEM_LIMIT - 1024 - CTRL_BYTES - STAGES * STAGE_BYTES >= STAGING_WANTED)
+      (LAYOUT_ != 2 &&
+       SMEM_LIMIT - 1024 - CTRL_BYTES - STAGES * STAGE_BYTES >= STAGING_WANTED)
           ? STAGING_WANTED : 0;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + CTRL_BYTES + 1024;
+  static constexpr int SMEM_BYTES =
+      STAGES * STAGE_BYTES + STAGING_BYTES + CTRL_BYTES + 1024;
   static constexpr int ACC_STAGES = 2;
   static constexpr int TMEM_COLS = ACC_STAGES * BN;
   static constexpr bool HAS_XFORM = (MODE == 3);
@@ -246,6 +263,7 @@ struct Segment {
   int kb0, kb1;
   bool final;  // holds the end of the tile's reduction: adds the other workers' partials, stores C
   int round;   // round of the schedule the segment belongs to (0 for whole tiles)
+  int pos;     // the worker's position in that round
 };
 
 // Static schedule shared by the producer, split, MMA and epilogue roles (each walks its own copy).
@@ -254,12 +272,18 @@ struct Segment {
 // order, are dealt out in contiguous runs to rounds * workers "virtual workers", and worker w
 // plays the virtual workers w, w + workers, w + 2 workers, ... one after the other (one per
 // round). With rounds == 1 that is the plain stream-K deal. The remaining tiles follow whole,
-// round-robin. `rounds` must divide sk_tiles, so that no tile straddles two rounds.
+// round-robin. `rounds` must divide sk_tiles, so that no tile straddles two rounds. From one
+// round to the next the workers change places (worker w plays position (w + round * rot) mod
+// workers of the round): every round has the same shape, and without the rotation the same few
+// workers would end up completing a tile -- and paying for the exchange of partial sums -- in
+// every round while all others wait for them.
 // All of it is 32-bit arithmetic (the host only enables the split when units < 2^31 and
 // virtual workers < 2^15): a 64-bit division is a subroutine call on the device.
 struct Schedule {
   int num_tiles, workers, worker, num_kb, chunk_kb, cpt, sk_tiles, rounds;
   int round;             // round whose units are being consumed
+  int rot;               // positions the workers move on from one round to the next
+  int pos;               // this worker's position in the current round
   uint32_t vworkers;     // rounds * workers
   uint32_t q, rem;       // units / vworkers and units % vworkers
   int u_begin, u_end;    // this worker's units of the current round, consumed from the end
@@ -274,11 +298,18 @@ struct Schedule {
     const uint32_t units = static_cast<uint32_t>(sk_tiles) * static_cast<uint32_t>(cpt);
     q = units / vworkers;
     rem = units % vworkers;
+    rot = rounds > 1 ? (workers * 3) / 8 + 1 : 0;
+    pos = worker;
     u_begin = unit_begin(worker);
     u_end = unit_begin(worker + 1);
     dp_next = sk_tiles + worker;
   }
-  // First unit of virtual worker v (v = round * workers + worker):
+  // Worker at position `p` of round `r`.
+  __device__ int worker_at(int p, int r) const {
+    int w = (p - r * rot) % workers;
+    return w < 0 ? w + workers : w;
+  }
+  // First unit of virtual worker v (v = round * workers + position in the round):
   // floor(units * v / vworkers) = q * v + floor(rem * v / vworkers), no product above 2^31.
   __device__ int unit_begin(int v) const {
     const uint32_t uv = static_cast<uint32_t>(v);
@@ -287,7 +318,8 @@ struct Schedule {
   __device__ bool next(Segment& s) {
     while (u_end <= u_begin && round + 1 < rounds) {
       ++round;
-      const int v = round * workers + worker;
+      pos = (worker + round * rot) % workers;
+      const int v = round * workers + pos;
       u_begin = unit_begin(v);
       u_end = unit_begin(v + 1);
     }
@@ -300,6 +332,7 @@ struct Schedule {
       s.kb1 = min((u_end - t0) * chunk_kb, num_kb);
       s.final = (u_end - t0 == cpt);
       s.round = round;
+      s.pos = pos;
       u_end = sb;
       return true;
     }
@@ -309,6 +342,7 @@ struct Schedule {
       s.kb1 = num_kb;
       s.final = true;
       s.round = 0;
+      s.pos = worker;
       dp_next += workers;
       return true;
     }
@@ -583,13 +617,17 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
 
       // Flags carry the launch and the round, so a slot's reader never takes one round's
-      // partial sums for another's; zero means "slot free".
+      // partial sums for another's; zero means "slot free". A worker owns two slots and
+      // alternates between them from round to round, so it only ever waits for a reader that
+      // is two rounds behind.
       const uint32_t tag = (epoch << 6) | static_cast<uint32_t>(sg.round);
+      const int parity = sg.round & 1;
+      auto slot_index = [&](int w) { return (static_cast<size_t>(w) * CG + cta_rank) * 2 + parity; };
       if (!sg.final) {
         // Publish this worker's partial sums of the tile, then raise its flag.
-        uint32_t* my_flag = sk_flags + sched.worker * CG + cta_rank;
-        if (sg.round > 0) {
-          // The slot still holds the previous round's partial until its reader hands it back.
+        uint32_t* my_flag = sk_flags + slot_index(sched.worker);
+        if (sg.round > 1) {
+          // The slot still holds the partial of two rounds ago until its reader hands it back.
           bool failed = false;
           if (et == 0) {
             const long long t0 = clock64();
@@ -607,12 +645,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           if (epi_bar_any(failed)) { ok = false; break; }
         }
-        float4* slot = reinterpret_cast<float4*>(
-            sk_ws + (static_cast<size_t>(sched.worker) * CG + cta_rank) * kSlotFloats);
+        float4* slot = reinterpret_cast<float4*>(sk_ws + slot_index(sched.worker) * kSlotFloats);
 #pragma unroll
         for (int j = 0; j < COLS / 4; ++j)
           slot[j * 256 + et] = make_float4(sum[4 * j], sum[4 * j + 1], sum[4 * j + 2], sum[4 * j + 3]);
-        __threadfence();
+        // The barrier orders all 256 threads' stores before thread 0's release store below, whose
+        // gpu scope then covers them for whoever acquires the flag.
         epi_bar_sync();
         // (a launch made for a test of the bounded waits leaves the flag down)
         if (et == 0 && !(flags & kFlagDropPublish)) st_release_gpu(my_flag, tag);
@@ -620,45 +658,52 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       if (sg.kb0 > 0) {
         // Add the partial sums of the workers that computed the earlier parts of this tile:
-        // the virtual workers before this one, all of the same round.
+        // the positions before this one in the same round, down to the one that started the
+        // tile. First every partial is awaited at once (thread i watches the flag of the i-th
+        // position back), then they are added in a fixed order -- the result does not depend on
+        // who arrived first -- and finally all slots are handed back together.
         const int tile_u0 = sg.tile * sched.cpt;
         const int v_round0 = sg.round * sched.workers;
-        for (int p = sched.worker - 1; p >= 0; --p) {
-          // A worker with no units in this round publishes nothing.
-          if (sched.unit_begin(v_round0 + p + 1) == sched.unit_begin(v_round0 + p)) continue;
-          bool failed = false;
-          if (et == 0) {
-            const uint32_t* flag = sk_flags + p * CG + cta_rank;
-            const long long t0 = clock64();
-            uint32_t spins = 0;
-            while (ld_acquire_gpu(flag) != tag) {
-              if ((++spins & 63u) == 0) {
-                if (*reinterpret_cast<volatile uint32_t*>(status) != kDevOk) { failed = true; break; }
-                if (clock64() - t0 > spin_limit) {
-                  atomicCAS(status, kDevOk, kDevTimeoutFixup);
-                  failed = true;
-                  break;
-                }
+        int p_first = sg.pos - 1;
+        while (p_first > 0 && sched.unit_begin(v_round0 + p_first) > tile_u0) --p_first;
+        const int mine = sg.pos - 1 - et;     // the position this thread watches, if any
+        const bool watching = mine >= p_first &&
+                              sched.unit_begin(v_round0 + mine + 1) != sched.unit_begin(v_round0 + mine);
+        bool failed = false;
+        if (watching) {
+          const uint32_t* flag = sk_flags + slot_index(sched.worker_at(mine, sg.round));
+          const long long t0 = clock64();
+          uint32_t spins = 0;
+          while (ld_acquire_gpu(flag) != tag) {
+            if ((++spins & 63u) == 0) {
+              if (*reinterpret_cast<volatile uint32_t*>(status) != kDevOk) { failed = true; break; }
+              if (clock64() - t0 > spin_limit) {
+                atomicCAS(status, kDevOk, kDevTimeoutFixup);
+                failed = true;
+                break;
               }
             }
           }
-          if (epi_bar_any(failed)) { ok = false; break; }
+        }
+        if (epi_bar_any(failed)) { ok = false; break; }
+        for (int p = sg.pos - 1; p >= p_first; --p) {
+          // A position with no units in this round published nothing.
+          if (sched.unit_begin(v_round0 + p + 1) == sched.unit_begin(v_round0 + p)) continue;
           const float4* slot = reinterpret_cast<const float4*>(
-              sk_ws + (static_cast<size_t>(p) * CG + cta_rank) * kSlotFloats);
+              sk_ws + slot_index(sched.worker_at(p, sg.round)) * kSlotFloats);
 #pragma unroll
           for (int j = 0; j < COLS / 4; ++j) {
             const float4 q = __ldcg(slot + j * 256 + et);
             sum[4 * j] += q.x; sum[4 * j + 1] += q.y; sum[4 * j + 2] += q.z; sum[4 * j + 3] += q.w;
           }
-          // Hand the slot back (each partial has exactly one reader): with the flag at zero
-          // again its owner may publish the next round's partial, and a replay of this very
-          // launch -- a captured CUDA graph re-issues the same epoch -- cannot take the old
-          // contents for new ones.
-          epi_bar_sync();
-          if (et == 0) st_release_gpu(sk_flags + p * CG + cta_rank, 0u);
-          if (sched.unit_begin(v_round0 + p) <= tile_u0) break;  // worker p started the tile
         }
-        if (!ok) break;
+        // Hand the slots back (each partial has exactly one reader): with the flag at zero
+        // again its owner may publish into the slot two rounds on, and a replay of this very
+        // launch -- a captured CUDA graph re-issues the same epoch -- cannot take the old
+        // contents for new ones.
+        epi_bar_sync();
+        if (watching)
+          st_release_gpu(sk_flags + slot_index(sched.worker_at(mine, sg.round)), 0u);
       }
       if constexpr (Cfg::STAGING_BYTES > 0) {
         if (tma_store) {

@@ -31,9 +31,9 @@ static cudaError_t launch_variant(const GemmArgs& a, int grid, cudaStream_t stre
 
 // The table's `mode` is the caller-visible one: 1 / 3 for fp32 operands (1xTF32 / 3xTF32),
 // 16 for bf16 and 17 for fp16 operands.
-template <int BN, int MODE, int CG, int LAYOUT = 0, int DT = 0>
+template <int BN, int MODE, int CG, int LAYOUT = 0, int DT = 0, int STAGED = 0>
 static KernelVariant make_variant() {
-  using Cfg = GemmCfg<BN, MODE, CG, LAYOUT, DT>;
+  using Cfg = GemmCfg<BN, MODE, CG, LAYOUT, DT, STAGED>;
   KernelVariant v;
   // In the skinny layout the kernel's 128-row side runs along N of the caller's problem.
   v.block_m = (LAYOUT == 2) ? BN : Cfg::TILE_M;
@@ -47,6 +47,7 @@ static KernelVariant make_variant() {
   v.tmem_cols = Cfg::TMEM_COLS;
   v.threads = Cfg::THREADS;
   v.staging_bytes = Cfg::STAGING_BYTES;
+  v.gave_up_stage = STAGED;
   v.func = reinterpret_cast<const void*>(&gemm_tf32_kernel<Cfg>);
   v.launch = &launch_variant<Cfg>;
   return v;

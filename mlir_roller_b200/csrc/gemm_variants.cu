@@ -25,6 +25,30 @@ static const KernelVariant* table(int* n) {
   return kTable;
 }
 
+// Kernels whose ring fills shared memory, compiled a second time with one stage less and the
+// staging area of the TMA-store output path.
+static const KernelVariant* staged_table(int* n) {
+  static const KernelVariant kTable[] = {
+      make_variant<256, 1, 2, 0, 0, 1>(),
+      make_variant<128, 1, 1, 0, 0, 1>(),
+  };
+  *n = static_cast<int>(sizeof(kTable) / sizeof(kTable[0]));
+  return kTable;
+}
+
+const KernelVariant* find_staged_form(const KernelVariant* kv) {
+  if (!kv || kv->staging_bytes > 0 || kv->gave_up_stage) return nullptr;
+  int n;
+  const KernelVariant* t = (kv->mode == 16 || kv->mode == 17) ? staged_forms_16bit(&n)
+                                                             : staged_table(&n);
+  for (int i = 0; i < n; ++i) {
+    if (t[i].block_m == kv->block_m && t[i].block_n == kv->block_n && t[i].rstep == kv->rstep &&
+        t[i].cta_group == kv->cta_group && t[i].mode == kv->mode && t[i].layout == kv->layout)
+      return &t[i];
+  }
+  return nullptr;
+}
+
 int variant_count() {
   int n;
   table(&n);

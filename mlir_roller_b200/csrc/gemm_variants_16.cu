@@ -37,4 +37,13 @@ const KernelVariant* variants_16bit(int* n) {
   return kTable;
 }
 
+const KernelVariant* staged_forms_16bit(int* n) {
+  static const KernelVariant kTable[] = {
+      make_variant<256, 1, 2, 0, 1, 1>(), make_variant<128, 1, 1, 0, 1, 1>(),
+      make_variant<256, 1, 2, 0, 2, 1>(), make_variant<128, 1, 1, 0, 2, 1>(),
+  };
+  *n = static_cast<int>(sizeof(kTable) / sizeof(kTable[0]));
+  return kTable;
+}
+
 }  // namespace rb200

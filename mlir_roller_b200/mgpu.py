@@ -186,6 +186,70 @@ class ShardedGemm:
         return 2 * self.block.rows * self.block.cols * self.K
 
 
+class HostStagedGemm:
+    """This rank's C block = A_rows @ B with all three matrices in (pinned) host memory, on a node
+    whose ranks all need the same B.
+
+    The reference uploads both operands of every GEMM from the host (src/roller.py:532-534). With
+    one process per GPU, doing the same on every rank would push `world` copies of B through the
+    host's PCIe links. Here a rank uploads its own rows of A and only its 1/world share of B's
+    rows; the shares are exchanged between the GPUs over NVLink (an in-place NCCL all-gather into
+    the rank's B buffer), which is more than ten times faster than the host link, and the kernel
+    follows on the same stream. C is read back into host memory at the end. Everything is
+    enqueued on the given stream; the caller synchronises.
+    """
+
+    def __init__(self, rows: int, N: int, K: int, rank: int, world_size: int, mode: int = 3,
+                 group=None, arch=None, measure: bool = False, tile=None):
+        import torch
+        import torch.distributed as dist
+        from . import _lib, roller
+        from .analyze import MatmulConfig
+        if K % world_size:
+            raise ValueError("B's rows are exchanged in equal shares: K must divide by the world size")
+        self.rows, self.N, self.K = rows, N, K
+        self.rank, self.world_size, self.mode = rank, world_size, mode
+        self.group = group if group is not None else dist.group.WORLD
+        self._torch, self._dist = torch, dist
+        dt = roller.operand_dtype(mode)
+        if tile is None:
+            hint, _fn, _ms = roller.best_hint(MatmulConfig(rows, N, K, _el_bits(mode)), arch,
+                                              mode=mode, measure=measure)
+            tile = roller.kernel_tile_for(hint)
+        self.plan = _lib.GemmPlan(tile, rows, N, K, mode=mode)
+        self.dA = torch.empty(rows, K, dtype=dt, device="cuda")
+        self.dB = torch.empty(K, N, dtype=dt, device="cuda")
+        self.dC = torch.empty(rows, N, dtype=torch.float32, device="cuda")
+        share = K // world_size
+        self.share = (rank * share, (rank + 1) * share)
+
+    def bytes_per_call(self):
+        """(host-to-device, device-to-host) bytes one `run` moves over this rank's host link."""
+        eb = self.dA.element_size()
+        return (eb * (self.rows * self.K + (self.share[1] - self.share[0]) * self.N),
+                4 * self.rows * self.N)
+
+    def run(self, hA, hB, hC, stream=None) -> None:
+        """hA: this rank's rows of A, hB: the whole B, hC: receives this rank's block of C; all
+        contiguous host tensors (pinned, for the copies to be asynchronous)."""
+        torch, dist = self._torch, self._dist
+        cs = stream if stream is not None else torch.cuda.current_stream()
+        r0, r1 = self.share
+        with torch.cuda.stream(cs):
+            self.dA.copy_(hA, non_blocking=True)
+            mine = self.dB[r0:r1]
+            mine.copy_(hB[r0:r1], non_blocking=True)
+            if self.world_size > 1:
+                dist.all_gather_into_tensor(self.dB, mine, group=self.group)   # in place
+            self.plan.run(self.dA, self.dB, self.dC, cs)
+            hC.copy_(self.dC, non_blocking=True)
+
+    def destroy(self) -> None:
+        if self.plan is not None:
+            self.plan.destroy()
+            self.plan = None
+
+
 def split_bands(row0: int, row1: int, bands: int, align: int = 256,
                 taper: bool = False) -> List[Tuple[int, int]]:
     """Cut the rows [row0, row1) of one rank's block into at most `bands` non-empty bands whose

@@ -60,16 +60,42 @@ def test_tma_store_writes_the_same_c(tile, shape):
     M, N, K = shape
     A, B = g.make_inputs(M, N, K, "uniform", seed=M + K)
     for ldc in (N, N + 8):
-        plain = run_plan(A, B, tile, 3, stream_k=0, ldc=ldc)[0]
+        plain = run_plan(A, B, tile, 3, [(_lib.OPT_TMA_STORE, 0)], stream_k=0, ldc=ldc)[0]
         staged = run_plan(A, B, tile, 3, [(_lib.OPT_TMA_STORE, 1)], stream_k=0, ldc=ldc, launches=2)
         assert not np.isnan(staged[0]).any()
         assert np.array_equal(staged[0], plain) and np.array_equal(staged[1], plain)
     assert g.err_norm(plain, g.matmul_fp64(A, B)) <= TIGHT_3X
 
 
+def test_the_shorter_ring_form_of_a_kernel_gives_the_same_bits():
+    """The 1xTF32 and bf16 kernels of the 256 x 256 pair tile fill shared memory with their
+    ring; a second form of each has one stage less and the staging area of the TMA-store path.
+    The library binds that form by itself up to K = 4096 and the deeper ring beyond; both give
+    the same C, as does the deeper ring told to use TMA stores (which switches forms)."""
+    tile = _lib.find_tile(256, 256, 2)
+    for K in (1024, 4352):
+        M, N = 512, 768
+        A, B = g.make_inputs(M, N, K, "uniform", seed=K)
+        dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+        outs = []
+        for option in (None, 0, 1):
+            plan = _lib.GemmPlan(tile, M, N, K, mode=1)
+            plan.set_stream_k(0)
+            if option is not None:
+                plan.set_option(_lib.OPT_TMA_STORE, option)
+            dC = torch.full((M, N), float("nan"), device="cuda")
+            plan.run(dA, dB, dC)
+            torch.cuda.synchronize()
+            plan.check_status()
+            outs.append(dC.cpu().numpy())
+            plan.destroy()
+        assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+        assert g.err_norm(outs[0], g.matmul_fp64(A, B)) <= TOL_1X
+
+
 def test_tma_store_is_refused_where_it_cannot_work():
-    # 1xTF32 on the 256 x 256 pair tile fills shared memory with its ring: no staging area
-    plan = _lib.GemmPlan(_lib.find_tile(256, 256, 2), 512, 512, 512, mode=1)
+    # 3xTF32 on the 256 x 64 pair tile fills shared memory with its ring and has no other form
+    plan = _lib.GemmPlan(_lib.find_tile(256, 64, 2), 512, 512, 512, mode=3)
     with pytest.raises(_lib.RollerError) as e:
         plan.set_option(_lib.OPT_TMA_STORE, 1)
     assert e.value.status == _lib.ERR_UNSUPPORTED
