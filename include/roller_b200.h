@@ -131,7 +131,10 @@ typedef struct roller_ktile {
   int threads_1x;
   int threads_3x;
   int layout;    /* 0 = general tile; 2 = "skinny": for a C with few rows the tensor core works on
-                    C^T, block_m (32 or 64) rows of C by block_n = 128 columns per tile */
+                    C^T, block_m (32 or 64) rows of C by block_n = 128 columns per tile;
+                    3 = "skinny" on the CUDA cores: plain fp32 FMAs, 16 rows of C by 256 columns
+                    per CTA, split along K. It exists for ROLLER_MODE_3XTF32 only (stages_1x =
+                    0): its results are fp32-exact products, which is what that mode promises */
   int rstep_16;  /* reduce step of the tile's kernel for 16-bit operands, in elements (64);
                     0 = the tile has no such kernel */
   int stages_16; /* its pipeline depth and dynamic shared memory */

@@ -20,6 +20,7 @@ FLAG_B_TRANSPOSED = 2
 FLAG_C_16BIT = 4    # 16-bit modes only: C is written in the operand type instead of fp32
 LAYOUT_GENERAL = 0
 LAYOUT_SKINNY = 2
+LAYOUT_CUDA_CORES = 3   # plain fp32 FMAs for a C of at most 16 rows per pass (3xTF32-class only)
 # roller_b200_gemm_set_option
 OPT_WAIT_LIMIT_CYCLES = 1
 OPT_OVERLAP_LAUNCH = 2

@@ -368,6 +368,8 @@ class BlackwellPolicy:
         macs_per_clk = dev.tf32_macs_per_clk_sm * (2 if sixteen else 1)
         td = TileDict([block_m, block_n], cfg, rstep)
         td.cta_group, td.stages, td.mode, td.layout = cta_group, stages, mode, layout
+        if layout == 3:
+            return self._analyse_cuda_core_tile(td, block_m, block_n)
         td.thread_tile = [1, 32]  # what one epilogue thread reads from TMEM at a time
         # the accumulator's columns are the tile's N side, or its M side in the skinny layout
         td.tmem_cols = 2 * (block_m if layout == 2 else block_n)
@@ -427,12 +429,33 @@ class BlackwellPolicy:
                      f"cg{cta_group},{arith}" + (",skinny>" if layout == 2 else ">"))
         return td
 
+    def _analyse_cuda_core_tile(self, td: TileDict, block_m: int, block_n: int) -> TileDict:
+        """The kernel that uses plain fp32 FMAs for a C of few rows (layout 3): a CTA per strip
+        of `block_n` columns and range of K, one pass over B per `block_m` rows of C. Each byte
+        of B feeds 16 FMAs, so a pass runs at whichever is slower, HBM or the FP32 lanes."""
+        cfg, dev = self.matmul_config, self.arch
+        td.thread_tile = [block_m, 4]       # partial sums one lane holds
+        td.tmem_cols = 0
+        td.smem_cost = 4 * block_m * 512    # one 512-k chunk of the A rows
+        td.valid = cfg.el_bits == 32
+        passes = -(-cfg.M // block_m)
+        td.grid_size = passes * (-(-cfg.N // block_n))
+        td.traffic = compute_memory_traffic([block_m, block_n], cfg, dev)
+        td.block_per_SM = 2
+        td.num_wave = -(-td.grid_size // (2 * dev.compute_max_core))
+        hbm_us = 4.0 * passes * cfg.K * cfg.N / (dev.hbm_gbs * 1e3 * dev.cuda_core_hbm_frac)
+        fma_us = (passes * block_m * cfg.K * cfg.N
+                  / (dev.compute_max_core * 128 * dev.sm_clock_mhz * dev.cuda_core_fma_frac))
+        td.est_us = max(hbm_us, fma_us) + 8.0
+        td.kernel = f"skinny_fp32<{block_m}x{block_n},cuda cores>"
+        return td
+
     def emit_config(self, topk: int = 10) -> List[TileDict]:
         sixteen = self.mode in (MODE_BF16, MODE_F16)
         tiles = [self._analyse(bm, bn, cg, s16 if sixteen else (s1 if self.mode == MODE_1XTF32 else s3),
                                layout)
                  for (bm, bn, cg, s1, s3, layout, s16) in self.arch.kernel_tiles
-                 if not sixteen or s16 > 0]
+                 if (s16 > 0 if sixteen else (s1 if self.mode == MODE_1XTF32 else s3) > 0)]
         tiles = [td for td in tiles if td.valid]
         tiles.sort(key=lambda td: (td.est_us, td.traffic * td.grid_size))
         return tiles[:topk]

@@ -69,6 +69,9 @@ B200_KERNEL_TILES: Tuple[Tuple[int, int, int, int, int, int, int], ...] = (
     (128, 64, 1, 8, 4, 0, 8),
     (64, 128, 1, 8, 4, 2, 8),
     (32, 128, 1, 8, 5, 2, 8),
+    # layout 3: the CUDA-core kernel (plain fp32 FMAs) for a C of at most 16 rows per pass;
+    # it has a 3xTF32-class form only (fp32-exact products), hence 0 stages for the others
+    (16, 256, 1, 0, 1, 3, 0),
 )
 
 
@@ -142,6 +145,10 @@ class B200(TileDevice):
     kblock_us: dict = field(default_factory=lambda: dict(B200_KBLOCK_US))
     kblock_us_16: dict = field(default_factory=lambda: dict(B200_KBLOCK_US_16))
     bf16_tflops: float = 1621.6         # measured dense bf16 rate (cuBLAS, 8192^3, burst)
+    # the CUDA-core kernel for a C of few rows: fraction of the HBM copy rate it streams B at,
+    # and fraction of the FP32 lanes' issue rate its FMAs reach (fitted to measurements)
+    cuda_core_hbm_frac: float = 0.75
+    cuda_core_fma_frac: float = 0.42
 
     @classmethod
     def from_device(cls, dev: int = 0) -> "B200":

@@ -14,7 +14,7 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libroller_b200.so"
 
-SOURCES = ["gemm_variants.cu", "gemm_variants_16.cu", "capi.cu", "noalloc.cu", "peer_flags.cu"]
+SOURCES = ["gemm_variants.cu", "gemm_variants_16.cu", "capi.cu", "noalloc.cu", "peer_flags.cu", "skinny_simt.cu"]
 HEADERS = ["ptx_sm100.cuh", "gemm_tf32_sm100.cuh", "gemm_launch.h", "gemm_variant_make.cuh"]
 
 NVCC_FLAGS = [

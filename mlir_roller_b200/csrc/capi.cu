@@ -225,14 +225,30 @@ static int enumerable_variant(int idx) {
   return -1;
 }
 
-int roller_b200_kernel_count(void) {
+// The tensor-core rTiles come first; the CUDA-core kernel for a C of few rows is the last one.
+static int tensor_tile_count() {
   int n = 0;
   while (enumerable_variant(n) >= 0) ++n;
   return n;
 }
 
+int roller_b200_kernel_count(void) { return tensor_tile_count() + 1; }
+
 int roller_b200_kernel_desc(int idx, roller_ktile* out) {
   if (!out || idx < 0) return ROLLER_ERR_INVALID;
+  if (idx == tensor_tile_count()) {
+    const KernelVariant* v = simt_skinny_variant();
+    memset(out, 0, sizeof(*out));
+    out->block_m = v->block_m;
+    out->block_n = v->block_n;
+    out->rstep = v->rstep;
+    out->cta_group = 1;
+    out->stages_3x = v->stages;      // fp32-accurate only: no 1xTF32 and no 16-bit form
+    out->smem_3x = v->smem_bytes;
+    out->threads_3x = v->threads;
+    out->layout = v->layout;
+    return ROLLER_OK;
+  }
   const int vi = enumerable_variant(idx);
   if (vi < 0) return ROLLER_ERR_INVALID;
   const KernelVariant& v1 = variant_at(vi);
@@ -271,8 +287,10 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
     return ROLLER_ERR_INVALID;
   const int elem = elem_bytes_of_mode(mode);
   if ((flags & ROLLER_FLAG_C_16BIT) && elem != 2) return ROLLER_ERR_INVALID;
-  if (tile->layout != 0 && tile->layout != 2) return ROLLER_ERR_INVALID;
+  if (tile->layout != 0 && tile->layout != 2 && tile->layout != 3) return ROLLER_ERR_INVALID;
   if (b_transposed && tile->layout != 0) return ROLLER_ERR_UNSUPPORTED;
+  // the CUDA-core kernel computes in plain fp32: it serves the fp32-accurate mode, C = A @ B
+  if (tile->layout == 3 && (mode != ROLLER_MODE_3XTF32 || flags != 0)) return ROLLER_ERR_UNSUPPORTED;
   const int layout = b_transposed ? 1 : tile->layout;
   // a 16-bit kernel reduces the same 128 bytes of k per step: twice the elements
   const KernelVariant* kv = find_variant(tile->block_m, tile->block_n,
@@ -299,7 +317,9 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
   p->c_elem = (flags & ROLLER_FLAG_C_16BIT) ? 2 : 4;
   p->flags = flags;
   p->layout = layout;
-  if (layout == 2) {
+  if (layout == 3) {
+    skinny_simt_tiles(M, N, &p->tiles_m, &p->tiles_n);
+  } else if (layout == 2) {
     // the kernel works on C^T: its tile rows (128) run along N, its tile columns along M
     p->tiles_m = (N + kv->block_n - 1) / kv->block_n;
     p->tiles_n = (M + kv->block_m - 1) / kv->block_m;
@@ -329,8 +349,9 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
   // only a split along K provides, so 1xTF32 gets chunks too (512 k).
   if (layout == 2 && mode != ROLLER_MODE_3XTF32 && num_kb > 16) p->chunk_kb = 16;
   p->unit_kb = default_unit_kb(p);
-  p->stage_a = (static_cast<long long>(lda) * elem % 16) != 0;
-  p->stage_b = (static_cast<long long>(ldb) * elem % 16) != 0;
+  // (the CUDA-core kernel loads with plain instructions and takes any alignment)
+  p->stage_a = layout != 3 && (static_cast<long long>(lda) * elem % 16) != 0;
+  p->stage_b = layout != 3 && (static_cast<long long>(ldb) * elem % 16) != 0;
 
   // Whether C can leave through TMA stores at all (the base address is checked per launch).
   const bool c_fits_tma = layout != 2 && p->c_elem == 4 && !(flags & ROLLER_FLAG_ACCUMULATE) &&
@@ -342,7 +363,7 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
     const KernelVariant* staged = find_staged_form(kv);
     if (staged && static_cast<int>(prop.sharedMemPerBlockOptin) >= staged->smem_bytes) kv = staged;
   }
-  cudaError_t e = bind_variant(p, kv);
+  cudaError_t e = layout == 3 ? cudaSuccess : bind_variant(p, kv);
   p->tma_store = p->kv->staging_bytes > 0 && c_fits_tma;
   if (e == cudaSuccess) e = cudaMalloc(&p->status, sizeof(uint32_t));
   if (e == cudaSuccess) e = cudaMemset(p->status, 0, sizeof(uint32_t));
@@ -378,6 +399,12 @@ int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, void* C, 
   if (cudaGetDevice(&cur) != cudaSuccess || cur != p->device) return ROLLER_ERR_DEVICE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const KernelVariant* kv = p->kv;
+  if (p->layout == 3) {
+    RB_CUDA(skinny_simt_launch(static_cast<const float*>(A), static_cast<const float*>(B),
+                               static_cast<float*>(C), p->M, p->N, p->K, p->lda, p->ldb, p->ldc,
+                               p->sk_rounds, p->sk_ws, p->sm_count, st));
+    return ROLLER_OK;
+  }
 
   // Operands that break TMA's rules (row stride or base not a multiple of 16 bytes) are staged
   // through a padded copy; the base-alignment case needs a workspace made on demand at create
@@ -574,6 +601,7 @@ int roller_b200_gemm_schedule_info(const roller_plan* p, int* sk_tiles, int* rou
 
 int roller_b200_gemm_set_chunk(roller_plan* p, int k_elems) {
   if (!p || k_elems < 0) return ROLLER_ERR_INVALID;
+  if (p->layout == 3) return ROLLER_OK;   // fp32 FMAs: there is no accumulator to drain
   const int num_kb = (p->K + p->kv->rstep - 1) / p->kv->rstep;
   int kb = (k_elems == 0) ? num_kb : (k_elems + p->kv->rstep - 1) / p->kv->rstep;
   if (kb < 1) kb = 1;
@@ -585,6 +613,7 @@ int roller_b200_gemm_set_chunk(roller_plan* p, int k_elems) {
 
 int roller_b200_gemm_set_grid(roller_plan* p, int ctas) {
   if (!p || ctas <= 0 || ctas % p->kv->cta_group != 0) return ROLLER_ERR_INVALID;
+  if (p->layout == 3) return ROLLER_ERR_UNSUPPORTED;
   const long long tiles = static_cast<long long>(p->tiles_m) * p->tiles_n;
   if (ctas / p->kv->cta_group > p->max_workers) return ROLLER_ERR_INVALID;
   if (ctas / p->kv->cta_group > tiles * ((p->K + p->kv->rstep - 1) / p->kv->rstep))
@@ -596,6 +625,7 @@ int roller_b200_gemm_set_grid(roller_plan* p, int ctas) {
 
 int roller_b200_gemm_set_stream_k(roller_plan* p, int mode) {
   if (!p || mode < -1 || mode > 1) return ROLLER_ERR_INVALID;
+  if (p->layout == 3) return ROLLER_OK;   // its split along K is fixed and always reproducible
   p->sk_mode = mode;
   return plan_configure(p);
 }
@@ -626,6 +656,7 @@ int roller_b200_gemm_set_option(roller_plan* p, int option, long long value) {
       p->overlap_launch = value != 0;
       return ROLLER_OK;
     case ROLLER_OPT_TMA_STORE:
+      if (value != 0 && p->layout == 3) return ROLLER_ERR_UNSUPPORTED;
       if (value != 0) {
         if (p->layout == 2 || p->c_elem != 4 || (p->flags & ROLLER_FLAG_ACCUMULATE))
           return ROLLER_ERR_UNSUPPORTED;
@@ -645,7 +676,8 @@ int roller_b200_gemm_set_option(roller_plan* p, int option, long long value) {
       return ROLLER_OK;
     case ROLLER_OPT_PROGRESSIVE_ROUNDS:
       if (value < -1 || value > 64) return ROLLER_ERR_INVALID;
-      if (value != 0 && (p->flags & ROLLER_FLAG_ACCUMULATE)) return ROLLER_ERR_UNSUPPORTED;
+      if (value != 0 && ((p->flags & ROLLER_FLAG_ACCUMULATE) || p->layout == 3))
+        return ROLLER_ERR_UNSUPPORTED;
       p->progressive = static_cast<int>(value);
       return plan_configure(p);
     case ROLLER_OPT_TEST_DROP_PUBLISH:
@@ -743,6 +775,22 @@ static int default_unit_kb(const roller_plan* p) {
 
 static int plan_configure(roller_plan* p) {
   const KernelVariant* kv = p->kv;
+  if (p->layout == 3) {
+    // CUDA-core kernel: strips x K-splits x row groups of CTAs; the partial results of the
+    // splits go through a workspace and are added by a second kernel
+    const int splits = skinny_simt_splits(p->M, p->N, p->K, p->sm_count);
+    p->sk_tiles = 0;
+    p->sk_rounds = splits;
+    p->grid = p->tiles_m * p->tiles_n * splits;
+    const size_t need = skinny_simt_workspace_floats(p->M, p->N, splits);
+    if (need && !p->sk_ws) {
+      if (cudaMalloc(&p->sk_ws, need * sizeof(float)) != cudaSuccess) {
+        cudaGetLastError();
+        return ROLLER_ERR_NOMEM;
+      }
+    }
+    return ROLLER_OK;
+  }
   const long long tiles = static_cast<long long>(p->tiles_m) * p->tiles_n;
   const int num_kb = (p->K + kv->rstep - 1) / kv->rstep;
   const int cpt = (num_kb + p->unit_kb - 1) / p->unit_kb;

@@ -47,7 +47,8 @@ struct KernelVariant {
   int rstep;      // k per stage
   int cta_group;  // 1 or 2
   int mode;       // 1 / 3 (fp32 operands: 1xTF32 / 3xTF32), 16 (bf16), 17 (fp16)
-  int layout;     // 0 = A[M,K], B[K,N]; 1 = B given as Bt[N,K]; 2 = skinny (roles swapped)
+  int layout;     // 0 = A[M,K], B[K,N]; 1 = B given as Bt[N,K]; 2 = skinny (roles swapped);
+                  // 3 = skinny on the CUDA cores (fp32 FMAs)
   int stages;
   int smem_bytes;
   int tmem_cols;
@@ -70,5 +71,14 @@ const KernelVariant* find_variant(int block_m, int block_n, int rstep, int cta_g
 const KernelVariant* find_staged_form(const KernelVariant* kv);
 // The kernels with a shorter ring for 16-bit operands, kept beside the 16-bit table.
 const KernelVariant* staged_forms_16bit(int* n);
+
+// The CUDA-core kernel for a C of at most 16 rows per pass (layout 3, fp32 FMAs; mode 3 only).
+const KernelVariant* simt_skinny_variant();
+int skinny_simt_tiles(int M, int N, int* row_groups, int* strips);
+int skinny_simt_splits(int M, int N, int K, int sm_count);
+size_t skinny_simt_workspace_floats(int M, int N, int splits);
+cudaError_t skinny_simt_launch(const float* A, const float* B, float* C, int M, int N, int K,
+                               long long lda, long long ldb, long long ldc, int splits,
+                               float* workspace, int sm_count, cudaStream_t stream);
 
 }  // namespace rb200

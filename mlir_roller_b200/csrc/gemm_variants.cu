@@ -62,6 +62,11 @@ const KernelVariant& variant_at(int idx) {
 
 const KernelVariant* find_variant(int block_m, int block_n, int rstep, int cta_group, int mode,
                                   int layout) {
+  if (layout == 3) {
+    const KernelVariant* v = simt_skinny_variant();
+    return (v->block_m == block_m && v->block_n == block_n && v->rstep == rstep &&
+            v->cta_group == cta_group && v->mode == mode) ? v : nullptr;
+  }
   int n;
   const KernelVariant* t = (mode == 16 || mode == 17) ? variants_16bit(&n) : table(&n);
   for (int i = 0; i < n; ++i) {

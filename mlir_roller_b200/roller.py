@@ -344,6 +344,8 @@ def calibrate(arch: Optional[B200] = None, modes=(MODE_1XTF32, MODE_3XTF32, MODE
     arch = B200.from_device(torch.cuda.current_device()) if arch is None else arch
     sms = arch.compute_max_core
     for (bm, bn, cg, _s1, _s3, layout, s16) in arch.kernel_tiles:
+        if layout == _lib.LAYOUT_CUDA_CORES:
+            continue        # no k-block pipeline to time: its cost model is bandwidth and FMA rate
         key = (bm, bn, cg) if layout == 0 else (bm, bn, cg, layout)
         M, N = (128 * sms, 512) if layout == 0 else (bm, 128 * sms)
         tile = _lib.find_tile(bm, bn, cg, layout)

@@ -19,6 +19,11 @@ def check_hint(h, M, N, K, mode):
     assert (h.block_tile[0], h.block_tile[1], h.cta_group) in (TILES_16 if sixteen else TILES)
     assert h.rstep == (64 if sixteen else 32) and h.mode == mode
     assert h.matmul_config.el_bits == (16 if sixteen else 32)
+    if h.layout == 3:
+        # the CUDA-core kernel for a C of few rows: fp32-accurate class only, no tensor memory
+        assert mode == MODE_3XTF32 and (h.block_tile, h.cta_group, h.tmem_cols) == ([16, 256], 1, 0)
+        assert h.grid_size == -(-M // 16) * -(-N // 256) and h.est_us > 0 and h.valid
+        return
     skinny = h.layout == 2
     assert skinny == ((h.block_tile[0], h.block_tile[1]) in SKINNY)
     assert h.tmem_cols == 2 * h.block_tile[0 if skinny else 1] <= dev.tmem_columns
@@ -101,7 +106,8 @@ def test_tile_table_matches_the_library():
                  for k in _lib.kernel_tiles()]
     assert sorted(lib_tiles) == sorted(arch.B200_KERNEL_TILES)
     for k in _lib.kernel_tiles():
-        assert k.rstep == 32 and k.tmem_cols == 2 * (k.block_m if k.layout == 2 else k.block_n)
+        want_tmem = 0 if k.layout == 3 else 2 * (k.block_m if k.layout == 2 else k.block_n)
+        assert k.rstep == 32 and k.tmem_cols == want_tmem
         assert max(k.smem_1x, k.smem_3x, k.smem_16) <= 227 * 1024
         assert k.rstep_16 in (0, 64) and (k.rstep_16 == 0) == (k.stages_16 == 0)
         assert isinstance(k, ctypes.Structure)

@@ -34,7 +34,7 @@ def test_every_declaration_cites_the_reference():
 def test_host_only_calls():
     lib = _lib.load()
     n = lib.roller_b200_kernel_count()
-    assert n == 8
+    assert n == 9
     kt = _lib.KTile()
     assert lib.roller_b200_kernel_desc(0, ctypes.byref(kt)) == _lib.OK
     assert lib.roller_b200_kernel_desc(n, ctypes.byref(kt)) == _lib.ERR_INVALID

@@ -427,3 +427,74 @@ def test_launches_can_be_replayed_from_a_cuda_graph(mode):
         plan.check_status()
         assert torch.equal(dC, eager * scale)
     plan.destroy()
+
+
+# ---------------------------------------------------------------- CUDA-core kernel, C of few rows
+CUDA_CORE_TILE = (16, 256, 1, 3)
+
+
+@pytest.mark.parametrize("shape", [(16, 512, 512), (1, 64, 64), (5, 7, 3), (16, 130, 1000),
+                                   (17, 300, 600), (40, 257, 1025), (16, 2048, 4100),
+                                   (3, 1000, 513), (16, 8192, 8192)])
+def test_cuda_core_kernel_for_few_rows_against_oracle(shape):
+    """The plain-fp32 kernel for a C of at most 16 rows per pass (more rows take more passes):
+    tails in all three dimensions, K ranges split across CTAs and added in a fixed order."""
+    M, N, K = shape
+    A, B = g.make_inputs(M, N, K, "normal", seed=M * 7 + N)
+    C64 = g.sample_rows_fp64(A, B, list(range(M)))
+    info = {}
+    C = gpu_gemm(A, B, CUDA_CORE_TILE, 3, info=info)
+    assert C.shape == (M, N) and not np.isnan(C).any()
+    assert g.err_norm(C, C64) <= 2e-6, shape          # fp32 FMAs: better than the 3xTF32 band
+    assert info["tiles_m"] == -(-M // 16) and info["tiles_n"] == -(-N // 256)
+    # bit-reproducible, and the same bits with a C that has pad columns
+    assert np.array_equal(C, gpu_gemm(A, B, CUDA_CORE_TILE, 3, ldc=N + 5))
+
+
+def test_cuda_core_kernel_takes_any_alignment():
+    """No TMA, so no 16-byte rule: odd leading dimensions and an operand that starts in the
+    middle of a 16-byte line go straight in (scalar loads), without a staging copy."""
+    M, N, K = 16, 333, 777
+    A, B = g.make_inputs(M, N, K, "uniform", seed=3)
+    C64 = g.matmul_fp64(A, B)
+    C = gpu_gemm(A, B, CUDA_CORE_TILE, 3, lda=K + 3, ldb=N + 1, ldc=N + 2)
+    assert g.err_norm(C, C64) <= 2e-6
+    dA = torch.from_numpy(A).cuda()
+    big = torch.zeros(K * N + 1, device="cuda")
+    dB = big[1:].view(K, N)                      # base address 4 bytes past a 16-byte boundary
+    dB.copy_(torch.from_numpy(B))
+    dC = torch.full((M, N), float("nan"), device="cuda")
+    plan = _lib.GemmPlan(_lib.find_tile(*CUDA_CORE_TILE), M, N, K, mode=3)
+    plan.run_ptr(dA.data_ptr(), dB.data_ptr(), dC.data_ptr())
+    torch.cuda.synchronize()
+    plan.check_status()
+    plan.destroy()
+    assert g.err_norm(dC.cpu().numpy(), C64) <= 2e-6
+
+
+def test_cuda_core_kernel_exists_for_the_fp32_accurate_mode_only():
+    tile = _lib.find_tile(*CUDA_CORE_TILE)
+    for kwargs in (dict(mode=1), dict(mode=16), dict(mode=3, flags=_lib.FLAG_ACCUMULATE)):
+        with pytest.raises(_lib.RollerError) as e:
+            _lib.GemmPlan(tile, 16, 256, 256, **kwargs)
+        assert e.value.status == _lib.ERR_UNSUPPORTED
+    plan = _lib.GemmPlan(tile, 16, 256, 256, mode=3)
+    for opt in (_lib.OPT_TMA_STORE, _lib.OPT_PROGRESSIVE_ROUNDS):
+        with pytest.raises(_lib.RollerError):
+            plan.set_option(opt, 1)
+    plan.set_stream_k(0)          # accepted: its split along K is always reproducible
+    plan.destroy()
+
+
+def test_search_ranks_the_cuda_core_kernel_where_it_wins():
+    """It is ranked first for a skinny problem whose operands would need staging copies on the
+    tensor-core path, second (within a tenth) for the aligned skinny configuration, never for
+    1xTF32 (it has no such form) and never for a C with many rows."""
+    from mlir_roller_b200 import B200, MatmulConfig, get_roller_hints
+    top = get_roller_hints(MatmulConfig(16, 2049, 8193, 32), B200(), topk=1, mode=3)[0]
+    assert (top.block_tile, top.layout) == ([16, 256], 3)
+    hints = get_roller_hints(MatmulConfig(16, 8192, 8192, 32), B200(), topk=3, mode=3)
+    assert [h.layout for h in hints[:2]] == [2, 3] and hints[1].est_us < 1.2 * hints[0].est_us
+    assert all(h.layout != 3 for h in
+               get_roller_hints(MatmulConfig(16, 8192, 8192, 32), B200(), topk=10, mode=1))
+    assert get_roller_hints(MatmulConfig(2048, 2048, 2048, 32), B200(), topk=1, mode=3)[0].layout == 0
