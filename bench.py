@@ -51,6 +51,16 @@ UNIT = "TFLOP/s"
 WORKLOAD = "README sweep M0-M13 fp32 GEMMs, uniform[-1,1) seeded inputs, one rTile-selected kernel per shape"
 
 
+_T0 = time.perf_counter()
+
+
+def progress(msg: str) -> None:
+    """One line on stderr (rank 0 only) with the seconds since start: where a slow run spends
+    its time. stdout stays reserved for the JSON line."""
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(f"[bench {time.perf_counter() - _T0:7.1f}s] {msg}", file=sys.stderr, flush=True)
+
+
 def sweep_flops(shapes=README_SHAPES) -> float:
     return float(sum(2 * m * n * k for m, n, k in shapes))
 
@@ -539,7 +549,7 @@ class _Checker:
         return float(d) / self.scale
 
 
-def strong_scaling(torch, dist, rank, world, steps, warmup):
+def strong_scaling(torch, dist, rank, world, steps, warmup, budget_s=240.0):
     """The sharded configurations. Per job and mode: the local kernels alone ("kernels"), followed
     by an NCCL gather of C to rank 0 ("gather"), with the exchange of C running underneath the
     computation through the copy engines to rank 0 ("banded_root") and to every rank
@@ -547,7 +557,9 @@ def strong_scaling(torch, dist, rank, world, steps, warmup):
     tiles straight into rank 0's C, progressive schedule, closed by flags). After timing, each
     path runs once more into a NaN-filled C and the delivered matrix is compared with fp64 on
     sampled rows. Returns a list of compact records (identical on all ranks); times are the max
-    over ranks, errors the max over the ranks that hold a result."""
+    over ranks, errors the max over the ranks that hold a result. Jobs that would start after
+    `budget_s` seconds of this function are recorded as skipped (rank 0 decides for all), so the
+    whole bench keeps to its few minutes whatever a box does."""
     from mlir_roller_b200 import mgpu
     from mlir_roller_b200.analyze import MODE_1XTF32, MODE_3XTF32
     jobs = [("M13_rows", (8192, 4096, 4096), (world, 1), 13, (MODE_3XTF32, MODE_1XTF32))]
@@ -579,12 +591,27 @@ def strong_scaling(torch, dist, rank, world, steps, warmup):
         return float(t.item())
 
     out = []
+    t_start = time.perf_counter()
+
+    def out_of_time():
+        t = torch.tensor([1.0 if time.perf_counter() - t_start > budget_s else 0.0], device="cuda")
+        dist.broadcast(t, src=0)
+        return bool(t.item())
+
     for name, (M, N, K), grid, seed, modes in jobs:
         gm, gn = grid
+        if out_of_time():
+            out.append({"job": name, "skipped": f"time budget of {budget_s:.0f} s used up"})
+            continue
         g = torch.Generator(device="cuda")
         g.manual_seed(seed)
         B_full = torch.rand(K, N, device="cuda", generator=g) * 2 - 1     # replicated
         for mode in modes:
+            if out_of_time():
+                out.append({"job": name, "mode": f"{mode}xTF32",
+                            "skipped": f"time budget of {budget_s:.0f} s used up"})
+                continue
+            progress(f"strong: {name} mode {mode} on {gm}x{gn}")
             sg = mgpu.ShardedGemm(M, N, K, rank, world, grid=grid, mode=mode, measure=True)
             b = sg.block
             A_rows = _block_rows_operand(torch, b.rows, K, seed, rank // gn)
@@ -628,6 +655,7 @@ def strong_scaling(torch, dist, rank, world, steps, warmup):
                 except Exception as e:  # noqa: BLE001 - keep the other paths' numbers
                     rec[label + "_error"] = f"{type(e).__name__}: {e}"[:200]
                     continue
+                progress(f"strong: {name} mode {mode}: {label}")
                 rec[label + "_ms"] = timed(lambda: (og.run(A_rows, B_full), og.finish()))
                 og.C.fill_(float("nan"))
                 torch.cuda.synchronize()
@@ -650,6 +678,7 @@ def strong_scaling(torch, dist, rank, world, steps, warmup):
                 torch.cuda.empty_cache()
             del checker
             # the same GEMM, unsharded, on this rank's GPU alone (the strong-scaling numerator)
+            progress(f"strong: {name} mode {mode}: single GPU")
             A_full = torch.rand(M, K, device="cuda", generator=g) * 2 - 1
             C_one = torch.empty(M, N, device="cuda")
             one = mgpu.ShardedGemm(M, N, K, 0, 1, grid=(1, 1), mode=mode, measure=True)
@@ -751,11 +780,14 @@ def run_gpu_arm(args) -> None:
         sampler.start()
 
     measure = args.select == "measure"
+    parts = set(args.parts.split(","))
+    progress(f"start, world {world}")
     cases = [ShapeCase(torch, i, s, MODE_3XTF32, arch, measure) for i, s in enumerate(README_SHAPES)]
     errs = [c.error(torch) for c in cases]
     for c in cases:
         c.plan.check_status()
 
+    progress("kernels selected, timing the sweep")
     sampler.mark_begin()
     step_ms = timed_sweep(torch, cases, args.steps, args.warmup, dist)
     sampler.mark_end()
@@ -773,6 +805,7 @@ def run_gpu_arm(args) -> None:
     loop_reps = max(args.steps, 10)
     per_shape_ms = per_shape_ms1 = errs1 = tiles1 = None
     step_ms16 = None
+    progress("sweep timed; per-shape loops, 1xTF32 and bf16 on rank 0")
     if rank == 0:
         per_shape_ms = [c.loop_ms(loop_reps) for c in cases]
         for c in cases:
@@ -809,6 +842,7 @@ def run_gpu_arm(args) -> None:
         del cases16, lib16, out16
         torch.cuda.empty_cache()
 
+    progress("end-to-end sweep from host memory")
     e2e_ms, h2d, d2h, _ = e2e_sweep(torch, cases, max(args.steps // 2, 1), dist, rank, world)
     if dist is not None:
         t = torch.tensor([e2e_ms], device="cuda")
@@ -822,8 +856,11 @@ def run_gpu_arm(args) -> None:
     torch.cuda.empty_cache()
 
     strong = None
-    if dist is not None:
-        strong = strong_scaling(torch, dist, rank, world, max(args.steps // 2, 3), 2)
+    if dist is not None and "strong" in parts:
+        progress("sharded jobs")
+        strong = strong_scaling(torch, dist, rank, world, max(args.steps // 2, 3), 2,
+                                budget_s=args.strong_budget_s)
+    progress("measurements done on all ranks")
 
     if rank != 0:
         if dist is not None:
@@ -874,8 +911,8 @@ def run_gpu_arm(args) -> None:
         "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
         "frac": achieved / peak,
         # DRAM bytes per launch: an ncu capture of this kernel at 4096 x 4096 x 2048 read+wrote
-        # 1.13 x its algorithmic bytes 4(MK+KN+MN); scaled to the sweep's mean launch.
-        "traffic": 1.13 * sum(4.0 * (m * k + k * n + m * n) for m, n, k in README_SHAPES)
+        # 1.18 x its algorithmic bytes 4(MK+KN+MN); scaled to the sweep's mean launch.
+        "traffic": 1.18 * sum(4.0 * (m * k + k * n + m * n) for m, n, k in README_SHAPES)
         / len(README_SHAPES),
         "traffic_unit": "bytes per launch (mean over the 14 shapes), scaled from an ncu capture",
         "peak_regime": "burst" if burst_regime else "sustained",
@@ -972,6 +1009,10 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--select", default="measure", choices=["measure", "model"],
                     help="rTile per shape: time the top hints (default) or trust the cost model")
+    ap.add_argument("--parts", default="all,strong",
+                    help="comma list; leave out 'strong' to skip the sharded jobs at N > 1")
+    ap.add_argument("--strong-budget-s", type=float, default=240.0,
+                    help="seconds after which no further sharded job is started")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":

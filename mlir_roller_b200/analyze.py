@@ -437,8 +437,9 @@ class BlackwellPolicy:
         td.thread_tile = [block_m, 4]       # partial sums one lane holds
         td.tmem_cols = 0
         td.smem_cost = 4 * block_m * 512    # one 512-k chunk of the A rows
-        td.valid = cfg.el_bits == 32
         passes = -(-cfg.M // block_m)
+        # one pass over B per 16 rows of C: only ranked for a C of few rows
+        td.valid = cfg.el_bits == 32 and passes <= 4
         td.grid_size = passes * (-(-cfg.N // block_n))
         td.traffic = compute_memory_traffic([block_m, block_n], cfg, dev)
         td.block_per_SM = 2

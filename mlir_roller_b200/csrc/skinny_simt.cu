@@ -6,10 +6,12 @@
 // columns wide run far below the tensor rate: 82 us. Plain fp32 FMAs need no split at all, and
 // they are exactly the arithmetic of the reference's generated kernel (an fp32 FMA chain per
 // output, src/roller.py:280-282). This kernel is that alternative as one more rTile for the
-// search to rank. Measured on B200: 86 us for 16 x 8192 x 8192 (the FP32 lanes reach half their
-// issue rate: every FMA needs an A value through a shared-memory broadcast read, and the
-// shared-memory pipe, not the FMA pipe, is what fills up), so the tensor-core skinny tile stays
-// ahead there by 5 %; it wins where that tile pays for staging copies -- it loads with plain
+// search to rank. Measured on B200: 86 us for 16 x 8192 x 8192. The profiler shows it bound by
+// instruction issue: 80 % of the schedulers' cycles issue, the FMA pipe is busy 53 % (loads from
+// the ring, broadcast reads of A, copy bookkeeping and addressing take the rest; Blackwell's
+// packed fma.rn.f32x2 was tried to halve the FMA instructions and ran slower, 103 us). So the
+// tensor-core skinny tile stays ahead there by 5 %; this one wins where that tile pays for
+// staging copies -- it loads with plain
 // instructions and takes any alignment (16 x 2049 x 8193: 33 us against 63 us) -- and at
 // 16 x 16384 x 16384 (285 against 296 us).
 //

@@ -488,13 +488,14 @@ def test_cuda_core_kernel_exists_for_the_fp32_accurate_mode_only():
 
 def test_search_ranks_the_cuda_core_kernel_where_it_wins():
     """It is ranked first for a skinny problem whose operands would need staging copies on the
-    tensor-core path, second (within a tenth) for the aligned skinny configuration, never for
+    tensor-core path, close behind the tensor-core skinny tiles for the aligned skinny configuration, never for
     1xTF32 (it has no such form) and never for a C with many rows."""
     from mlir_roller_b200 import B200, MatmulConfig, get_roller_hints
     top = get_roller_hints(MatmulConfig(16, 2049, 8193, 32), B200(), topk=1, mode=3)[0]
     assert (top.block_tile, top.layout) == ([16, 256], 3)
     hints = get_roller_hints(MatmulConfig(16, 8192, 8192, 32), B200(), topk=3, mode=3)
-    assert [h.layout for h in hints[:2]] == [2, 3] and hints[1].est_us < 1.2 * hints[0].est_us
+    assert hints[0].layout == 2
+    assert any(h.layout == 3 and h.est_us < 1.2 * hints[0].est_us for h in hints)
     assert all(h.layout != 3 for h in
                get_roller_hints(MatmulConfig(16, 8192, 8192, 32), B200(), topk=10, mode=1))
     assert get_roller_hints(MatmulConfig(2048, 2048, 2048, 32), B200(), topk=1, mode=3)[0].layout == 0
