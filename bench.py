@@ -549,7 +549,7 @@ class _Checker:
         return float(d) / self.scale
 
 
-def strong_scaling(torch, dist, rank, world, steps, warmup, budget_s=240.0):
+def strong_scaling(torch, dist, rank, world, steps, warmup, budget_s=240.0, all_jobs=False):
     """The sharded configurations. Per job and mode: the local kernels alone ("kernels"), followed
     by an NCCL gather of C to rank 0 ("gather"), with the exchange of C running underneath the
     computation through the copy engines to rank 0 ("banded_root") and to every rank
@@ -566,6 +566,11 @@ def strong_scaling(torch, dist, rank, world, steps, warmup, budget_s=240.0):
     if world == 8:
         jobs.append(("16384_rows", (16384, 16384, 16384), (8, 1), 0, (MODE_3XTF32,)))
         jobs.append(("16384_4x2", (16384, 16384, 16384), (4, 2), 0, (MODE_3XTF32, MODE_1XTF32)))
+    elif all_jobs and world % 2 == 0:
+        # the 8-GPU jobs' code paths on fewer GPUs (a check of the plumbing, not a figure)
+        jobs.append(("16384_rows", (16384, 16384, 16384), (world, 1), 0, (MODE_3XTF32,)))
+        jobs.append((f"16384_{world // 2}x2", (16384, 16384, 16384), (world // 2, 2), 0,
+                     (MODE_3XTF32, MODE_1XTF32)))
 
     def timed(fn):
         for _ in range(warmup):
@@ -641,7 +646,7 @@ def strong_scaling(torch, dist, rank, world, steps, warmup, budget_s=240.0):
             sg.plan.check_status()
 
             paths = [("banded_root", ob, False), ("banded_all", None, True), ("fused_root", None, False)]
-            if M * N // world <= 1024 * 4096:
+            if M * N // world <= 1024 * 4096 or (all_jobs and name.startswith("M13")):
                 # a block of less than one wave of tiles: also with more rounds than the
                 # library would pick (earlier output, dearer exchange of partial tiles)
                 paths.append(("fused_root_r4", None, False))
@@ -859,7 +864,7 @@ def run_gpu_arm(args) -> None:
     if dist is not None and "strong" in parts:
         progress("sharded jobs")
         strong = strong_scaling(torch, dist, rank, world, max(args.steps // 2, 3), 2,
-                                budget_s=args.strong_budget_s)
+                                budget_s=args.strong_budget_s, all_jobs="alljobs" in parts)
     progress("measurements done on all ranks")
 
     if rank != 0:
@@ -1010,7 +1015,8 @@ def main() -> None:
     ap.add_argument("--select", default="measure", choices=["measure", "model"],
                     help="rTile per shape: time the top hints (default) or trust the cost model")
     ap.add_argument("--parts", default="all,strong",
-                    help="comma list; leave out 'strong' to skip the sharded jobs at N > 1")
+                    help="comma list; leave out 'strong' to skip the sharded jobs at N > 1; "
+                         "'alljobs' also runs the 8-GPU jobs' code paths on fewer GPUs")
     ap.add_argument("--strong-budget-s", type=float, default=240.0,
                     help="seconds after which no further sharded job is started")
     args = ap.parse_args()

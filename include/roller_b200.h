@@ -91,6 +91,11 @@ typedef enum roller_status {
                                           early on rather than together at the end (rounded down
                                           to a divisor of the tile count; at most 64). -1 = the
                                           library picks n; 0 = off */
+#define ROLLER_OPT_COOPERATIVE_FIXUP 6  /* 1 (default): in the progressive schedule with TMA stores a
+                                          tile shared by several workers is completed by all of
+                                          them together, each adding a slice of everybody's
+                                          partial sums; 0: by the worker holding the end of its
+                                          reduction alone, as the plain stream-K schedule does */
 #define ROLLER_OPT_TEST_DROP_PUBLISH 5 /* test aid, 1: workers that hand a partial tile to another
                                           worker write it but never raise its flag, so the bounded
                                           wait of the receiving worker runs out and the launch ends

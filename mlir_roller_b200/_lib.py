@@ -27,6 +27,7 @@ OPT_OVERLAP_LAUNCH = 2
 OPT_TMA_STORE = 3
 OPT_PROGRESSIVE_ROUNDS = 4
 OPT_TEST_DROP_PUBLISH = 5
+OPT_COOPERATIVE_FIXUP = 6
 MAX_FLAG_TARGETS = 32
 # device status words (what a bounded wait that ran out records)
 DEV_TIMEOUT_FIXUP = 7

@@ -17,6 +17,8 @@ constexpr int kFlagAccumulate = 1;  // C += A@B instead of C = A@B
 constexpr int kFlagVecStore = 2;    // C rows are 16-byte aligned: use 128-bit stores
 constexpr int kFlagC16 = 4;         // 16-bit kernels only: C holds elements of the operand type
 constexpr int kFlagTmaStore = 8;    // C leaves through shared memory and TMA stores (GemmArgs::tmC)
+constexpr int kFlagCoopFixup = 32;  // shared tiles are completed by all their workers together (needs
+                                    // kFlagTmaStore; four scratch slots and reader counts per CTA)
 constexpr int kFlagDropPublish = 16;  // test aid: partial tiles are written but never flagged, so
                                       // the worker completing the tile sees its bounded wait run out
 
@@ -36,8 +38,9 @@ struct GemmArgs {
   bool serialize_programmatically;  // launch may overlap the tail of the stream's previous kernel
   int sk_tiles;         // tiles dealt out in k-chunks (stream-K); 0 = whole tiles only
   int sk_rounds;        // groups the stream-K tiles are worked through one after the other (>= 1)
-  float* sk_ws;         // two 128 x block_n slots per CTA for partial tiles
-  uint32_t* sk_flags;   // one flag per slot, set to a tag of `epoch` and the round when valid
+  float* sk_ws;         // four 128 x block_n slots per CTA for partial tiles
+  uint32_t* sk_flags;   // one flag per slot (a tag of `epoch` and the round when valid), followed
+                        // at 4 * grid words by one reader count per slot
   uint32_t epoch;       // distinguishes this launch's flags from earlier launches' (1 .. 2^26-1)
 };
 

@@ -577,7 +577,128 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t acc_ph = 0;
     bool ok = true;
     float sum[COLS];
+
+    // ---- cooperative completion of shared tiles (kFlagCoopFixup; needs the staging area).
+    // Every worker holding part of a tile publishes its partial sums, and the tile is then
+    // completed by all of them together: each takes some of the 32-column boxes, adds that
+    // slice of everybody's partial in a fixed order and hands it to the TMA unit. The cost per
+    // worker no longer grows with the number of workers sharing a tile, and nobody waits for
+    // one worker that adds everything alone. A worker publishes up to two partials per round
+    // (the head of one tile, the tail of another), notes them here, and completes its slices
+    // when it moves on to the next round, while its MMAs already run ahead.
+    const bool coop = Cfg::STAGING_BYTES > 0 && (flags & kFlagCoopFixup) != 0 && tma_store;
+    constexpr int NB = COLS / 32 > 0 ? COLS / 32 : 1;   // boxes per warp and tile
+    int pend_tile0 = 0, pend_tile1 = 0, pend_pos0 = 0, pend_pos1 = 0;   // (scalars: no local array)
+    int npend = 0, pend_round = 0;
+    uint32_t* const sk_reads = sk_flags + 4 * gridDim.x;   // one reader count per slot
+    // slot of worker w's partial of a round: two per round (see `which_of`), two rounds alive
+    auto coop_slot = [&](int w, int round, int which) {
+      return (static_cast<size_t>(w) * CG + cta_rank) * 4 + static_cast<size_t>((round & 1) * 2 + which);
+    };
+    // which of a position's two partials of a round belongs to tile t: the one holding the
+    // position's last unit is published first (0), the other one (1) second
+    auto which_of = [&](int v_round0, int p, int t) {
+      return ((sched.unit_begin(v_round0 + p + 1) - 1) / sched.cpt == t) ? 0 : 1;
+    };
+    auto flush_pending = [&]() -> bool {
+      for (int e = 0; e < npend; ++e) {
+        const int T = e ? pend_tile1 : pend_tile0, pos = e ? pend_pos1 : pend_pos0, round = pend_round;
+        const uint32_t tag = (epoch << 6) | static_cast<uint32_t>(round);
+        const int v0 = round * sched.workers;
+        const int u0 = T * sched.cpt, u1 = u0 + sched.cpt;
+        int p_first = pos, p_last = pos;
+        while (p_first > 0 && sched.unit_begin(v0 + p_first) > u0) --p_first;
+        while (p_last < sched.workers - 1 && sched.unit_begin(v0 + p_last + 1) < u1) ++p_last;
+        int P = 0, my_idx = 0;
+        for (int p = p_first; p <= p_last; ++p) {
+          if (sched.unit_begin(v0 + p + 1) == sched.unit_begin(v0 + p)) continue;   // no units
+          if (p < pos) ++my_idx;
+          ++P;
+        }
+        const int R = P < NB ? P : NB;          // workers that complete a share of the tile
+        if (my_idx >= R) continue;              // (uniform over the CTA) not one of them
+        // wait for every partial of the tile: thread i watches position p_first + i
+        const int mine = p_first + et;
+        const bool watching = mine <= p_last &&
+                              sched.unit_begin(v0 + mine + 1) != sched.unit_begin(v0 + mine);
+        uint32_t* my_watch = nullptr;
+        bool failed = false;
+        if (watching) {
+          my_watch = sk_flags + coop_slot(sched.worker_at(mine, round), round, which_of(v0, mine, T));
+          const long long t0 = clock64();
+          uint32_t spins = 0;
+          while (ld_acquire_gpu(my_watch) != tag) {
+            if ((++spins & 63u) == 0) {
+              if (*reinterpret_cast<volatile uint32_t*>(status) != kDevOk) { failed = true; break; }
+              if (clock64() - t0 > spin_limit) {
+                atomicCAS(status, kDevOk, kDevTimeoutFixup);
+                failed = true;
+                break;
+              }
+            }
+          }
+        }
+        if (epi_bar_any(failed)) return false;
+        int mb, nb;
+        tile_coords(T, tiles_m, tiles_n, mb, nb);
+        const int row0 = (mb * CG + static_cast<int>(cta_rank)) * Cfg::BM + quarter * 32;
+        const uint32_t box = staging + static_cast<uint32_t>(warp - Cfg::FIRST_EPI_WARP) * 4096u;
+        for (int c = my_idx; c < NB; c += R) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.0f;
+          for (int p = p_first; p <= p_last; ++p) {
+            if (sched.unit_begin(v0 + p + 1) == sched.unit_begin(v0 + p)) continue;
+            const float4* slot = reinterpret_cast<const float4*>(
+                sk_ws + coop_slot(sched.worker_at(p, round), round, which_of(v0, p, T)) * kSlotFloats);
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+              const float4 q = __ldcg(slot + (8 * c + jj) * 256 + et);
+              v[4 * jj] += q.x; v[4 * jj + 1] += q.y; v[4 * jj + 2] += q.z; v[4 * jj + 3] += q.w;
+            }
+          }
+          const int col0 = nb * BN + half * COLS + c * 32;
+          if (row0 < M && col0 < N) {
+            if (lane == 0) bulk_wait_read_all();   // the box's previous contents have left
+            __syncwarp();
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+              const uint32_t at = box + static_cast<uint32_t>(lane) * 128u +
+                                  (static_cast<uint32_t>(jj ^ (lane & 7)) << 4);
+              asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(at), "f"(v[4 * jj]),
+                           "f"(v[4 * jj + 1]), "f"(v[4 * jj + 2]), "f"(v[4 * jj + 3])
+                           : "memory");
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmC, box, col0, row0);
+              bulk_commit_group();
+            }
+          }
+        }
+        // Every thread has read what it needs. Count this reader on each partial's slot; the
+        // last of the R readers hands the slot back to its owner.
+        epi_bar_sync();
+        if (watching) {
+          uint32_t* reads = sk_reads + (my_watch - sk_flags);
+          if (atomicAdd(reads, 1u) == static_cast<uint32_t>(R - 1)) {
+            *reinterpret_cast<volatile uint32_t*>(reads) = 0u;
+            __threadfence();
+            st_release_gpu(my_watch, 0u);
+          }
+        }
+      }
+      npend = 0;
+      return true;
+    };
+
     while (ok && sched.next(sg)) {
+      if constexpr (Cfg::STAGING_BYTES > 0) {
+        if (coop && npend > 0 && sg.round != pend_round) {
+          if (!flush_pending()) { ok = false; break; }
+        }
+      }
       int mb, nb;
       tile_coords(sg.tile, tiles_m, tiles_n, mb, nb);
       const int row = (mb * CG + static_cast<int>(cta_rank)) * Cfg::BM + quarter * 32 + lane;
@@ -616,6 +737,45 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         break;
       }
 
+      if constexpr (Cfg::STAGING_BYTES > 0) {
+        if (coop && !(sg.kb0 == 0 && sg.final)) {
+          // part of a shared tile: publish it and note it; it is completed in flush_pending
+          const int v0 = sg.round * sched.workers;
+          const size_t slot_i = coop_slot(sched.worker, sg.round, which_of(v0, sg.pos, sg.tile));
+          uint32_t* my_flag = sk_flags + slot_i;
+          if (sg.round > 1) {
+            // the slot still holds the partial of two rounds ago until its readers are done
+            bool failed = false;
+            if (et == 0) {
+              const long long t0 = clock64();
+              uint32_t spins = 0;
+              while (ld_acquire_gpu(my_flag) != 0u) {
+                if ((++spins & 63u) == 0) {
+                  if (*reinterpret_cast<volatile uint32_t*>(status) != kDevOk) { failed = true; break; }
+                  if (clock64() - t0 > spin_limit) {
+                    atomicCAS(status, kDevOk, kDevTimeoutSlot);
+                    failed = true;
+                    break;
+                  }
+                }
+              }
+            }
+            if (epi_bar_any(failed)) { ok = false; break; }
+          }
+          float4* slot = reinterpret_cast<float4*>(sk_ws + slot_i * kSlotFloats);
+#pragma unroll
+          for (int j = 0; j < COLS / 4; ++j)
+            slot[j * 256 + et] = make_float4(sum[4 * j], sum[4 * j + 1], sum[4 * j + 2], sum[4 * j + 3]);
+          epi_bar_sync();
+          if (et == 0 && !(flags & kFlagDropPublish))
+            st_release_gpu(my_flag, (epoch << 6) | static_cast<uint32_t>(sg.round));
+          if (npend == 0) { pend_tile0 = sg.tile; pend_pos0 = sg.pos; }
+          else { pend_tile1 = sg.tile; pend_pos1 = sg.pos; }
+          pend_round = sg.round;
+          ++npend;
+          continue;
+        }
+      }
       // Flags carry the launch and the round, so a slot's reader never takes one round's
       // partial sums for another's; zero means "slot free". A worker owns two slots and
       // alternates between them from round to round, so it only ever waits for a reader that
@@ -837,6 +997,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
     if constexpr (Cfg::STAGING_BYTES > 0) {
+      if (coop && ok && npend > 0) flush_pending();
       // Stores handed to the TMA unit must have been performed before the CTA may go.
       if (tma_store && lane == 0) bulk_wait_all();
     }

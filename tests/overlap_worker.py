@@ -1,6 +1,7 @@
 """Worker for test_overlap_gpu.py: one process per GPU (launched through torch.distributed.run),
-checks mgpu.OverlappedGemm -- bands pushed into the destination ranks' C over symmetric memory
--- against an fp64 product. Exits non-zero on any mismatch."""
+checks mgpu.OverlappedGemm -- bands pushed into the destination ranks' C over symmetric memory,
+or tiles stored there by the kernel itself -- and mgpu.HostStagedGemm against an fp64 product.
+Exits non-zero on any mismatch."""
 import os
 import sys
 
@@ -74,6 +75,24 @@ def main() -> int:
     bad += 0 if err <= TOL_3X else 1
     og.destroy()
     del og
+    dist.barrier()
+    # operands in host memory: each rank uploads its rows of A and a 1/world share of B's rows,
+    # the shares are exchanged over NVLink, C comes back to the host
+    rows = M // world
+    hs = mgpu.HostStagedGemm(rows, N, K, rank, world)
+    hA = A[rank * rows:(rank + 1) * rows].cpu().pin_memory()
+    hB = B.cpu().pin_memory()
+    hC = torch.full((rows, N), float("nan")).pin_memory()
+    for _ in range(2):
+        hs.run(hA, hB, hC)
+        torch.cuda.synchronize()
+    hs.plan.check_status()
+    err = float((hC.double() - ref[rank * rows:(rank + 1) * rows].cpu()).abs().max()) / scale
+    up, down = hs.bytes_per_call()
+    ok = err <= TOL_3X and up == 4 * (rows * K + (K // world) * N) and down == 4 * rows * N
+    print(f"rank {rank} host-staged: err {err:.2e} h2d {up} d2h {down} {'ok' if ok else 'FAIL'}", flush=True)
+    bad += 0 if ok else 1
+    hs.destroy()
     dist.barrier()
     t = torch.tensor([bad], device="cuda")
     dist.all_reduce(t)

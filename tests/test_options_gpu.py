@@ -127,17 +127,20 @@ def test_progressive_schedule_matches_the_oracle(tile, mode, rounds):
     A, B = g.make_inputs(M, N, K, "uniform", seed=11)
     C64 = g.matmul_fp64(A, B)
     tol = TIGHT_3X if mode == 3 else TOL_1X
-    for staged in ((0, 1) if mode == 3 else (0,)):
+    # without the TMA-store path, with it and the tile completed by one worker, and with it
+    # and the tile completed by all its workers together (the default)
+    for staged, coop in (((0, 0), (1, 0), (1, 1)) if mode == 3 else ((0, 0),)):
         info = {}
         outs = run_plan(A, B, tile, mode, [(_lib.OPT_PROGRESSIVE_ROUNDS, rounds),
-                                           (_lib.OPT_TMA_STORE, staged)], launches=3, info=info)
+                                           (_lib.OPT_TMA_STORE, staged),
+                                           (_lib.OPT_COOPERATIVE_FIXUP, coop)], launches=3, info=info)
         tiles = info["tiles_m"] * info["tiles_n"]
         assert info["sk_tiles"] == tiles and tiles % info["rounds"] == 0
         if rounds > 0:
             assert info["rounds"] == rounds
         for out in outs:
             assert not np.isnan(out).any()
-            assert g.err_norm(out, C64) <= tol, (tile, mode, rounds, staged)
+            assert g.err_norm(out, C64) <= tol, (tile, mode, rounds, staged, coop)
         assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[1], outs[2])
 
 
@@ -230,6 +233,36 @@ def test_a_bounded_wait_that_runs_out_ends_the_kernel_with_an_error_code():
     fresh.check_status()
     assert g.err_norm(dC.cpu().numpy(), C64) <= TIGHT_3X
     fresh.destroy()
+
+
+def test_a_wait_runs_out_in_the_cooperative_completion_of_a_tile():
+    """The progressive schedule with tiles completed by all their workers: with the flags
+    withheld every worker waits in vain for the others' partial sums, gives up after the limit,
+    and the launch ends with the same error code; afterwards the plan works."""
+    M, N, K = 1024, 2048, 2048
+    A, B = g.make_inputs(M, N, K, "uniform", seed=10)
+    dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    dC = torch.empty(M, N, device="cuda")
+    plan = _lib.GemmPlan(_lib.find_tile(256, 256, 2), M, N, K, mode=3)
+    plan.set_option(_lib.OPT_TMA_STORE, 1)
+    plan.set_option(_lib.OPT_PROGRESSIVE_ROUNDS, 4)
+    assert plan.schedule_info()["rounds"] == 4
+    plan.set_option(_lib.OPT_WAIT_LIMIT_CYCLES, 2_000_000)
+    plan.set_option(_lib.OPT_TEST_DROP_PUBLISH, 1)
+    plan.run(dA, dB, dC)
+    torch.cuda.synchronize()
+    # (whichever role's wait ran out first has recorded its code: the workers waiting for the
+    # partial sums, or the producer and MMA issuer stalled behind them)
+    assert plan.device_status() != 0
+    plan.set_option(_lib.OPT_TEST_DROP_PUBLISH, 0)
+    plan.set_option(_lib.OPT_WAIT_LIMIT_CYCLES, 0)
+    for _ in range(2):
+        dC.fill_(float("nan"))
+        plan.run(dA, dB, dC)
+        torch.cuda.synchronize()
+        plan.check_status()
+        assert g.err_norm(dC.cpu().numpy(), g.matmul_fp64(A, B)) <= TIGHT_3X
+    plan.destroy()
 
 
 def test_a_cta_pair_winds_down_together_when_a_wait_runs_out():
