@@ -441,6 +441,9 @@ def e2e_sweep(torch, cases, steps, dist=None, rank=0, world=1):
     each byte of B once per node instead of once per rank."""
     from mlir_roller_b200 import mgpu, roller
     host, staged = [], []
+    if world > 1:
+        # host buffers in the memory of the NUMA node this rank's GPU hangs off
+        mgpu.run_near_gpu(torch.cuda.current_device())
     for c in cases:
         hA = c.A.cpu().pin_memory()
         hB = c.B.cpu().pin_memory()

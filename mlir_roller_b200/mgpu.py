@@ -186,6 +186,46 @@ class ShardedGemm:
         return 2 * self.block.rows * self.block.cols * self.K
 
 
+def run_near_gpu(device_index: int) -> Optional[int]:
+    """Restrict this process to the CPU cores of the NUMA node its GPU hangs off, so that host
+    buffers it allocates (and pins) afterwards are placed in that node's memory by first touch
+    and its copies do not cross the socket interconnect. With one process per GPU and all of
+    them uploading at once that is where the host side saturates first. Returns the node, or
+    None when the topology cannot be read (nothing is changed then)."""
+    import os
+    try:
+        import torch
+        props = torch.cuda.get_device_properties(device_index)
+        bus = props.pci_bus_id
+        if isinstance(bus, str):                  # "00000000:1B:00.0"
+            bdf = bus.lower()
+        else:                                     # numbers: domain, bus, device
+            bdf = f"{props.pci_domain_id:04x}:{bus:02x}:{props.pci_device_id:02x}.0"
+    except Exception:  # noqa: BLE001 - no GPU, or a torch without these properties
+        bdf = None
+    try:
+        if bdf is None:
+            return None
+        if len(bdf.split(":")[0]) == 8:          # 00000000:1b:00.0 -> 0000:1b:00.0
+            bdf = bdf[4:]
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0) & cpus
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except (OSError, ValueError, AttributeError):
+        return None
+
+
 class HostStagedGemm:
     """This rank's C block = A_rows @ B with all three matrices in (pinned) host memory, on a node
     whose ranks all need the same B.

@@ -188,3 +188,46 @@ def test_band_schedule_delivers_every_block(M, N, K, world, bands, dest, two_d):
     holders = range(world) if dest == "all" else [0]
     for r in holders:
         assert np.array_equal(Cs[r].reshape(M, N), truth)
+
+
+def test_run_near_gpu_changes_nothing_when_the_topology_cannot_be_read(monkeypatch):
+    """Without a GPU (or without the sysfs entries) the helper reports None and leaves the
+    process's CPU affinity alone; with a readable topology it narrows the affinity to the
+    GPU's NUMA node."""
+    import builtins
+    import io
+    import os
+    import types
+
+    import torch
+
+    before = os.sched_getaffinity(0)
+    assert mgpu.run_near_gpu(0) is None or not torch.cuda.is_available()
+    assert os.sched_getaffinity(0) == before
+    # a fake machine: GPU 0 at 0000:1b:00.0 on node 1, whose cores are the ones we may use
+    cpus = sorted(before)
+    keep = cpus[: max(1, len(cpus) // 2)]
+    files = {"/sys/bus/pci/devices/0000:1b:00.0/numa_node": "1\n",
+             "/sys/devices/system/node/node1/cpulist": ",".join(str(c) for c in keep) + "\n"}
+    real_open = builtins.open
+
+    def fake_open(path, *a, **k):
+        if path in files:
+            return io.StringIO(files[path])
+        return real_open(path, *a, **k)
+
+    monkeypatch.setattr(builtins, "open", fake_open)
+    monkeypatch.setattr(torch.cuda, "get_device_properties",
+                        lambda i: types.SimpleNamespace(pci_bus_id="00000000:1B:00.0"))
+    try:
+        assert mgpu.run_near_gpu(0) == 1
+        assert os.sched_getaffinity(0) == set(keep)
+        os.sched_setaffinity(0, before)
+        # the same device described by numbers, as torch reports it
+        monkeypatch.setattr(torch.cuda, "get_device_properties",
+                            lambda i: types.SimpleNamespace(pci_bus_id=0x1B, pci_device_id=0,
+                                                            pci_domain_id=0))
+        assert mgpu.run_near_gpu(0) == 1
+        assert os.sched_getaffinity(0) == set(keep)
+    finally:
+        os.sched_setaffinity(0, before)
