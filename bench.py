@@ -441,8 +441,10 @@ def e2e_sweep(torch, cases, steps, dist=None, rank=0, world=1):
     each byte of B once per node instead of once per rank."""
     from mlir_roller_b200 import mgpu, roller
     host, staged = [], []
+    affinity = os.sched_getaffinity(0)
     if world > 1:
-        # host buffers in the memory of the NUMA node this rank's GPU hangs off
+        # host buffers in the memory of the NUMA node this rank's GPU hangs off (first touch
+        # while the process is restricted to that node's cores; restored below)
         mgpu.run_near_gpu(torch.cuda.current_device())
     for c in cases:
         hA = c.A.cpu().pin_memory()
@@ -453,6 +455,7 @@ def e2e_sweep(torch, cases, steps, dist=None, rank=0, world=1):
             m, n, k = c.shape
             staged.append(mgpu.HostStagedGemm(m, n, k, rank, world, mode=c.mode,
                                               tile=roller.kernel_tile_for(c.hint)))
+    os.sched_setaffinity(0, affinity)
     # Shapes are spread over three streams so that one GEMM's upload, another's kernel and a
     # third's readback overlap (the two PCIe directions are independent); a shape always uses
     # the same stream, so its device buffers are never touched by two launches at once.

@@ -314,6 +314,10 @@ def best_hint(config: MatmulConfig, arch=None, topk: int = 20, mode: Optional[in
         try:
             fn = Compiler(config, hint, mode=mode).compile()
             ms = fn.time(dA, dB, dC, warmup=2, iters=5)   # raises when a launch gave up
+            if ms < 2.0:
+                # short kernels: the first candidate is timed while the clocks still ramp up,
+                # so take the better of two passes (costs a few milliseconds)
+                ms = min(ms, fn.time(dA, dB, dC, warmup=1, iters=5))
         except _lib.RollerError:
             continue
         if best is None or ms < best[2]:
