@@ -239,6 +239,22 @@ int roller_b200_gemm_set_option(roller_plan* plan, int option, long long value);
  * reference, which runs on one device (.env:5-6). */
 int roller_b200_flag_signal_async(uint32_t* const* targets, int n, uint32_t value, void* stream);
 
+/* roller_b200_gemm_run with the hand-shake of a multi-GPU step carried out by the kernel itself,
+ * for a C that is another GPU's memory: no store into C leaves before the word at `go_flag`
+ * (this GPU's memory; the other GPU raises it when it is done with the previous contents of C)
+ * has reached `go_value`, and once all stores of the launch have been performed `arrive_value`
+ * is stored (system-scope release) into `arrive_flag` (normally the other GPU's memory). Either
+ * pointer may be null. The wait for "go" sits in front of the first store, so the first tiles
+ * are computed meanwhile; it is bounded like every device-side wait (ROLLER_OPT_WAIT_LIMIT_CYCLES):
+ * when it runs out the launch is reported by roller_b200_last_status and raises no flag.
+ * ROLLER_ERR_UNSUPPORTED unless the plan writes C through the TMA-store output path
+ * (ROLLER_OPT_TMA_STORE); the caller then brackets roller_b200_gemm_run with
+ * roller_b200_flag_wait_async / roller_b200_flag_signal_async. There is no counterpart in the
+ * reference, which runs on one device (.env:5-6). */
+int roller_b200_gemm_run_synced(roller_plan* plan, const void* A, const void* B, void* C,
+                                const uint32_t* go_flag, uint32_t go_value, uint32_t* arrive_flag,
+                                uint32_t arrive_value, void* stream);
+
 /* Enqueues a one-block kernel that waits until each of the first `n` (<= 64) words of `flags`
  * selected by `mask` (bit i = word i) has reached `value` (flags count steps; the comparison
  * survives wrap-around). The wait is bounded: after `limit_cycles` clock cycles (0 = about two

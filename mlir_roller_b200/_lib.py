@@ -98,6 +98,9 @@ SIGNATURES = {
     "roller_b200_gemm_set_grid": (C.c_int, [C.c_void_p, C.c_int]),
     "roller_b200_gemm_set_stream_k": (C.c_int, [C.c_void_p, C.c_int]),
     "roller_b200_gemm_set_option": (C.c_int, [C.c_void_p, C.c_int, C.c_longlong]),
+    "roller_b200_gemm_run_synced": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                              C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32,
+                                              C.c_void_p]),
     "roller_b200_flag_signal_async": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_uint32,
                                                 C.c_void_p]),
     "roller_b200_flag_wait_async": (C.c_int, [C.c_void_p, C.c_int, C.c_ulonglong, C.c_uint32,
@@ -242,6 +245,17 @@ class GemmPlan:
     def run_ptr(self, a_ptr: int, b_ptr: int, c_ptr: int, stream=None) -> None:
         check(self._lib.roller_b200_gemm_run(self._h, a_ptr, b_ptr, c_ptr, _stream_ptr(stream)),
               "roller_b200_gemm_run")
+
+    def run_synced_ptr(self, a_ptr: int, b_ptr: int, c_ptr: int, *, go_ptr: int = 0,
+                       go_value: int = 0, arrive_ptr: int = 0, arrive_value: int = 0,
+                       stream=None) -> None:
+        """`run_ptr` whose kernel itself waits for the word at `go_ptr` to reach `go_value`
+        before its first store into C and stores `arrive_value` at `arrive_ptr` after its last
+        (RollerError(ERR_UNSUPPORTED) when the plan does not use the TMA-store output path)."""
+        check(self._lib.roller_b200_gemm_run_synced(
+            self._h, a_ptr, b_ptr, c_ptr, go_ptr or None, go_value & 0xFFFFFFFF,
+            arrive_ptr or None, arrive_value & 0xFFFFFFFF, _stream_ptr(stream)),
+            "roller_b200_gemm_run_synced")
 
     def _check_dtypes(self, A, B, Cout) -> None:
         """A and B must hold the element type the plan's mode names, C fp32 -- or that type too

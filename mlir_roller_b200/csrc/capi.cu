@@ -176,7 +176,8 @@ struct roller_plan {
   void* ws_a;             // padded copies (device), owned
   void* ws_b;
   long long ws_lda, ws_ldb;
-  uint32_t* status;  // device status word, owned
+  uint32_t* status;  // device status word, followed by the arrival counter of synced launches; owned
+  rb200::PeerSync peer;  // set for the duration of one roller_b200_gemm_run_synced call
   // cached tensor maps for the last (A, B) pointers seen
   const void* map_a_ptr;
   const void* map_b_ptr;
@@ -367,8 +368,8 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
   }
   cudaError_t e = layout == 3 ? cudaSuccess : bind_variant(p, kv);
   p->tma_store = p->kv->staging_bytes > 0 && c_fits_tma;
-  if (e == cudaSuccess) e = cudaMalloc(&p->status, sizeof(uint32_t));
-  if (e == cudaSuccess) e = cudaMemset(p->status, 0, sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMalloc(&p->status, 2 * sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMemset(p->status, 0, 2 * sizeof(uint32_t));
   if (e == cudaSuccess && p->stage_a) {
     p->ws_lda = round_up_ld(K, elem);
     e = cudaMalloc(&p->ws_a, static_cast<size_t>(elem) * p->ws_lda * M);
@@ -420,6 +421,8 @@ int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, void* C, 
   const bool c_aligned = (reinterpret_cast<uintptr_t>(C) & 15) == 0;
   if (p->tma_store && p->tma_forced && !c_aligned) return ROLLER_ERR_INVALID;
   const bool tma_store = p->tma_store && c_aligned;
+  const bool peer_sync = p->peer.go_flag || p->peer.arrive_flag;
+  if (peer_sync && !tma_store) return ROLLER_ERR_UNSUPPORTED;
   if (p->stage_a) {
     pad_rows(A, p->lda, p->ws_a, p->ws_lda, p->M, p->K, p->elem, p->sm_count * 8, st);
     a_src = p->ws_a;
@@ -498,6 +501,11 @@ int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, void* C, 
       static_cast<long long>(p->grid / kv->cta_group) * p->sk_rounds >= 3ll * p->sk_tiles)
     args.flags |= kFlagCoopFixup;
   if (p->drop_publish) args.flags |= kFlagDropPublish;
+  args.peer = p->peer;
+  if (peer_sync) {
+    args.flags |= kFlagPeerSync;
+    args.peer.arrive_count = p->status + 1;
+  }
   args.status = p->status;
   args.spin_limit = p->spin_limit;
   args.serialize_programmatically = p->overlap_launch;
@@ -509,6 +517,23 @@ int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, void* C, 
   args.epoch = p->epoch;
   RB_CUDA(kv->launch(args, p->grid, st));
   return ROLLER_OK;
+}
+
+int roller_b200_gemm_run_synced(roller_plan* p, const void* A, const void* B, void* C,
+                                const uint32_t* go_flag, uint32_t go_value, uint32_t* arrive_flag,
+                                uint32_t arrive_value, void* stream) {
+  if (!p) return ROLLER_ERR_INVALID;
+  if ((reinterpret_cast<uintptr_t>(go_flag) & 3) || (reinterpret_cast<uintptr_t>(arrive_flag) & 3))
+    return ROLLER_ERR_INVALID;
+  // the kernel's own hand-shake exists on the TMA-store output path only
+  if (p->layout == 3 || !p->tma_store) return ROLLER_ERR_UNSUPPORTED;
+  p->peer.go_flag = go_flag;
+  p->peer.go_value = go_value;
+  p->peer.arrive_flag = arrive_flag;
+  p->peer.arrive_value = arrive_value;
+  const int rc = roller_b200_gemm_run(p, A, B, C, stream);
+  p->peer = rb200::PeerSync{};
+  return rc;
 }
 
 int roller_b200_gemm_time(roller_plan* p, const void* A, const void* B, void* C, void* stream,
@@ -648,7 +673,7 @@ int roller_b200_last_status(roller_plan* p, uint32_t* device_status) {
   if (h != 0) {
     // Read and clear: the failed launch has been reported, later launches start clean. The
     // stream-K flags of a launch that gave up may be left raised, so they are reset as well.
-    RB_CUDA(cudaMemset(p->status, 0, sizeof(uint32_t)));
+    RB_CUDA(cudaMemset(p->status, 0, 2 * sizeof(uint32_t)));   // (with the arrival counter)
     if (p->sk_flags) RB_CUDA(cudaMemset(p->sk_flags, 0, sizeof(uint32_t) * p->sk_slots * 2));
   }
   return h == 0 ? ROLLER_OK : ROLLER_ERR_TIMEOUT;

@@ -19,8 +19,24 @@ constexpr int kFlagC16 = 4;         // 16-bit kernels only: C holds elements of 
 constexpr int kFlagTmaStore = 8;    // C leaves through shared memory and TMA stores (GemmArgs::tmC)
 constexpr int kFlagCoopFixup = 32;  // shared tiles are completed by all their workers together (needs
                                     // kFlagTmaStore; four scratch slots and reader counts per CTA)
+constexpr int kFlagPeerSync = 64;   // the launch waits for and raises another GPU's flags itself
+                                    // (GemmArgs::peer; needs kFlagTmaStore)
 constexpr int kFlagDropPublish = 16;  // test aid: partial tiles are written but never flagged, so
                                       // the worker completing the tile sees its bounded wait run out
+
+// Hand-shake of one launch with another GPU of the node, carried out by the kernel itself (with
+// kFlagPeerSync, TMA-store output path only). `go_flag` (this GPU's memory) must have reached
+// `go_value` before the first store into C leaves; once every store of the launch has been
+// performed, `arrive_value` is stored -- release, system scope -- into `arrive_flag` (normally
+// the other GPU's memory). Either pointer may be null. `arrive_count` is a word of this GPU
+// that counts the warps done with their stores; the last one raises the flag and leaves zero.
+struct PeerSync {
+  const uint32_t* go_flag;
+  uint32_t* arrive_flag;
+  uint32_t* arrive_count;
+  uint32_t go_value;
+  uint32_t arrive_value;
+};
 
 struct GemmArgs {
   CUtensorMap tmA;
@@ -42,6 +58,7 @@ struct GemmArgs {
   uint32_t* sk_flags;   // one flag per slot (a tag of `epoch` and the round when valid), followed
                         // at 4 * grid words by one reader count per slot
   uint32_t epoch;       // distinguishes this launch's flags from earlier launches' (1 .. 2^26-1)
+  PeerSync peer;        // all zero unless kFlagPeerSync is set
 };
 
 struct KernelVariant {

@@ -350,6 +350,17 @@ struct Schedule {
   }
 };
 
+// System scope: the other party is another GPU of the node (or its copy engine).
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -384,7 +395,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                  const __grid_constant__ CUtensorMap tmC, float* __restrict__ C, int M, int N, int K,
                  long long ldc, int tiles_m, int tiles_n, int chunk_kb, int acc_kb, int flags,
                  uint32_t* status, long long spin_limit, int sk_tiles, int sk_rounds, float* sk_ws,
-                 uint32_t* sk_flags, uint32_t epoch) {
+                 uint32_t* sk_flags, uint32_t epoch, const PeerSync peer) {
   // chunk_kb: the unit of the stream-K schedule (a tile's reduction is dealt out in pieces of
   // that many k-blocks); acc_kb: how many k-blocks accumulate in TMEM before the accumulate
   // warps drain them into registers. 3xTF32 uses the same value for both; the modes whose
@@ -590,6 +601,23 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     constexpr int NB = COLS / 32 > 0 ? COLS / 32 : 1;   // boxes per warp and tile
     int pend_tile0 = 0, pend_tile1 = 0, pend_pos0 = 0, pend_pos1 = 0;   // (scalars: no local array)
     int npend = 0, pend_round = 0;
+    // ---- hand-shake with another GPU (kFlagPeerSync): C is that GPU's memory, which it may
+    // still be reading for the previous step. Nothing is stored before its "go" has arrived;
+    // the wait sits in front of a warp's first store, so it costs nothing while the first
+    // tiles are being computed. A wait that runs out records kDevTimeoutPeer and lets the
+    // stores go ahead: the launch is reported as failed and its C is not to be used.
+    bool go_pending = Cfg::STAGING_BYTES > 0 && (flags & kFlagPeerSync) != 0 && peer.go_flag != nullptr;
+    auto await_go = [&]() {     // (lane 0 of the warp, which issues its stores)
+      const long long t0 = clock64();
+      uint32_t spins = 0;
+      while (static_cast<int32_t>(ld_acquire_sys(peer.go_flag) - peer.go_value) < 0) {
+        if ((++spins & 15u) == 0 && clock64() - t0 > spin_limit) {
+          atomicCAS(status, kDevOk, kDevTimeoutPeer);
+          break;
+        }
+      }
+      go_pending = false;
+    };
     uint32_t* const sk_reads = sk_flags + 4 * gridDim.x;   // one reader count per slot
     // slot of worker w's partial of a round: two per round (see `which_of`), two rounds alive
     auto coop_slot = [&](int w, int round, int which) {
@@ -672,6 +700,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
+              if (go_pending) await_go();
               tma_store_2d(&tmC, box, col0, row0);
               bulk_commit_group();
             }
@@ -892,6 +921,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               fence_proxy_async_smem();
               __syncwarp();
               if (lane == 0) {
+                if (go_pending) await_go();
                 tma_store_2d(&tmC, box, col0, row0);
                 bulk_commit_group();
               }
@@ -999,7 +1029,23 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if constexpr (Cfg::STAGING_BYTES > 0) {
       if (coop && ok && npend > 0) flush_pending();
       // Stores handed to the TMA unit must have been performed before the CTA may go.
-      if (tma_store && lane == 0) bulk_wait_all();
+      if (tma_store && lane == 0) {
+        bulk_wait_all();
+        if ((flags & kFlagPeerSync) != 0 && peer.arrive_flag != nullptr && ok &&
+            *reinterpret_cast<volatile uint32_t*>(status) == kDevOk) {
+          // This warp's stores have been performed. Count it; the last warp of the launch tells
+          // the other GPU (the fences order every warp's stores, which the counter's chain of
+          // atomics has made visible to this one, before the flag). A launch that gave up
+          // somewhere raises nothing, so the other side's bounded wait reports it too.
+          fence_proxy_async_all();
+          __threadfence_system();
+          const uint32_t total = gridDim.x * static_cast<uint32_t>(Cfg::EPI_WARPS);
+          if (atomicInc(peer.arrive_count, total - 1u) == total - 1u) {
+            __threadfence_system();
+            st_release_sys(peer.arrive_flag, peer.arrive_value);
+          }
+        }
+      }
     }
   } else {
     // ------------------------------------------------------------ split warps

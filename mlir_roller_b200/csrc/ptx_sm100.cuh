@@ -147,6 +147,12 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// Orders this thread's view of what the async proxy (the TMA unit) wrote, in any state space,
+// with its generic-proxy accesses that follow.
+__device__ __forceinline__ void fence_proxy_async_all() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+
 __device__ __forceinline__ void tcgen05_fence_before_sync() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }

@@ -397,10 +397,14 @@ class OverlappedGemm:
     time, so finished tiles leave at a steady rate from the first microseconds on and the
     transfer runs underneath the rest of the computation instead of after it). The step is
     closed by flags: each rank stores a step counter into its word of the root's flag array
-    once its kernel has completed, the root waits (bounded) for all of them, then releases the
-    others into the next step by storing the counter into their "go" word, so that nobody
-    overwrites a C that the root may still be reading. An rTile whose kernel lacks the staging
-    area keeps the kernel's own stores.
+    once its stores have been performed, the root waits (bounded) for all of them, then releases
+    the others into the next step by storing the counter into their "go" word, so that nobody
+    overwrites a C that the root may still be reading. The kernel does both halves of a rank's
+    hand-shake itself (`GemmPlan.run_synced_ptr`): it waits for "go" only in front of its first
+    store, i.e. while the first tiles are being computed, and its last warp to finish raises
+    the arrival flag, so no launch boundary lies between the last store and the flag. An rTile
+    whose kernel lacks the staging area keeps the kernel's own stores and is bracketed by the
+    two flag kernels instead.
     C must not be read while another rank may still be pushing the next step into it: separate
     consecutive steps by whatever makes the readers finish first (the bench only times).
 
@@ -468,6 +472,7 @@ class OverlappedGemm:
         self.steps = band_schedule(self.block, N, K, bands, self.dests, taper=taper)
         self.bands = [(st.row0, st.row1) for st in self.steps]
         self.plans, self.tiles, self._events = [], [], []
+        self._synced = self._signalled = False
         by_shape = {}
         for r0, r1 in self.bands:
             shape = (r1 - r0, self.block.cols)
@@ -482,6 +487,7 @@ class OverlappedGemm:
                 # C lives on the other side of NVLink: decoupled stores, steady tile completion
                 try:
                     plan.set_option(_lib.OPT_TMA_STORE, 1)
+                    self._synced = True        # ... and the kernel does its own hand-shake
                     plan.set_option(_lib.OPT_PROGRESSIVE_ROUNDS, -1 if rounds is None else rounds)
                 except _lib.RollerError as e:
                     if e.status not in (_lib.ERR_UNSUPPORTED, _lib.ERR_INVALID):
@@ -503,16 +509,32 @@ class OverlappedGemm:
         n = 0
         if self.fused:
             self._step += 1
+            # one kernel per rank; its C is the root's matrix (this rank's own on the root)
+            out = self.peer_C[self.dests[0]] if self.dests else self.C
+            step, plan = self.steps[0], self.plans[0]
+            ptrs = (A_rows.data_ptr() + step.a_off * eb, B_full.data_ptr() + step.b_off * eb,
+                    out.data_ptr() + step.c_off * 4)
+            self._signalled = False
+            if self.rank != self.root and self._synced:
+                try:
+                    # "go": the root has finished with the previous step's C; "arrive": this
+                    # rank's stores of this step have landed
+                    plan.run_synced_ptr(
+                        *ptrs, go_ptr=self.flags.data_ptr() + 4 * FLAG_GO if self._step > 1 else 0,
+                        go_value=self._step - 1,
+                        arrive_ptr=self.peer_flags[self.root].data_ptr() + 4 * self.rank,
+                        arrive_value=self._step, stream=cs)
+                    self._signalled = True
+                    return
+                except self._lib.RollerError as e:
+                    if e.status != self._lib.ERR_UNSUPPORTED:
+                        raise
+                    self._synced = False
             if self.rank != self.root and self._step > 1:
-                # the root has finished with the previous step's C
                 self._lib.flag_wait_async(self.flags.data_ptr(), FLAG_WORDS, 1 << FLAG_GO,
                                           self._step - 1, self.flag_status.data_ptr(),
                                           self._wait_limit, cs)
-            # one kernel per rank; its C is the root's matrix (this rank's own on the root)
-            out = self.peer_C[self.dests[0]] if self.dests else self.C
-            for step, plan in zip(self.steps, self.plans):
-                plan.run_ptr(A_rows.data_ptr() + step.a_off * eb, B_full.data_ptr() + step.b_off * eb,
-                             out.data_ptr() + step.c_off * 4, cs)
+            plan.run_ptr(*ptrs, cs)
             return
         for step, plan, ev in zip(self.steps, self.plans, self._events):
             plan.run_ptr(A_rows.data_ptr() + step.a_off * eb, B_full.data_ptr() + step.b_off * eb,
@@ -533,6 +555,8 @@ class OverlappedGemm:
         cs = stream if stream is not None else torch.cuda.current_stream()
         if self.fused:
             if self.rank != self.root:
+                if self._signalled:
+                    return      # the kernel raised the flag itself
                 # behind the kernel on the stream: its stores into the root's C have been performed
                 self._lib.flag_signal_async([self.peer_flags[self.root].data_ptr() + 4 * self.rank],
                                             self._step, cs)

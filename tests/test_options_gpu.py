@@ -341,3 +341,76 @@ def test_arrival_flags_signal_and_bounded_wait():
         _lib.flag_signal_async([base + 2], 1)           # misaligned word
     with pytest.raises(_lib.RollerError):
         _lib.flag_signal_async([base] * 40, 1)          # more targets than one call takes
+
+
+@pytest.mark.parametrize("tile,rounds", [((256, 256, 2), 0), ((256, 256, 2), 4), ((128, 128, 1), 2)])
+def test_a_launch_that_does_its_own_hand_shake(tile, rounds):
+    """roller_b200_gemm_run_synced on one GPU, both flags in local memory: with "go" already
+    raised the result is the plain launch's and the arrival word holds the step afterwards; a
+    later "go" value also satisfies the wait; with "go" never raised the wait in front of the
+    first store runs out after about a millisecond, the launch is reported as failed and
+    raises no arrival flag; the plan is usable afterwards."""
+    M, N, K = 1024, 1536, 1024
+    A, B = g.make_inputs(M, N, K, "uniform", seed=21)
+    C64 = g.matmul_fp64(A, B)
+    dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    dC = torch.full((M, N), float("nan"), device="cuda")
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    go, arrive = flags.data_ptr(), flags.data_ptr() + 16
+    plan = _lib.GemmPlan(_lib.find_tile(*tile), M, N, K, mode=3)
+    plan.set_option(_lib.OPT_TMA_STORE, 1)
+    if rounds:
+        plan.set_option(_lib.OPT_PROGRESSIVE_ROUNDS, rounds)
+    ptrs = (dA.data_ptr(), dB.data_ptr(), dC.data_ptr())
+    for step, go_now in ((1, 0), (2, 1), (3, 5)):
+        flags[0] = go_now
+        dC.fill_(float("nan"))
+        torch.cuda.synchronize()
+        plan.run_synced_ptr(*ptrs, go_ptr=go if step > 1 else 0, go_value=step - 1,
+                            arrive_ptr=arrive, arrive_value=step)
+        torch.cuda.synchronize()
+        plan.check_status()
+        assert int(flags[4].item()) == step
+        assert g.err_norm(dC.cpu().numpy(), C64) <= TIGHT_3X
+    # without an arrival flag: only the wait for "go"
+    plan.run_synced_ptr(*ptrs, go_ptr=go, go_value=5)
+    torch.cuda.synchronize()
+    plan.check_status()
+    assert int(flags[4].item()) == 3
+    # "go" = 9 never comes
+    plan.set_option(_lib.OPT_WAIT_LIMIT_CYCLES, 2_000_000)
+    plan.run_synced_ptr(*ptrs, go_ptr=go, go_value=9, arrive_ptr=arrive, arrive_value=4)
+    torch.cuda.synchronize()
+    st = plan.device_status()
+    # (with tiles shared between workers, one waiting for another's partial sums may be the
+    # first whose limit runs out: the code then names that wait)
+    assert st == _lib.DEV_TIMEOUT_PEER or (rounds and st != 0)
+    assert int(flags[4].item()) == 3                # no arrival from a failed launch
+    plan.set_option(_lib.OPT_WAIT_LIMIT_CYCLES, 0)
+    flags[0] = 9
+    dC.fill_(float("nan"))
+    torch.cuda.synchronize()
+    plan.run_synced_ptr(*ptrs, go_ptr=go, go_value=9, arrive_ptr=arrive, arrive_value=4)
+    torch.cuda.synchronize()
+    plan.check_status()
+    assert int(flags[4].item()) == 4
+    assert g.err_norm(dC.cpu().numpy(), C64) <= TIGHT_3X
+    plan.destroy()
+
+
+def test_the_hand_shake_needs_the_tma_store_path():
+    M, N, K = 256, 250, 128        # rows of C are not multiples of 16 bytes: no TMA stores
+    dA = torch.zeros(M, K, device="cuda")
+    dB = torch.zeros(K, N, device="cuda")
+    dC = torch.zeros(M, N, device="cuda")
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    plan = _lib.GemmPlan(_lib.find_tile(128, 128, 1), M, N, K, mode=3)
+    with pytest.raises(_lib.RollerError) as e:
+        plan.run_synced_ptr(dA.data_ptr(), dB.data_ptr(), dC.data_ptr(),
+                            arrive_ptr=flags.data_ptr(), arrive_value=1)
+    assert e.value.status == _lib.ERR_UNSUPPORTED
+    with pytest.raises(_lib.RollerError) as e:
+        plan.run_synced_ptr(dA.data_ptr(), dB.data_ptr(), dC.data_ptr(),
+                            arrive_ptr=flags.data_ptr() + 2, arrive_value=1)
+    assert e.value.status == _lib.ERR_INVALID
+    plan.destroy()
