@@ -661,9 +661,9 @@ def strong_scaling(torch, dist, rank, world, steps, warmup, budget_s=240.0, all_
             paths = [("banded_root", ob, False), ("banded_all", None, True), ("fused_root", None, False)]
             if ob is None:
                 paths = []
-            elif M * N // world <= 1024 * 4096 or (all_jobs and name.startswith("M13")):
-                # a block of less than one wave of tiles: also with more rounds than the
-                # library would pick (earlier output, dearer exchange of partial tiles)
+            elif name.startswith("M13"):
+                # for comparison: four equal rounds instead of the geometric sequence the
+                # driver derives from t_link / t_compute
                 paths.append(("fused_root_r4", None, False))
             for label, og, everywhere in paths:
                 try:
@@ -671,7 +671,8 @@ def strong_scaling(torch, dist, rank, world, steps, warmup, budget_s=240.0, all_
                         og = mgpu.OverlappedGemm(M, N, K, rank, world, grid=grid, mode=mode,
                                                  dest="all" if everywhere else "root",
                                                  fused=label.startswith("fused_root"),
-                                                 rounds=4 if label.endswith("_r4") else None)
+                                                 rounds=4 if label.endswith("_r4") else None,
+                                                 round_ratio=100 if label.endswith("_r4") else None)
                 except Exception as e:  # noqa: BLE001 - keep the other paths' numbers
                     rec[label + "_error"] = f"{type(e).__name__}: {e}"[:200]
                     continue
@@ -693,6 +694,8 @@ def strong_scaling(torch, dist, rank, world, steps, warmup, budget_s=240.0, all_
                     info = og.plans[0].schedule_info()
                     rec[label.replace("fused_root", "fused_rounds")] = int(
                         max_over_ranks(float(info["rounds"])))
+                    rec[label.replace("fused_root", "fused_ratio")] = int(
+                        max_over_ranks(float(getattr(og, "round_ratio", 100) or 100)))
                 og.destroy()
                 del og
                 torch.cuda.empty_cache()

@@ -88,9 +88,17 @@ typedef enum roller_status {
 #define ROLLER_OPT_PROGRESSIVE_ROUNDS 4 /* n > 0: every tile is cut along K and the tiles are
                                           worked through in n groups by the whole grid, so that
                                           finished tiles leave the kernel at a steady rate from
-                                          early on rather than together at the end (rounded down
-                                          to a divisor of the tile count; at most 64). -1 = the
-                                          library picks n; 0 = off */
+                                          early on rather than together at the end (at most 16,
+                                          and at most one per tile). -1 = the library picks n;
+                                          0 = off */
+#define ROLLER_OPT_ROUND_RATIO 7        /* size of each round of the progressive schedule relative
+                                          to the one before it, in percent (25 .. 400; default
+                                          100 = equal rounds). When C leaves over a link while
+                                          the computation goes on, the time to the last byte is
+                                          shortest with a ratio of about t_link / t_compute:
+                                          shrinking rounds when the computation is the longer of
+                                          the two (little is left to send after the last round),
+                                          growing ones when the link is (it starts early) */
 #define ROLLER_OPT_COOPERATIVE_FIXUP 6  /* 1 (default): in the progressive schedule with TMA stores a
                                           tile shared by several workers is completed by all of
                                           them together, each adding a slice of everybody's
@@ -208,6 +216,12 @@ int roller_b200_gemm_launch_info(const roller_plan* plan, int* grid, int* block,
  * accumulation chunk. Any out pointer may be NULL. */
 int roller_b200_gemm_schedule_info(const roller_plan* plan, int* sk_tiles, int* rounds,
                                    int* unit_kb, int* chunk_kb);
+
+/* The rounds of the progressive schedule: writes the first tile of each round followed by the
+ * number of tiles cut along K into tile_begin[0 .. rounds] (`capacity` >= rounds + 1 entries,
+ * else ROLLER_ERR_INVALID). The reference has one block per tile and no rounds
+ * (src/roller.py:536). */
+int roller_b200_gemm_round_tiles(const roller_plan* plan, int* tile_begin, int capacity);
 
 /* Accumulation chunk of the 3xTF32 mode: the TMEM accumulator is drained into fp32 registers
  * every `k_elems` elements of the reduction (rounded up to whole 32-element steps; 0 = never,

@@ -28,6 +28,8 @@ OPT_TMA_STORE = 3
 OPT_PROGRESSIVE_ROUNDS = 4
 OPT_TEST_DROP_PUBLISH = 5
 OPT_COOPERATIVE_FIXUP = 6
+OPT_ROUND_RATIO = 7
+MAX_ROUNDS = 16
 MAX_FLAG_TARGETS = 32
 # device status words (what a bounded wait that ran out records)
 DEV_TIMEOUT_FIXUP = 7
@@ -94,6 +96,7 @@ SIGNATURES = {
                                               C.c_void_p]),
     "roller_b200_gemm_launch_info": (C.c_int, [C.c_void_p] + [C.POINTER(C.c_int)] * 6),
     "roller_b200_gemm_schedule_info": (C.c_int, [C.c_void_p] + [C.POINTER(C.c_int)] * 4),
+    "roller_b200_gemm_round_tiles": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.c_int]),
     "roller_b200_gemm_set_chunk": (C.c_int, [C.c_void_p, C.c_int]),
     "roller_b200_gemm_set_grid": (C.c_int, [C.c_void_p, C.c_int]),
     "roller_b200_gemm_set_stream_k": (C.c_int, [C.c_void_p, C.c_int]),
@@ -315,6 +318,14 @@ class GemmPlan:
         check(self._lib.roller_b200_gemm_schedule_info(self._h, *[C.byref(v) for v in vals]),
               "roller_b200_gemm_schedule_info")
         return {k: v.value for k, v in zip(("sk_tiles", "rounds", "unit_kb", "chunk_kb"), vals)}
+
+    def round_tiles(self) -> list:
+        """First tile of every round of the progressive schedule, then the number of tiles cut
+        along K: rounds + 1 values."""
+        buf = (C.c_int * (MAX_ROUNDS + 1))()
+        check(self._lib.roller_b200_gemm_round_tiles(self._h, buf, MAX_ROUNDS + 1),
+              "roller_b200_gemm_round_tiles")
+        return list(buf[: self.schedule_info()["rounds"] + 1])
 
     def device_status(self) -> int:
         """The plan's device status word (0 = every bounded wait completed). Synchronises the

@@ -166,6 +166,8 @@ struct roller_plan {
   uint32_t epoch;         // launch counter for the flags (1 .. 2^26-1)
   int sk_rounds;          // rounds of the progressive schedule in use (1 = plain stream-K)
   int progressive;        // requested rounds of the progressive schedule; 0 = off
+  int round_ratio;        // size of a round relative to the previous one, in percent
+  rb200::RoundPlan round_plan;  // first tile of every round in use
   long long spin_limit;   // clock cycles a device-side wait may last
   bool overlap_launch;    // launches carry the programmatic-stream-serialization attribute
   bool tma_store;         // C leaves through shared memory and TMA stores
@@ -493,14 +495,13 @@ int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, void* C, 
     args.flags |= kFlagVecStore;
   if (p->c_elem == 2) args.flags |= kFlagC16;
   if (tma_store) args.flags |= kFlagTmaStore;
-  // In the progressive schedule tiles are shared on purpose. Where a tile is shared by three
-  // workers or more it is completed by all of them together; with fewer, the worker holding the
-  // end of the reduction does it alone (measured: the cooperative form costs a tenth more when
-  // tiles are shared by one or two workers and saves a third to a half beyond four).
-  if (tma_store && p->progressive != 0 && p->sk_tiles > 0 && p->coop_fixup &&
-      static_cast<long long>(p->grid / kv->cta_group) * p->sk_rounds >= 3ll * p->sk_tiles)
+  // In the progressive schedule tiles are shared on purpose. With this flag the kernel lets
+  // all workers of a tile complete it together in the rounds where a tile is shared by three
+  // workers or more; in the others the worker holding the end of the reduction does it alone.
+  if (tma_store && p->progressive != 0 && p->sk_tiles > 0 && p->coop_fixup)
     args.flags |= kFlagCoopFixup;
   if (p->drop_publish) args.flags |= kFlagDropPublish;
+  args.round_plan = p->round_plan;
   args.peer = p->peer;
   if (peer_sync) {
     args.flags |= kFlagPeerSync;
@@ -633,6 +634,14 @@ int roller_b200_gemm_schedule_info(const roller_plan* p, int* sk_tiles, int* rou
   return ROLLER_OK;
 }
 
+int roller_b200_gemm_round_tiles(const roller_plan* p, int* tile_begin, int capacity) {
+  if (!p || !tile_begin || capacity < p->sk_rounds + 1) return ROLLER_ERR_INVALID;
+  if (p->layout == 3) return ROLLER_ERR_UNSUPPORTED;
+  for (int r = 0; r <= p->sk_rounds; ++r)
+    tile_begin[r] = p->sk_rounds > 1 ? p->round_plan.tile_begin[r] : (r == 0 ? 0 : p->sk_tiles);
+  return ROLLER_OK;
+}
+
 int roller_b200_gemm_set_chunk(roller_plan* p, int k_elems) {
   if (!p || k_elems < 0) return ROLLER_ERR_INVALID;
   if (p->layout == 3) return ROLLER_OK;   // fp32 FMAs: there is no accumulator to drain
@@ -708,8 +717,12 @@ int roller_b200_gemm_set_option(roller_plan* p, int option, long long value) {
       p->tma_forced = value != 0;
       p->map_c_ptr = nullptr;
       return ROLLER_OK;
+    case ROLLER_OPT_ROUND_RATIO:
+      if (value < 25 || value > 400) return ROLLER_ERR_INVALID;
+      p->round_ratio = static_cast<int>(value);
+      return plan_configure(p);
     case ROLLER_OPT_PROGRESSIVE_ROUNDS:
-      if (value < -1 || value > 64) return ROLLER_ERR_INVALID;
+      if (value < -1 || value > kMaxRounds) return ROLLER_ERR_INVALID;
       if (value != 0 && ((p->flags & ROLLER_FLAG_ACCUMULATE) || p->layout == 3))
         return ROLLER_ERR_UNSUPPORTED;
       p->progressive = static_cast<int>(value);
@@ -855,12 +868,12 @@ static int plan_configure(roller_plan* p) {
       // Less than one wave of tiles: without rounds everything would leave at the very end.
       // Four rounds (tiles shared by four to five workers, completed cooperatively) cost a
       // quarter more time and put three quarters of the output on its way early.
-      if (tiles <= workers && tiles % 4 == 0 && tiles >= workers / 2) want = 4;
+      if (tiles <= workers && tiles >= workers / 2) want = 4;
     }
-    if (want > 64) want = 64;
+    if (want > kMaxRounds) want = kMaxRounds;
+    if (want > tiles) want = tiles;
     if (want < 1) want = 1;
     rounds = static_cast<int>(want);
-    while (rounds > 1 && tiles % rounds != 0) --rounds;
     sk_tiles = static_cast<int>(tiles);
   } else if (p->sk_mode != 0 && r != 0 && cpt > 1 && !(p->flags & ROLLER_FLAG_ACCUMULATE)) {
     const long long full = tiles / workers;
@@ -885,6 +898,26 @@ static int plan_configure(roller_plan* p) {
   }
   p->sk_tiles = sk_tiles;
   p->sk_rounds = rounds;
+  // The rounds' shares of the tiles: a geometric sequence with the plan's ratio, every round at
+  // least one tile (the boundaries are rounded cumulative shares, pushed apart where needed).
+  {
+    const double ratio = p->round_ratio > 0 ? p->round_ratio / 100.0 : 1.0;
+    double total = 0.0, term = 1.0;
+    for (int r = 0; r < rounds; ++r, term *= ratio) total += term;
+    double cum = 0.0;
+    term = 1.0;
+    p->round_plan.tile_begin[0] = 0;
+    for (int r = 1; r <= rounds; ++r, term *= ratio) {
+      cum += term;
+      long long b = static_cast<long long>(cum / total * sk_tiles + 0.5);
+      const long long lo = p->round_plan.tile_begin[r - 1] + 1;   // a tile for round r - 1 ...
+      const long long hi = sk_tiles - (rounds - r);               // ... and one for each later round
+      if (b < lo) b = lo;
+      if (b > hi) b = hi;
+      p->round_plan.tile_begin[r] = static_cast<int>(r == rounds ? sk_tiles : b);
+    }
+    for (int r = rounds + 1; r <= kMaxRounds; ++r) p->round_plan.tile_begin[r] = sk_tiles;
+  }
   if (sk_tiles && p->sk_slots < p->grid) {
     cudaFree(p->sk_ws);
     cudaFree(p->sk_flags);

@@ -38,6 +38,13 @@ struct PeerSync {
   uint32_t arrive_value;
 };
 
+// Rounds of the progressive schedule: round r owns the stream-K tiles
+// [tile_begin[r], tile_begin[r + 1]); tile_begin[rounds] = sk_tiles. Unused with one round.
+constexpr int kMaxRounds = 16;
+struct RoundPlan {
+  int tile_begin[kMaxRounds + 1];
+};
+
 struct GemmArgs {
   CUtensorMap tmA;
   CUtensorMap tmB;
@@ -59,6 +66,7 @@ struct GemmArgs {
                         // at 4 * grid words by one reader count per slot
   uint32_t epoch;       // distinguishes this launch's flags from earlier launches' (1 .. 2^26-1)
   PeerSync peer;        // all zero unless kFlagPeerSync is set
+  RoundPlan round_plan; // read when sk_rounds > 1
 };
 
 struct KernelVariant {

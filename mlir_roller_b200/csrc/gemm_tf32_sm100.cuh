@@ -268,60 +268,75 @@ struct Segment {
 
 // Static schedule shared by the producer, split, MMA and epilogue roles (each walks its own copy).
 //
-// The first `sk_tiles` tiles are cut into units of `chunk_kb` k-blocks; the units, in tile
-// order, are dealt out in contiguous runs to rounds * workers "virtual workers", and worker w
-// plays the virtual workers w, w + workers, w + 2 workers, ... one after the other (one per
-// round). With rounds == 1 that is the plain stream-K deal. The remaining tiles follow whole,
-// round-robin. `rounds` must divide sk_tiles, so that no tile straddles two rounds. From one
-// round to the next the workers change places (worker w plays position (w + round * rot) mod
-// workers of the round): every round has the same shape, and without the rotation the same few
-// workers would end up completing a tile -- and paying for the exchange of partial sums -- in
-// every round while all others wait for them.
-// All of it is 32-bit arithmetic (the host only enables the split when units < 2^31 and
-// virtual workers < 2^15): a 64-bit division is a subroutine call on the device.
+// The first `sk_tiles` tiles are cut into units of `chunk_kb` k-blocks and worked through in
+// `rounds` rounds: round r owns tiles [tile_begin[r], tile_begin[r + 1]) (RoundPlan, made by
+// the host; no tile straddles two rounds), and its units, in tile order, are dealt out in
+// contiguous runs to the `workers` positions of the round. With rounds == 1 that is the plain
+// stream-K deal. The remaining tiles follow whole, round-robin. Rounds need not be equally
+// large: when C leaves over a link while the computation goes on, rounds that shrink (or grow)
+// geometrically keep the link busy from early on and leave little to send after the last one.
+// From one round to the next the workers change places (worker w plays position
+// (w + round * rot) mod workers of the round): without the rotation the same few workers would
+// end up completing a tile -- and paying for the exchange of partial sums -- in every round
+// while all others wait for them.
+// All of it is 32-bit arithmetic (the host only enables the split when units < 2^31): a 64-bit
+// division is a subroutine call on the device.
+struct RoundShape {
+  int base;          // first unit of the round
+  int tiles;         // tiles the round owns
+  uint32_t q, rem;   // units of the round / workers, and the remainder
+};
+
 struct Schedule {
   int num_tiles, workers, worker, num_kb, chunk_kb, cpt, sk_tiles, rounds;
+  const RoundPlan* plan;
   int round;             // round whose units are being consumed
   int rot;               // positions the workers move on from one round to the next
   int pos;               // this worker's position in the current round
-  uint32_t vworkers;     // rounds * workers
-  uint32_t q, rem;       // units / vworkers and units % vworkers
   int u_begin, u_end;    // this worker's units of the current round, consumed from the end
   int dp_next;           // next whole tile
 
   __device__ Schedule(int num_tiles_, int workers_, int worker_, int num_kb_, int chunk_kb_,
-                      int sk_tiles_, int rounds_)
+                      int sk_tiles_, int rounds_, const RoundPlan* plan_)
       : num_tiles(num_tiles_), workers(workers_), worker(worker_), num_kb(num_kb_),
-        chunk_kb(chunk_kb_), sk_tiles(sk_tiles_), rounds(rounds_), round(0) {
+        chunk_kb(chunk_kb_), sk_tiles(sk_tiles_), rounds(rounds_), plan(plan_), round(0) {
     cpt = (num_kb + chunk_kb - 1) / chunk_kb;
-    vworkers = static_cast<uint32_t>(workers) * static_cast<uint32_t>(rounds);
-    const uint32_t units = static_cast<uint32_t>(sk_tiles) * static_cast<uint32_t>(cpt);
-    q = units / vworkers;
-    rem = units % vworkers;
     rot = rounds > 1 ? (workers * 3) / 8 + 1 : 0;
     pos = worker;
-    u_begin = unit_begin(worker);
-    u_end = unit_begin(worker + 1);
+    const RoundShape rs = shape(0);
+    u_begin = unit_begin(rs, worker);
+    u_end = unit_begin(rs, worker + 1);
     dp_next = sk_tiles + worker;
+  }
+  __device__ RoundShape shape(int r) const {
+    RoundShape rs;
+    const int t0 = rounds > 1 ? static_cast<int>(plan->tile_begin[r]) : 0;
+    const int t1 = rounds > 1 ? static_cast<int>(plan->tile_begin[r + 1]) : sk_tiles;
+    rs.base = t0 * cpt;
+    rs.tiles = t1 - t0;
+    const uint32_t units = static_cast<uint32_t>(rs.tiles) * static_cast<uint32_t>(cpt);
+    rs.q = units / static_cast<uint32_t>(workers);
+    rs.rem = units - rs.q * static_cast<uint32_t>(workers);
+    return rs;
   }
   // Worker at position `p` of round `r`.
   __device__ int worker_at(int p, int r) const {
     int w = (p - r * rot) % workers;
     return w < 0 ? w + workers : w;
   }
-  // First unit of virtual worker v (v = round * workers + position in the round):
-  // floor(units * v / vworkers) = q * v + floor(rem * v / vworkers), no product above 2^31.
-  __device__ int unit_begin(int v) const {
-    const uint32_t uv = static_cast<uint32_t>(v);
-    return static_cast<int>(q * uv + rem * uv / vworkers);
+  // First unit of position p (0 .. workers) of a round:
+  // base + floor(units * p / workers) = base + q * p + floor(rem * p / workers).
+  __device__ int unit_begin(const RoundShape& rs, int p) const {
+    const uint32_t up = static_cast<uint32_t>(p);
+    return rs.base + static_cast<int>(rs.q * up + rs.rem * up / static_cast<uint32_t>(workers));
   }
   __device__ bool next(Segment& s) {
     while (u_end <= u_begin && round + 1 < rounds) {
       ++round;
       pos = (worker + round * rot) % workers;
-      const int v = round * workers + pos;
-      u_begin = unit_begin(v);
-      u_end = unit_begin(v + 1);
+      const RoundShape rs = shape(round);
+      u_begin = unit_begin(rs, pos);
+      u_end = unit_begin(rs, pos + 1);
     }
     if (u_end > u_begin) {
       const int tile = (u_end - 1) / cpt;
@@ -395,7 +410,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                  const __grid_constant__ CUtensorMap tmC, float* __restrict__ C, int M, int N, int K,
                  long long ldc, int tiles_m, int tiles_n, int chunk_kb, int acc_kb, int flags,
                  uint32_t* status, long long spin_limit, int sk_tiles, int sk_rounds, float* sk_ws,
-                 uint32_t* sk_flags, uint32_t epoch, const PeerSync peer) {
+                 uint32_t* sk_flags, uint32_t epoch, const PeerSync peer,
+                 const __grid_constant__ RoundPlan round_plan) {
   // chunk_kb: the unit of the stream-K schedule (a tile's reduction is dealt out in pieces of
   // that many k-blocks); acc_kb: how many k-blocks accumulate in TMEM before the accumulate
   // warps drain them into registers. 3xTF32 uses the same value for both; the modes whose
@@ -459,7 +475,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int num_kb = (K + BK - 1) / BK;
   Schedule sched(tiles_m * tiles_n, static_cast<int>(gridDim.x) / CG,
-                 static_cast<int>(blockIdx.x) / CG, num_kb, chunk_kb, sk_tiles, sk_rounds);
+                 static_cast<int>(blockIdx.x) / CG, num_kb, chunk_kb, sk_tiles, sk_rounds,
+                 &round_plan);
   Segment sg;
 
   if (warp < Cfg::FIRST_EPI_WARP) {
@@ -625,21 +642,21 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     };
     // which of a position's two partials of a round belongs to tile t: the one holding the
     // position's last unit is published first (0), the other one (1) second
-    auto which_of = [&](int v_round0, int p, int t) {
-      return ((sched.unit_begin(v_round0 + p + 1) - 1) / sched.cpt == t) ? 0 : 1;
+    auto which_of = [&](const RoundShape& rs, int p, int t) {
+      return ((sched.unit_begin(rs, p + 1) - 1) / sched.cpt == t) ? 0 : 1;
     };
     auto flush_pending = [&]() -> bool {
       for (int e = 0; e < npend; ++e) {
         const int T = e ? pend_tile1 : pend_tile0, pos = e ? pend_pos1 : pend_pos0, round = pend_round;
         const uint32_t tag = (epoch << 6) | static_cast<uint32_t>(round);
-        const int v0 = round * sched.workers;
+        const RoundShape rs = sched.shape(round);
         const int u0 = T * sched.cpt, u1 = u0 + sched.cpt;
         int p_first = pos, p_last = pos;
-        while (p_first > 0 && sched.unit_begin(v0 + p_first) > u0) --p_first;
-        while (p_last < sched.workers - 1 && sched.unit_begin(v0 + p_last + 1) < u1) ++p_last;
+        while (p_first > 0 && sched.unit_begin(rs, p_first) > u0) --p_first;
+        while (p_last < sched.workers - 1 && sched.unit_begin(rs, p_last + 1) < u1) ++p_last;
         int P = 0, my_idx = 0;
         for (int p = p_first; p <= p_last; ++p) {
-          if (sched.unit_begin(v0 + p + 1) == sched.unit_begin(v0 + p)) continue;   // no units
+          if (sched.unit_begin(rs, p + 1) == sched.unit_begin(rs, p)) continue;   // no units
           if (p < pos) ++my_idx;
           ++P;
         }
@@ -648,11 +665,11 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // wait for every partial of the tile: thread i watches position p_first + i
         const int mine = p_first + et;
         const bool watching = mine <= p_last &&
-                              sched.unit_begin(v0 + mine + 1) != sched.unit_begin(v0 + mine);
+                              sched.unit_begin(rs, mine + 1) != sched.unit_begin(rs, mine);
         uint32_t* my_watch = nullptr;
         bool failed = false;
         if (watching) {
-          my_watch = sk_flags + coop_slot(sched.worker_at(mine, round), round, which_of(v0, mine, T));
+          my_watch = sk_flags + coop_slot(sched.worker_at(mine, round), round, which_of(rs, mine, T));
           const long long t0 = clock64();
           uint32_t spins = 0;
           while (ld_acquire_gpu(my_watch) != tag) {
@@ -676,9 +693,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0.0f;
           for (int p = p_first; p <= p_last; ++p) {
-            if (sched.unit_begin(v0 + p + 1) == sched.unit_begin(v0 + p)) continue;
+            if (sched.unit_begin(rs, p + 1) == sched.unit_begin(rs, p)) continue;
             const float4* slot = reinterpret_cast<const float4*>(
-                sk_ws + coop_slot(sched.worker_at(p, round), round, which_of(v0, p, T)) * kSlotFloats);
+                sk_ws + coop_slot(sched.worker_at(p, round), round, which_of(rs, p, T)) * kSlotFloats);
 #pragma unroll
             for (int jj = 0; jj < 8; ++jj) {
               const float4 q = __ldcg(slot + (8 * c + jj) * 256 + et);
@@ -722,11 +739,23 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       return true;
     };
 
+    int rs_round = -1;
+    RoundShape rs_cur = {0, 0, 0u, 0u};
+    bool coop_round = false;
     while (ok && sched.next(sg)) {
       if constexpr (Cfg::STAGING_BYTES > 0) {
         if (coop && npend > 0 && sg.round != pend_round) {
           if (!flush_pending()) { ok = false; break; }
         }
+      }
+      if (sk_active && sg.round != rs_round) {
+        rs_round = sg.round;
+        rs_cur = sched.shape(sg.round);
+        // Whether the round's shared tiles are completed by all their workers together is
+        // decided per round, the same way by everybody: it pays where a tile is shared by
+        // three workers or more (measured: a tenth dearer with one or two, a third to a half
+        // cheaper beyond four).
+        coop_round = coop && sched.workers >= 3 * rs_cur.tiles;
       }
       int mb, nb;
       tile_coords(sg.tile, tiles_m, tiles_n, mb, nb);
@@ -767,10 +796,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
 
       if constexpr (Cfg::STAGING_BYTES > 0) {
-        if (coop && !(sg.kb0 == 0 && sg.final)) {
+        if (coop_round && !(sg.kb0 == 0 && sg.final)) {
           // part of a shared tile: publish it and note it; it is completed in flush_pending
-          const int v0 = sg.round * sched.workers;
-          const size_t slot_i = coop_slot(sched.worker, sg.round, which_of(v0, sg.pos, sg.tile));
+          const size_t slot_i = coop_slot(sched.worker, sg.round, which_of(rs_cur, sg.pos, sg.tile));
           uint32_t* my_flag = sk_flags + slot_i;
           if (sg.round > 1) {
             // the slot still holds the partial of two rounds ago until its readers are done
@@ -806,12 +834,15 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       }
       // Flags carry the launch and the round, so a slot's reader never takes one round's
-      // partial sums for another's; zero means "slot free". A worker owns two slots and
-      // alternates between them from round to round, so it only ever waits for a reader that
-      // is two rounds behind.
+      // partial sums for another's; zero means "slot free". Here a worker publishes at most once
+      // per round, into the first of the round's two slots (the same numbering as the
+      // cooperative form, which may be in use in other rounds of the launch); the slots
+      // alternate from round to round, so a worker only ever waits for a reader that is two
+      // rounds behind.
       const uint32_t tag = (epoch << 6) | static_cast<uint32_t>(sg.round);
-      const int parity = sg.round & 1;
-      auto slot_index = [&](int w) { return (static_cast<size_t>(w) * CG + cta_rank) * 2 + parity; };
+      auto slot_index = [&](int w) {
+        return (static_cast<size_t>(w) * CG + cta_rank) * 4 + static_cast<size_t>((sg.round & 1) * 2);
+      };
       if (!sg.final) {
         // Publish this worker's partial sums of the tile, then raise its flag.
         uint32_t* my_flag = sk_flags + slot_index(sched.worker);
@@ -852,12 +883,11 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // position back), then they are added in a fixed order -- the result does not depend on
         // who arrived first -- and finally all slots are handed back together.
         const int tile_u0 = sg.tile * sched.cpt;
-        const int v_round0 = sg.round * sched.workers;
         int p_first = sg.pos - 1;
-        while (p_first > 0 && sched.unit_begin(v_round0 + p_first) > tile_u0) --p_first;
+        while (p_first > 0 && sched.unit_begin(rs_cur, p_first) > tile_u0) --p_first;
         const int mine = sg.pos - 1 - et;     // the position this thread watches, if any
         const bool watching = mine >= p_first &&
-                              sched.unit_begin(v_round0 + mine + 1) != sched.unit_begin(v_round0 + mine);
+                              sched.unit_begin(rs_cur, mine + 1) != sched.unit_begin(rs_cur, mine);
         bool failed = false;
         if (watching) {
           const uint32_t* flag = sk_flags + slot_index(sched.worker_at(mine, sg.round));
@@ -877,7 +907,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (epi_bar_any(failed)) { ok = false; break; }
         for (int p = sg.pos - 1; p >= p_first; --p) {
           // A position with no units in this round published nothing.
-          if (sched.unit_begin(v_round0 + p + 1) == sched.unit_begin(v_round0 + p)) continue;
+          if (sched.unit_begin(rs_cur, p + 1) == sched.unit_begin(rs_cur, p)) continue;
           const float4* slot = reinterpret_cast<const float4*>(
               sk_ws + slot_index(sched.worker_at(p, sg.round)) * kSlotFloats);
 #pragma unroll

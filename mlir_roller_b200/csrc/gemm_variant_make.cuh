@@ -27,7 +27,7 @@ static cudaError_t launch_variant(const GemmArgs& a, int grid, cudaStream_t stre
   return cudaLaunchKernelEx(&cfg, gemm_tf32_kernel<Cfg>, a.tmA, a.tmB, a.tmC, a.C, a.M, a.N, a.K,
                             a.ldc, a.tiles_m, a.tiles_n, a.chunk_kb, a.acc_kb, a.flags, a.status,
                             a.spin_limit, a.sk_tiles, a.sk_rounds, a.sk_ws, a.sk_flags, a.epoch,
-                            a.peer);
+                            a.peer, a.round_plan);
 }
 
 // The table's `mode` is the caller-visible one: 1 / 3 for fp32 operands (1xTF32 / 3xTF32),

@@ -210,6 +210,7 @@ extern "C" int roller_b200_gemm_static_scratch(const roller_ktile* tile, int mod
   args.sk_flags = nullptr;
   args.epoch = 1;
   args.peer = PeerSync{};
+  args.round_plan = RoundPlan{};
   const long long tiles = static_cast<long long>(args.tiles_m) * args.tiles_n;
   int workers = dev->sm_count / kv->cta_group;
   if (kv->cta_group == 2 && variant_idx >= 0) {

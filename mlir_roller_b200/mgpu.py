@@ -378,6 +378,31 @@ def band_schedule(block: Block, N: int, K: int, bands: int, dests: Sequence[int]
             for r0, r1 in split_bands(block.row0, block.row1, bands, taper=taper)]
 
 
+# What the TMA units of several GPUs together push into one GPU's memory over NVLink (measured
+# on B200 / NVSwitch; a copy engine reaches 770).
+PEER_STORE_GBS = 690.0
+
+
+def fused_round_shape(ingress_bytes: int, kernel_ms: float, rounds: Optional[int] = None,
+                      round_ratio: Optional[int] = None) -> Tuple[int, int]:
+    """Rounds of the progressive schedule for a kernel whose C leaves over NVLink while it
+    computes: (number of rounds, size of each round relative to the previous one in percent).
+
+    With a = t_link / t_compute and rounds whose sizes form a geometric sequence of ratio a,
+    every round's output has just left when the next round's arrives, and the last byte lands
+    at t_compute * (a + (1 - a) / (1 - a^R)): for a < 1 (the computation is the longer of the
+    two) the rounds shrink, so little is left to send at the end; for a > 1 they grow, so the
+    link -- the bottleneck -- starts after a small first round. `ingress_bytes` is what all
+    senders together push into the collecting GPU, `kernel_ms` one sender's kernel time."""
+    link_ms = ingress_bytes / (PEER_STORE_GBS * 1e6)
+    a = link_ms / max(kernel_ms, 1e-6)
+    if rounds is None:
+        rounds = 4 if a <= 1.0 else 8
+    if round_ratio is None:
+        round_ratio = int(min(250, max(40, round(100 * a))))
+    return rounds, round_ratio
+
+
 class OverlappedGemm:
     """Sharded C = A @ B whose exchange of C runs underneath the computation.
 
@@ -416,7 +441,8 @@ class OverlappedGemm:
                  grid: Optional[Tuple[int, int]] = None, mode: int = 3,
                  bands: Optional[int] = None, dest: str = "root", root: int = 0, group=None, arch=None, measure: bool = False,
                  comm_streams: int = 2, taper: bool = False, fused: bool = False,
-                 rounds: Optional[int] = None, wait_limit_cycles: int = 0):
+                 rounds: Optional[int] = None, round_ratio: Optional[int] = None,
+                 wait_limit_cycles: int = 0):
         import os
         # plain peer mappings only: no NVLink multicast object is bound to the buffer
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
@@ -473,14 +499,15 @@ class OverlappedGemm:
         self.bands = [(st.row0, st.row1) for st in self.steps]
         self.plans, self.tiles, self._events = [], [], []
         self._synced = self._signalled = False
+        self.rounds = self.round_ratio = None
         by_shape = {}
         for r0, r1 in self.bands:
             shape = (r1 - r0, self.block.cols)
             if shape not in by_shape:
                 cfg = MatmulConfig(shape[0], shape[1], K, _el_bits(mode))
-                hint, _fn, _ms = roller.best_hint(cfg, arch, mode=mode, measure=measure)
-                by_shape[shape] = roller.kernel_tile_for(hint)
-            tile = by_shape[shape]
+                hint, _fn, ms = roller.best_hint(cfg, arch, mode=mode, measure=measure)
+                by_shape[shape] = (roller.kernel_tile_for(hint), ms if ms else hint.est_us * 1e-3)
+            tile, kernel_ms = by_shape[shape]
             self.tiles.append(tile)
             plan = _lib.GemmPlan(tile, shape[0], shape[1], K, lda=K, ldb=N, ldc=N, mode=mode)
             if fused and self.dests:
@@ -488,7 +515,11 @@ class OverlappedGemm:
                 try:
                     plan.set_option(_lib.OPT_TMA_STORE, 1)
                     self._synced = True        # ... and the kernel does its own hand-shake
-                    plan.set_option(_lib.OPT_PROGRESSIVE_ROUNDS, -1 if rounds is None else rounds)
+                    self.rounds, self.round_ratio = fused_round_shape(
+                        self.block.rows * self.block.cols * 4 * (world_size - 1), kernel_ms,
+                        rounds, round_ratio)
+                    plan.set_option(_lib.OPT_PROGRESSIVE_ROUNDS, self.rounds)
+                    plan.set_option(_lib.OPT_ROUND_RATIO, self.round_ratio)
                 except _lib.RollerError as e:
                     if e.status not in (_lib.ERR_UNSUPPORTED, _lib.ERR_INVALID):
                         raise

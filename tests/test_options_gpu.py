@@ -135,7 +135,7 @@ def test_progressive_schedule_matches_the_oracle(tile, mode, rounds):
                                            (_lib.OPT_TMA_STORE, staged),
                                            (_lib.OPT_COOPERATIVE_FIXUP, coop)], launches=3, info=info)
         tiles = info["tiles_m"] * info["tiles_n"]
-        assert info["sk_tiles"] == tiles and tiles % info["rounds"] == 0
+        assert info["sk_tiles"] == tiles and 1 <= info["rounds"] <= min(tiles, _lib.MAX_ROUNDS)
         if rounds > 0:
             assert info["rounds"] == rounds
         for out in outs:
@@ -151,8 +151,42 @@ def test_progressive_schedule_on_a_ragged_problem():
     for tile in [(256, 128, 2), (128, 64, 1)]:
         info = {}
         out = run_plan(A, B, tile, 3, [(_lib.OPT_PROGRESSIVE_ROUNDS, 5)], launches=2, info=info)
-        assert info["rounds"] >= 1 and (info["tiles_m"] * info["tiles_n"]) % info["rounds"] == 0
+        assert info["rounds"] == 5          # (the tile count need not be a multiple of it)
         assert g.err_norm(out[1], C64) <= TIGHT_3X
+
+
+@pytest.mark.parametrize("tile", [(256, 256, 2), (128, 128, 1)])
+@pytest.mark.parametrize("rounds,ratio", [(4, 60), (4, 150), (7, 40), (16, 100), (3, 400)])
+def test_rounds_of_unequal_size(tile, rounds, ratio):
+    """ROLLER_OPT_ROUND_RATIO: the rounds' shares of the tiles form a geometric sequence. The
+    library's boundaries are the host model's (tests/test_schedule_model.py), rounds of both
+    kinds (tiles completed by one worker or by all) follow each other in one launch, and the
+    result is the oracle's on three launches in a row."""
+    from test_schedule_model import round_tiles
+    M, N, K = 1280, 2304, 1024
+    A, B = g.make_inputs(M, N, K, "uniform", seed=12)
+    C64 = g.matmul_fp64(A, B)
+    dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    dC = torch.empty(M, N, device="cuda")
+    plan = _lib.GemmPlan(_lib.find_tile(*tile), M, N, K, mode=3)
+    plan.set_option(_lib.OPT_TMA_STORE, 1)
+    plan.set_option(_lib.OPT_PROGRESSIVE_ROUNDS, rounds)
+    plan.set_option(_lib.OPT_ROUND_RATIO, ratio)
+    tiles = -(-M // tile[0]) * -(-N // tile[1])
+    assert plan.schedule_info()["rounds"] == rounds
+    assert plan.round_tiles() == round_tiles(tiles, rounds, ratio)
+    outs = []
+    for _ in range(3):
+        dC.fill_(float("nan"))
+        plan.run(dA, dB, dC)
+        torch.cuda.synchronize()
+        plan.check_status()
+        outs.append(dC.cpu().numpy())
+        assert g.err_norm(outs[-1], C64) <= TIGHT_3X
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[1], outs[2])
+    with pytest.raises(_lib.RollerError):
+        plan.set_option(_lib.OPT_ROUND_RATIO, 10)
+    plan.destroy()
 
 
 def test_back_to_back_launches_with_and_without_overlap():
