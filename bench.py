@@ -555,7 +555,8 @@ class _Checker:
         return float(d) / self.scale
 
 
-def strong_scaling(torch, dist, rank, world, steps, warmup, budget_s=240.0, all_jobs=False):
+def strong_scaling(torch, dist, rank, world, steps, warmup, budget_s=240.0, all_jobs=False,
+                   fused_shapes=()):
     """The sharded configurations. Per job and mode: the local kernels alone ("kernels"), followed
     by an NCCL gather of C to rank 0 ("gather"), with the exchange of C running underneath the
     computation through the copy engines to rank 0 ("banded_root") and to every rank
@@ -594,6 +595,13 @@ def strong_scaling(torch, dist, rank, world, steps, warmup, budget_s=240.0, all_
         t = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
+
+    def shape_of(label):
+        # "fused_root_R<rounds>_<ratio>" -> (rounds, ratio); anything else: the driver's choice
+        if "_R" not in label:
+            return None, None
+        r, q = label.split("_R")[1].split("_")
+        return int(r), int(q)
 
     def max_over_ranks(x):
         # NaN must survive the reduction: send it as +inf
@@ -665,14 +673,16 @@ def strong_scaling(torch, dist, rank, world, steps, warmup, budget_s=240.0, all_
                 # for comparison: four equal rounds instead of the geometric sequence the
                 # driver derives from t_link / t_compute
                 paths.append(("fused_root_r4", None, False))
+                # (--fused-shapes: other round counts and ratios of the progressive schedule)
+                paths.extend((f"fused_root_R{r}_{q}", None, False) for r, q in fused_shapes)
             for label, og, everywhere in paths:
                 try:
                     if og is None:
                         og = mgpu.OverlappedGemm(M, N, K, rank, world, grid=grid, mode=mode,
                                                  dest="all" if everywhere else "root",
                                                  fused=label.startswith("fused_root"),
-                                                 rounds=4 if label.endswith("_r4") else None,
-                                                 round_ratio=100 if label.endswith("_r4") else None)
+                                                 rounds=4 if label.endswith("_r4") else shape_of(label)[0],
+                                                 round_ratio=100 if label.endswith("_r4") else shape_of(label)[1])
                 except Exception as e:  # noqa: BLE001 - keep the other paths' numbers
                     rec[label + "_error"] = f"{type(e).__name__}: {e}"[:200]
                     continue
@@ -692,10 +702,11 @@ def strong_scaling(torch, dist, rank, world, steps, warmup, budget_s=240.0, all_
                     rec["bands"] = len(og.bands)
                 if label.startswith("fused_root") and og.plans:
                     info = og.plans[0].schedule_info()
+                    # (the sending ranks' schedule; rank 0 keeps C at home and runs whole tiles)
                     rec[label.replace("fused_root", "fused_rounds")] = int(
-                        max_over_ranks(float(info["rounds"])))
+                        max_over_ranks(float(info["rounds"]) if rank != 0 else 0.0))
                     rec[label.replace("fused_root", "fused_ratio")] = int(
-                        max_over_ranks(float(getattr(og, "round_ratio", 100) or 100)))
+                        max_over_ranks(float(og.round_ratio or 0) if rank != 0 else 0.0))
                 og.destroy()
                 del og
                 torch.cuda.empty_cache()
@@ -713,8 +724,8 @@ def strong_scaling(torch, dist, rank, world, steps, warmup, budget_s=240.0, all_
             # measured 770 GB/s per direction
             link_ms = (world - 1) / world * M * N * 4 / 770e9 * 1e3
             rec["link_bound_ms"] = link_ms
-            best_root = min(rec.get(k, float("inf")) for k in ("banded_root_ms", "fused_root_ms",
-                                                               "fused_root_r4_ms", "gather_ms"))
+            best_root = min(v for k, v in rec.items() if k.endswith("_ms") and
+                            k.startswith(("banded_root", "fused_root", "gather")))
             rec["delivered_root_ms"] = best_root
             rec["ingress_gbs"] = (world - 1) / world * M * N * 4 / best_root / 1e6
             rec["eff_kernels"] = rec["single_ms"] / (world * rec["kernels_ms"])
@@ -882,7 +893,9 @@ def run_gpu_arm(args) -> None:
     if dist is not None and "strong" in parts:
         progress("sharded jobs")
         strong = strong_scaling(torch, dist, rank, world, max(args.steps // 2, 3), 2,
-                                budget_s=args.strong_budget_s, all_jobs="alljobs" in parts)
+                                budget_s=args.strong_budget_s, all_jobs="alljobs" in parts,
+                                fused_shapes=[tuple(int(v) for v in s.split(":"))
+                                              for s in args.fused_shapes.split(",") if s])
     progress("measurements done on all ranks")
 
     if rank != 0:
@@ -1035,6 +1048,9 @@ def main() -> None:
     ap.add_argument("--parts", default="all,strong",
                     help="comma list; leave out 'strong' to skip the sharded jobs at N > 1; "
                          "'alljobs' also runs the 8-GPU jobs' code paths on fewer GPUs")
+    ap.add_argument("--fused-shapes", default="",
+                    help="sharded M13 job: also time the fused exchange with these rounds of the "
+                         "progressive schedule, 'rounds:ratio,...' (ratio in percent)")
     ap.add_argument("--strong-budget-s", type=float, default=240.0,
                     help="seconds after which no further sharded job is started")
     args = ap.parse_args()

@@ -383,24 +383,36 @@ def band_schedule(block: Block, N: int, K: int, bands: int, dests: Sequence[int]
 PEER_STORE_GBS = 690.0
 
 
-def fused_round_shape(ingress_bytes: int, kernel_ms: float, rounds: Optional[int] = None,
+def fused_round_shape(ingress_bytes: int, kernel_ms: float, tiles: int, workers: int,
+                      rounds: Optional[int] = None,
                       round_ratio: Optional[int] = None) -> Tuple[int, int]:
     """Rounds of the progressive schedule for a kernel whose C leaves over NVLink while it
     computes: (number of rounds, size of each round relative to the previous one in percent).
 
-    With a = t_link / t_compute and rounds whose sizes form a geometric sequence of ratio a,
-    every round's output has just left when the next round's arrives, and the last byte lands
-    at t_compute * (a + (1 - a) / (1 - a^R)): for a < 1 (the computation is the longer of the
-    two) the rounds shrink, so little is left to send at the end; for a > 1 they grow, so the
-    link -- the bottleneck -- starts after a small first round. `ingress_bytes` is what all
-    senders together push into the collecting GPU, `kernel_ms` one sender's kernel time."""
+    With a = t_link / t_compute: for a < 1 (the computation is the longer of the two) little
+    should be left to send when the kernel ends, so the rounds shrink; for a > 1 the link is the
+    bottleneck and should start early, so they grow. On paper rounds in a geometric sequence of
+    ratio a are ideal -- every round's output has just left when the next one's arrives -- but
+    every round in which a tile is shared by several workers costs 10-25 us of exchange, while
+    rounds of more tiles than workers are nearly free. Measured on 4 and 8 B200s (8192 x 4096 x
+    4096 and 16384^3 sharded by rows; rounds 1-8, ratios 40-250 %), the best shapes were:
+    a block of many waves (tiles >= 4 x workers): the library's own choice, equal rounds of
+    about one wave each (-1); a block of one to four waves: two rounds, the second 40 % of the
+    first, when the computation dominates, four rounds growing by 160 % when the link does; a
+    block of less than one wave (every round shares its tiles): four equal rounds.
+    `ingress_bytes` is what all senders together push into the collecting GPU, `kernel_ms` one
+    sender's kernel time, `tiles` and `workers` the block's tile count and the CTAs (or CTA
+    pairs) of the grid."""
     link_ms = ingress_bytes / (PEER_STORE_GBS * 1e6)
     a = link_ms / max(kernel_ms, 1e-6)
-    if rounds is None:
-        rounds = 4 if a <= 1.0 else 8
-    if round_ratio is None:
-        round_ratio = int(min(250, max(40, round(100 * a))))
-    return rounds, round_ratio
+    if tiles >= 4 * workers:
+        shape = (-1, 100)
+    elif tiles < workers:
+        shape = (4, 100)
+    else:
+        shape = (2, 40) if a <= 1.0 else (4, 160)
+    return (shape[0] if rounds is None else rounds,
+            shape[1] if round_ratio is None else round_ratio)
 
 
 class OverlappedGemm:
@@ -505,7 +517,8 @@ class OverlappedGemm:
             shape = (r1 - r0, self.block.cols)
             if shape not in by_shape:
                 cfg = MatmulConfig(shape[0], shape[1], K, _el_bits(mode))
-                hint, _fn, ms = roller.best_hint(cfg, arch, mode=mode, measure=measure)
+                hint, fn, ms = roller.best_hint(cfg, arch, mode=mode, measure=measure)
+                fn.plan.destroy()      # only the choice is kept; the bands get plans of their own
                 by_shape[shape] = (roller.kernel_tile_for(hint), ms if ms else hint.est_us * 1e-3)
             tile, kernel_ms = by_shape[shape]
             self.tiles.append(tile)
@@ -517,6 +530,8 @@ class OverlappedGemm:
                     self._synced = True        # ... and the kernel does its own hand-shake
                     self.rounds, self.round_ratio = fused_round_shape(
                         self.block.rows * self.block.cols * 4 * (world_size - 1), kernel_ms,
+                        -(-shape[0] // tile.block_m) * -(-shape[1] // tile.block_n),
+                        _lib.device_info(torch.cuda.current_device()).sm_count // tile.cta_group,
                         rounds, round_ratio)
                     plan.set_option(_lib.OPT_PROGRESSIVE_ROUNDS, self.rounds)
                     plan.set_option(_lib.OPT_ROUND_RATIO, self.round_ratio)

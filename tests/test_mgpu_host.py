@@ -234,16 +234,18 @@ def test_run_near_gpu_changes_nothing_when_the_topology_cannot_be_read(monkeypat
 
 
 def test_round_shape_of_the_fused_exchange():
-    """The rounds of a kernel whose C leaves over NVLink while it computes: four shrinking
-    rounds when the computation is the longer of the two, eight growing ones when the link is,
-    the ratio t_link / t_compute clamped to what the library accepts; explicit values win."""
+    """The rounds of a kernel whose C leaves over NVLink while it computes, by the size of the
+    block: the library's equal rounds for many waves; for one to four waves two shrinking
+    rounds when the computation is the longer of the two and four growing ones when the link
+    is; four equal rounds below one wave; explicit values win."""
     from mlir_roller_b200 import mgpu
     gb = 690e6        # bytes the link moves per millisecond at the measured rate
-    assert mgpu.fused_round_shape(int(0.6 * gb), 1.0) == (4, 60)
-    assert mgpu.fused_round_shape(int(1.2 * gb), 1.0) == (8, 120)
-    assert mgpu.fused_round_shape(int(0.1 * gb), 1.0) == (4, 40)
-    assert mgpu.fused_round_shape(int(10 * gb), 1.0) == (8, 250)
-    assert mgpu.fused_round_shape(int(1.2 * gb), 1.0, rounds=4, round_ratio=100) == (4, 100)
-    assert mgpu.fused_round_shape(int(0.6 * gb), 1.0, rounds=2) == (2, 60)
-    assert mgpu.fused_round_shape(int(gb), 0.0) == (8, 250)  # no time estimate: treated as link-bound
-    assert mgpu.fused_round_shape(0, 1.0) == (4, 40)
+    assert mgpu.fused_round_shape(int(0.6 * gb), 1.0, 128, 74) == (2, 40)
+    assert mgpu.fused_round_shape(int(1.2 * gb), 1.0, 128, 74) == (4, 160)
+    assert mgpu.fused_round_shape(int(1.2 * gb), 1.0, 64, 74) == (4, 100)     # less than one wave
+    assert mgpu.fused_round_shape(int(0.3 * gb), 1.0, 64, 74) == (4, 100)
+    assert mgpu.fused_round_shape(int(0.4 * gb), 1.0, 512, 74) == (-1, 100)   # the library's choice
+    assert mgpu.fused_round_shape(int(1.2 * gb), 1.0, 128, 74, rounds=8, round_ratio=100) == (8, 100)
+    assert mgpu.fused_round_shape(int(0.6 * gb), 1.0, 128, 74, rounds=3) == (3, 40)
+    assert mgpu.fused_round_shape(int(gb), 0.0, 128, 74) == (4, 160)  # no time estimate: link-bound
+    assert mgpu.fused_round_shape(0, 1.0, 128, 74) == (2, 40)
