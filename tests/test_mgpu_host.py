@@ -235,7 +235,7 @@ def test_run_near_gpu_changes_nothing_when_the_topology_cannot_be_read(monkeypat
 
 def test_round_shape_of_the_fused_exchange():
     """The rounds of a kernel whose C leaves over NVLink while it computes, by the size of the
-    block: the library's equal rounds for many waves; for one to four waves two shrinking
+    block: none for many waves; for one to four waves two shrinking
     rounds when the computation is the longer of the two and four growing ones when the link
     is; four equal rounds below one wave; explicit values win."""
     from mlir_roller_b200 import mgpu
@@ -244,7 +244,7 @@ def test_round_shape_of_the_fused_exchange():
     assert mgpu.fused_round_shape(int(1.2 * gb), 1.0, 128, 74) == (4, 160)
     assert mgpu.fused_round_shape(int(1.2 * gb), 1.0, 64, 74) == (4, 100)     # less than one wave
     assert mgpu.fused_round_shape(int(0.3 * gb), 1.0, 64, 74) == (4, 100)
-    assert mgpu.fused_round_shape(int(0.4 * gb), 1.0, 512, 74) == (-1, 100)   # the library's choice
+    assert mgpu.fused_round_shape(int(0.4 * gb), 1.0, 512, 74) == (0, 100)    # whole tiles, wave after wave
     assert mgpu.fused_round_shape(int(1.2 * gb), 1.0, 128, 74, rounds=8, round_ratio=100) == (8, 100)
     assert mgpu.fused_round_shape(int(0.6 * gb), 1.0, 128, 74, rounds=3) == (3, 40)
     assert mgpu.fused_round_shape(int(gb), 0.0, 128, 74) == (4, 160)  # no time estimate: link-bound
