@@ -364,7 +364,10 @@ int roller_b200_gemm_create(const roller_ktile* tile, int M, int N, int K, int l
   // A kernel whose ring fills shared memory also exists with one stage less and the staging
   // area of that path; for the pair tile that form is the faster one up to K = 4096 (see
   // GemmCfg; the single-CTA 128 x 128 tile gains nothing from it and switches only on request).
-  if (c_fits_tma && K <= 4096 && kv->cta_group == 2) {
+  // An fp32 C whose rows are not 16-byte aligned is written through the same staging area (see
+  // kFlagSmemStore): the form with the area then pays at any K.
+  const bool c_ragged = layout == 0 || layout == 1 ? (p->c_elem == 4 && ldc % 4 != 0) : false;
+  if ((c_fits_tma && K <= 4096 && kv->cta_group == 2) || (c_ragged && kv->staging_bytes == 0)) {
     const KernelVariant* staged = find_staged_form(kv);
     if (staged && static_cast<int>(prop.sharedMemPerBlockOptin) >= staged->smem_bytes) kv = staged;
   }
@@ -495,6 +498,10 @@ int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, void* C, 
     args.flags |= kFlagVecStore;
   if (p->c_elem == 2) args.flags |= kFlagC16;
   if (tma_store) args.flags |= kFlagTmaStore;
+  // rows of an fp32 C that start anywhere: coalesced stores through the staging area
+  if (!tma_store && kv->staging_bytes > 0 && p->c_elem == 4 && p->layout != 2 &&
+      !(args.flags & kFlagVecStore))
+    args.flags |= kFlagSmemStore;
   // In the progressive schedule tiles are shared on purpose. With this flag the kernel lets
   // all workers of a tile complete it together in the rounds where a tile is shared by three
   // workers or more; in the others the worker holding the end of the reduction does it alone.

@@ -19,6 +19,10 @@ constexpr int kFlagC16 = 4;         // 16-bit kernels only: C holds elements of 
 constexpr int kFlagTmaStore = 8;    // C leaves through shared memory and TMA stores (GemmArgs::tmC)
 constexpr int kFlagCoopFixup = 32;  // shared tiles are completed by all their workers together (needs
                                     // kFlagTmaStore; four scratch slots and reader counts per CTA)
+constexpr int kFlagSmemStore = 128; // fp32 C whose rows are not 16-byte aligned: tiles are turned
+                                    // through the staging area so that a warp writes 32
+                                    // consecutive floats of one row per store (needs the
+                                    // staging area; not together with kFlagTmaStore)
 constexpr int kFlagPeerSync = 64;   // the launch waits for and raises another GPU's flags itself
                                     // (GemmArgs::peer; needs kFlagTmaStore)
 constexpr int kFlagDropPublish = 16;  // test aid: partial tiles are written but never flagged, so

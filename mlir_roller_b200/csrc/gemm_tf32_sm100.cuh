@@ -596,6 +596,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // 16-bit kernels can also write C in their operand type (C then points to 16-bit elements)
     const bool c16 = Cfg::DT != 0 && (flags & kFlagC16) != 0;
     const bool tma_store = Cfg::STAGING_BYTES > 0 && (flags & kFlagTmaStore) != 0;
+    const bool smem_store = Cfg::STAGING_BYTES > 0 && !tma_store && (flags & kFlagSmemStore) != 0;
     // With partial tiles in play the 256 threads meet at barriers, so they must also leave
     // together: every decision to give up is then taken by a vote at such a barrier.
     const bool sk_active = sk_tiles > 0;
@@ -954,6 +955,50 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (go_pending) await_go();
                 tma_store_2d(&tmC, box, col0, row0);
                 bulk_commit_group();
+              }
+            }
+          }
+          continue;
+        }
+        if (smem_store) {
+          // C's rows start anywhere (an odd leading dimension), so neither TMA nor 128-bit
+          // stores apply, and a lane storing its own row would touch 32 different rows per
+          // instruction. The 32 x 32 pieces go through this warp's staging box instead and
+          // are read back row by row: lane l then holds column l, and one store writes 128
+          // consecutive bytes of a row of C.
+          const uint32_t box = staging + static_cast<uint32_t>(warp - Cfg::FIRST_EPI_WARP) * 4096u;
+          const int row0 = (mb * CG + static_cast<int>(cta_rank)) * Cfg::BM + quarter * 32;
+          if (row0 < M) {
+#pragma unroll
+            for (int c = 0; c < COLS / 32; ++c) {
+              const int col0 = n0 + c * 32;
+              if (col0 >= N) break;
+              __syncwarp();     // the previous piece has been read back by every lane
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const uint32_t at = box + static_cast<uint32_t>(lane) * 128u +
+                                    (static_cast<uint32_t>(j ^ (lane & 7)) << 4);
+                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(at),
+                             "f"(sum[c * 32 + 4 * j]), "f"(sum[c * 32 + 4 * j + 1]),
+                             "f"(sum[c * 32 + 4 * j + 2]), "f"(sum[c * 32 + 4 * j + 3])
+                             : "memory");
+              }
+              __syncwarp();
+              const int col = col0 + lane;
+              const int rows_here = min(32, M - row0);
+              float* dst = C + static_cast<size_t>(row0) * static_cast<size_t>(ldc) + col;
+              if (col < N) {
+#pragma unroll 8
+                for (int r = 0; r < rows_here; ++r) {
+                  const uint32_t at = box + static_cast<uint32_t>(r) * 128u +
+                                      (static_cast<uint32_t>((lane >> 2) ^ (r & 7)) << 4) +
+                                      (static_cast<uint32_t>(lane & 3) << 2);
+                  float v;
+                  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(at) : "memory");
+                  if (accumulate) v += *dst;
+                  *dst = v;
+                  dst += ldc;
+                }
               }
             }
           }
