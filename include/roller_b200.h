@@ -99,6 +99,12 @@ typedef enum roller_status {
                                           shrinking rounds when the computation is the longer of
                                           the two (little is left to send after the last round),
                                           growing ones when the link is (it starts early) */
+#define ROLLER_OPT_EARLY_EXIT 8         /* 1: with TMA stores, a CTA leaves as soon as the TMA unit
+                                          has read its last tile from shared memory instead of
+                                          waiting for the stores to be performed; C is complete
+                                          when the kernel is (stream order), and a kernel of
+                                          another stream can take the SM meanwhile. Ignored by a
+                                          launch that raises an arrival flag itself. Default 0 */
 #define ROLLER_OPT_COOPERATIVE_FIXUP 6  /* 1 (default): in the progressive schedule with TMA stores a
                                           tile shared by several workers is completed by all of
                                           them together, each adding a slice of everybody's

@@ -29,6 +29,7 @@ OPT_PROGRESSIVE_ROUNDS = 4
 OPT_TEST_DROP_PUBLISH = 5
 OPT_COOPERATIVE_FIXUP = 6
 OPT_ROUND_RATIO = 7
+OPT_EARLY_EXIT = 8
 MAX_ROUNDS = 16
 MAX_FLAG_TARGETS = 32
 # device status words (what a bounded wait that ran out records)

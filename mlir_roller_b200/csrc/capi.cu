@@ -174,6 +174,7 @@ struct roller_plan {
   bool tma_forced;        // ... because the caller asked for it (else: chosen by the library)
   bool coop_fixup;        // progressive schedule: shared tiles are completed by all their workers
   bool drop_publish;      // test aid: partial tiles are never flagged
+  bool early_exit;        // CTAs leave once their last tile has been read from shared memory
   bool stage_a, stage_b;  // operands go through a padded copy
   void* ws_a;             // padded copies (device), owned
   void* ws_b;
@@ -508,6 +509,7 @@ int roller_b200_gemm_run(roller_plan* p, const void* A, const void* B, void* C, 
   if (tma_store && p->progressive != 0 && p->sk_tiles > 0 && p->coop_fixup)
     args.flags |= kFlagCoopFixup;
   if (p->drop_publish) args.flags |= kFlagDropPublish;
+  if (p->early_exit) args.flags |= kFlagEarlyExit;
   args.round_plan = p->round_plan;
   args.peer = p->peer;
   if (peer_sync) {
@@ -734,6 +736,9 @@ int roller_b200_gemm_set_option(roller_plan* p, int option, long long value) {
         return ROLLER_ERR_UNSUPPORTED;
       p->progressive = static_cast<int>(value);
       return plan_configure(p);
+    case ROLLER_OPT_EARLY_EXIT:
+      p->early_exit = value != 0;
+      return ROLLER_OK;
     case ROLLER_OPT_COOPERATIVE_FIXUP:
       p->coop_fixup = value != 0;
       return ROLLER_OK;

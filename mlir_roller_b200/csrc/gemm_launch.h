@@ -23,6 +23,10 @@ constexpr int kFlagSmemStore = 128; // fp32 C whose rows are not 16-byte aligned
                                     // through the staging area so that a warp writes 32
                                     // consecutive floats of one row per store (needs the
                                     // staging area; not together with kFlagTmaStore)
+constexpr int kFlagEarlyExit = 256; // with kFlagTmaStore: a CTA leaves once the TMA unit has read its
+                                    // last tile from shared memory; the stores are complete
+                                    // when the kernel is, so the next kernel of another stream
+                                    // can take the SM while they are still on their way
 constexpr int kFlagPeerSync = 64;   // the launch waits for and raises another GPU's flags itself
                                     // (GemmArgs::peer; needs kFlagTmaStore)
 constexpr int kFlagDropPublish = 16;  // test aid: partial tiles are written but never flagged, so

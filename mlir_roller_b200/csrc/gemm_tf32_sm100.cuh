@@ -1105,8 +1105,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (coop && ok && npend > 0) flush_pending();
       // Stores handed to the TMA unit must have been performed before the CTA may go.
       if (tma_store && lane == 0) {
-        bulk_wait_all();
-        if ((flags & kFlagPeerSync) != 0 && peer.arrive_flag != nullptr && ok &&
+        const bool arrives = (flags & kFlagPeerSync) != 0 && peer.arrive_flag != nullptr;
+        // (shared memory may be given up as soon as the TMA unit has read it; an arrival flag
+        // needs the stores themselves to have been performed)
+        if ((flags & kFlagEarlyExit) != 0 && !arrives) bulk_wait_read_all();
+        else bulk_wait_all();
+        if (arrives && ok &&
             *reinterpret_cast<volatile uint32_t*>(status) == kDevOk) {
           // This warp's stores have been performed. Count it; the last warp of the launch tells
           // the other GPU (the fences order every warp's stores, which the counter's chain of

@@ -378,6 +378,9 @@ def band_schedule(block: Block, N: int, K: int, bands: int, dests: Sequence[int]
             for r0, r1 in split_bands(block.row0, block.row1, bands, taper=taper)]
 
 
+# Steps a pipelined fused exchange can count (the arrival flags are copied from a table).
+STEP_TABLE = 1 << 20
+
 # What the TMA units of several GPUs together push into one GPU's memory over NVLink (measured
 # on B200 / NVSwitch; a copy engine reaches 770).
 PEER_STORE_GBS = 690.0
@@ -444,8 +447,13 @@ class OverlappedGemm:
     the arrival flag, so no launch boundary lies between the last store and the flag. An rTile
     whose kernel lacks the staging area keeps the kernel's own stores and is bracketed by the
     two flag kernels instead.
-    C must not be read while another rank may still be pushing the next step into it: separate
-    consecutive steps by whatever makes the readers finish first (the bench only times).
+    C must not be read while another rank may still be pushing the next step into it: on the
+    root call `finish(release=False)`, enqueue the reader, then `release()` -- the "go" that lets
+    the others overwrite the buffer. With `depth=2` (fused only) C alternates between two
+    buffers and a sender waits for the "go" of the step before last, so the senders compute and
+    push step s + 1 while the root still reads step s: consecutive jobs then take
+    max(t_compute, t_link) each instead of their sum's exposed part (`og.C` is the buffer of
+    the latest step).
 
         og = OverlappedGemm(M, N, K, rank, world, bands=4, dest="all")
         og.run(A_rows, B_full); og.finish()       # og.C now holds the product
@@ -456,7 +464,7 @@ class OverlappedGemm:
                  bands: Optional[int] = None, dest: str = "root", root: int = 0, group=None, arch=None, measure: bool = False,
                  comm_streams: int = 2, taper: bool = False, fused: bool = False,
                  rounds: Optional[int] = None, round_ratio: Optional[int] = None,
-                 wait_limit_cycles: int = 0):
+                 wait_limit_cycles: int = 0, depth: int = 1):
         import os
         # plain peer mappings only: no NVLink multicast object is bound to the buffer
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
@@ -484,9 +492,17 @@ class OverlappedGemm:
         self._dist = dist
         self._torch = torch
 
-        self.C = symm_mem.empty((M, N), dtype=torch.float32, device=torch.device("cuda"))
-        self.handle = symm_mem.rendezvous(self.C, self.group)
-        self.peer_C = {d: self.handle.get_buffer(d, (M, N), torch.float32) for d in self.dests}
+        if depth < 1 or (depth > 1 and not fused):
+            raise ValueError("depth > 1 (several C buffers in flight) exists for the fused exchange only")
+        # `depth` buffers for C, used in turn: with two, the senders already work on step s + 1
+        # while the root still reads step s (they wait for "go" of step s + 1 - depth)
+        self.depth = depth
+        self.C_bufs = [symm_mem.empty((M, N), dtype=torch.float32, device=torch.device("cuda"))
+                       for _ in range(depth)]
+        self.handles = [symm_mem.rendezvous(c, self.group) for c in self.C_bufs]
+        self.peer_C_bufs = [{d: h.get_buffer(d, (M, N), torch.float32) for d in self.dests}
+                            for h in self.handles]
+        self.handle = self.handles[0]
         self._token = torch.zeros(1, dtype=torch.float32, device="cuda")
         self._step = 0
         self._wait_limit = wait_limit_cycles
@@ -513,6 +529,7 @@ class OverlappedGemm:
         self.bands = [(st.row0, st.row1) for st in self.steps]
         self.plans, self.tiles, self._events = [], [], []
         self._synced = self._signalled = False
+        self._pipe_plans, self._pipe_streams = None, None
         self.rounds = self.round_ratio = None
         by_shape = {}
         for r0, r1 in self.bands:
@@ -524,26 +541,44 @@ class OverlappedGemm:
                 by_shape[shape] = (roller.kernel_tile_for(hint), ms if ms else hint.est_us * 1e-3)
             tile, kernel_ms = by_shape[shape]
             self.tiles.append(tile)
-            plan = _lib.GemmPlan(tile, shape[0], shape[1], K, lda=K, ldb=N, ldc=N, mode=mode)
-            if fused and self.dests:
-                # C lives on the other side of NVLink: decoupled stores, steady tile completion
-                try:
-                    plan.set_option(_lib.OPT_TMA_STORE, 1)
-                    self._synced = True        # ... and the kernel does its own hand-shake
-                    self.rounds, self.round_ratio = fused_round_shape(
-                        self.block.rows * self.block.cols * 4 * (world_size - 1), kernel_ms,
-                        -(-shape[0] // tile.block_m) * -(-shape[1] // tile.block_n),
-                        _lib.device_info(torch.cuda.current_device()).sm_count // tile.cta_group,
-                        rounds, round_ratio)
-                    plan.set_option(_lib.OPT_PROGRESSIVE_ROUNDS, self.rounds)
-                    plan.set_option(_lib.OPT_ROUND_RATIO, self.round_ratio)
-                except _lib.RollerError as e:
-                    if e.status not in (_lib.ERR_UNSUPPORTED, _lib.ERR_INVALID):
-                        raise
-            if wait_limit_cycles:
-                plan.set_option(_lib.OPT_WAIT_LIMIT_CYCLES, wait_limit_cycles)
-            self.plans.append(plan)
+            def new_plan(tile=tile, shape=shape, kernel_ms=kernel_ms):
+                plan = _lib.GemmPlan(tile, shape[0], shape[1], K, lda=K, ldb=N, ldc=N, mode=mode)
+                if fused and self.dests:
+                    # C lives on the other side of NVLink: decoupled stores, steady tile completion
+                    try:
+                        plan.set_option(_lib.OPT_TMA_STORE, 1)
+                        self._synced = True        # ... and the kernel does its own hand-shake
+                        self.rounds, self.round_ratio = fused_round_shape(
+                            self.block.rows * self.block.cols * 4 * (world_size - 1), kernel_ms,
+                            -(-shape[0] // tile.block_m) * -(-shape[1] // tile.block_n),
+                            _lib.device_info(torch.cuda.current_device()).sm_count // tile.cta_group,
+                            rounds, round_ratio)
+                        plan.set_option(_lib.OPT_PROGRESSIVE_ROUNDS, self.rounds)
+                        plan.set_option(_lib.OPT_ROUND_RATIO, self.round_ratio)
+                    except _lib.RollerError as e:
+                        if e.status not in (_lib.ERR_UNSUPPORTED, _lib.ERR_INVALID):
+                            raise
+                if wait_limit_cycles:
+                    plan.set_option(_lib.OPT_WAIT_LIMIT_CYCLES, wait_limit_cycles)
+                return plan
+
+            self.plans.append(new_plan())
             self._events.append(torch.cuda.Event())
+            if fused and depth > 1 and self.dests and self._synced:
+                # Several steps in flight on a sending rank: a plan (scratch area, status word)
+                # and a stream per C buffer. The kernels of consecutive steps share nothing but
+                # the read-only operands, so they may run side by side: a CTA leaves as soon as
+                # its last tile has been read from shared memory, the next step's CTA takes the
+                # SM, and the arrival flag follows the kernel on its own stream once all its
+                # stores have been performed. That flag is written by a copy engine (a 4-byte
+                # copy of the step's number from a table on this GPU): a kernel could not run
+                # before the next step's persistent CTAs, which fill every SM, have left.
+                self._pipe_plans = [self.plans[0]] + [new_plan() for _ in range(depth - 1)]
+                self.plans.extend(self._pipe_plans[1:])
+                for p in self._pipe_plans:
+                    p.set_option(_lib.OPT_EARLY_EXIT, 1)
+                self._pipe_streams = [torch.cuda.Stream() for _ in range(depth)]
+                self._step_table = torch.arange(1, STEP_TABLE + 1, dtype=torch.int32, device="cuda")
 
     def run(self, A_rows, B_full, stream=None) -> None:
         """Enqueue this rank's bands and their pushes. `A_rows` = A[rows of this rank's block, :]
@@ -558,18 +593,35 @@ class OverlappedGemm:
         if self.fused:
             self._step += 1
             # one kernel per rank; its C is the root's matrix (this rank's own on the root)
-            out = self.peer_C[self.dests[0]] if self.dests else self.C
+            peer_C = self.peer_C_bufs[(self._step - 1) % self.depth]
+            out = peer_C[self.dests[0]] if self.dests else self.C
             step, plan = self.steps[0], self.plans[0]
+            behind = self._step - self.depth       # the step whose C this one overwrites
             ptrs = (A_rows.data_ptr() + step.a_off * eb, B_full.data_ptr() + step.b_off * eb,
                     out.data_ptr() + step.c_off * 4)
             self._signalled = False
+            if self._pipe_plans is not None:
+                # (sending rank, several C buffers) this buffer's plan on this buffer's stream
+                k = (self._step - 1) % self.depth
+                st = self._pipe_streams[k]
+                st.wait_stream(cs)            # the operands are ready
+                self._pipe_plans[k].run_synced_ptr(
+                    *ptrs, go_ptr=self.flags.data_ptr() + 4 * FLAG_GO if behind >= 1 else 0,
+                    go_value=max(behind, 0), stream=st)
+                if self._step > STEP_TABLE:
+                    raise ValueError(f"the pipelined exchange counts at most {STEP_TABLE} steps")
+                self._lib.copy_block_async(
+                    self.peer_flags[self.root].data_ptr() + 4 * self.rank, 1,
+                    self._step_table.data_ptr() + 4 * (self._step - 1), 1, 1, 1, st)
+                self._signalled = True
+                return
             if self.rank != self.root and self._synced:
                 try:
                     # "go": the root has finished with the previous step's C; "arrive": this
                     # rank's stores of this step have landed
                     plan.run_synced_ptr(
-                        *ptrs, go_ptr=self.flags.data_ptr() + 4 * FLAG_GO if self._step > 1 else 0,
-                        go_value=self._step - 1,
+                        *ptrs, go_ptr=self.flags.data_ptr() + 4 * FLAG_GO if behind >= 1 else 0,
+                        go_value=max(behind, 0),
                         arrive_ptr=self.peer_flags[self.root].data_ptr() + 4 * self.rank,
                         arrive_value=self._step, stream=cs)
                     self._signalled = True
@@ -578,9 +630,9 @@ class OverlappedGemm:
                     if e.status != self._lib.ERR_UNSUPPORTED:
                         raise
                     self._synced = False
-            if self.rank != self.root and self._step > 1:
+            if self.rank != self.root and behind >= 1:
                 self._lib.flag_wait_async(self.flags.data_ptr(), FLAG_WORDS, 1 << FLAG_GO,
-                                          self._step - 1, self.flag_status.data_ptr(),
+                                          behind, self.flag_status.data_ptr(),
                                           self._wait_limit, cs)
             plan.run_ptr(*ptrs, cs)
             return
@@ -596,15 +648,40 @@ class OverlappedGemm:
                                            self.C.data_ptr() + step.c_off * 4, N,
                                            step.row1 - step.row0, step.cols, st)
 
-    def finish(self, stream=None) -> None:
+    @property
+    def C(self):
+        """The matrix the current step delivers into (the last `run`'s; buffer 0 before any)."""
+        return self.C_bufs[max(self._step - 1, 0) % self.depth]
+
+    @property
+    def peer_C(self):
+        return self.peer_C_bufs[max(self._step - 1, 0) % self.depth]
+
+    def release(self, stream=None) -> None:
+        """Fused exchange, on the root: tell the other ranks that this step's C has been read
+        (enqueued on `stream` behind the reader). `finish` does it right away unless called
+        with `release=False`."""
+        if not self.fused or self.rank != self.root:
+            return
+        cs = stream if stream is not None else self._torch.cuda.current_stream()
+        others = [r for r in range(self.world_size) if r != self.root]
+        if others:
+            self._lib.flag_signal_async([self.peer_flags[r].data_ptr() + 4 * FLAG_GO
+                                         for r in others], self._step, cs)
+
+    def finish(self, stream=None, release: bool = True) -> None:
         """Enqueue the closing fence; once `stream` has passed it, every rank's pushes of this
         step have landed."""
         torch = self._torch
         cs = stream if stream is not None else torch.cuda.current_stream()
         if self.fused:
             if self.rank != self.root:
+                if self._pipe_streams is not None:
+                    # stay at most `depth` steps ahead of the caller's stream: it waits for the
+                    # oldest step still in flight (the stream the next `run` will use)
+                    cs.wait_stream(self._pipe_streams[self._step % self.depth])
                 if self._signalled:
-                    return      # the kernel raised the flag itself
+                    return      # the flag has been (or will be) raised behind the kernel
                 # behind the kernel on the stream: its stores into the root's C have been performed
                 self._lib.flag_signal_async([self.peer_flags[self.root].data_ptr() + 4 * self.rank],
                                             self._step, cs)
@@ -614,8 +691,8 @@ class OverlappedGemm:
                 mask = sum(1 << r for r in others)
                 self._lib.flag_wait_async(self.flags.data_ptr(), FLAG_WORDS, mask, self._step,
                                           self.flag_status.data_ptr(), self._wait_limit, cs)
-                self._lib.flag_signal_async([self.peer_flags[r].data_ptr() + 4 * FLAG_GO
-                                             for r in others], self._step, cs)
+                if release:
+                    self.release(cs)
             return
         lead = self.comm[0]
         for st in self.comm[1:]:

@@ -61,6 +61,30 @@ def main() -> int:
             og.destroy()
             del og
             dist.barrier()
+    # two C buffers in flight: the senders work on step s + 1 while rank 0 still reads step s.
+    # Five steps with different operands and no host synchronisation between them; rank 0 copies
+    # every step's C on the stream between the arrival wait and the release of the buffer.
+    og = mgpu.OverlappedGemm(M, N, K, rank, world, grid=(world, 1), dest="root", fused=True, depth=2)
+    b = og.block
+    As = [(A[b.row0:b.row1] * (s + 1)).contiguous() for s in range(5)]
+    got = []
+    for s in range(5):
+        og.run(As[s], B)
+        og.finish(release=False)
+        if rank == 0:
+            got.append(og.C.clone())
+        og.release()
+    torch.cuda.synchronize()
+    dist.barrier()
+    og.check_status()
+    err = max((float((c.double() - (s + 1) * ref).abs().max()) / ((s + 1) * scale)
+               for s, c in enumerate(got)), default=0.0)
+    ok = err <= TOL_3X and len({c.data_ptr() for c in og.C_bufs}) == 2
+    print(f"rank {rank} fused, two C buffers, 5 steps: err {err:.2e} {'ok' if ok else 'FAIL'}", flush=True)
+    bad += 0 if ok else 1
+    og.destroy()
+    del og, got
+    dist.barrier()
     # the same exchange with bf16 operands (the band offsets into A and B are in elements)
     A16, B16 = A.to(torch.bfloat16), B.to(torch.bfloat16)
     ref16 = A16.double() @ B16.double()

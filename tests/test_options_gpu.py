@@ -448,3 +448,32 @@ def test_the_hand_shake_needs_the_tma_store_path():
                             arrive_ptr=flags.data_ptr() + 2, arrive_value=1)
     assert e.value.status == _lib.ERR_INVALID
     plan.destroy()
+
+
+def test_early_exit_leaves_the_result_alone():
+    """ROLLER_OPT_EARLY_EXIT: CTAs leave once the TMA unit has read their last tile from shared
+    memory; C is complete when the kernel is. Same bits as without the option, launch after
+    launch, also with rounds; a launch that raises an arrival flag still waits for its stores."""
+    M, N, K = 1024, 1536, 1024
+    A, B = g.make_inputs(M, N, K, "uniform", seed=23)
+    ref = run_plan(A, B, (256, 256, 2), 3, [(_lib.OPT_TMA_STORE, 1)])[0]
+    for opts in ([], [(_lib.OPT_PROGRESSIVE_ROUNDS, 2), (_lib.OPT_ROUND_RATIO, 40)]):
+        plain = run_plan(A, B, (256, 256, 2), 3, [(_lib.OPT_TMA_STORE, 1)] + opts, launches=2)
+        early = run_plan(A, B, (256, 256, 2), 3, [(_lib.OPT_TMA_STORE, 1), (_lib.OPT_EARLY_EXIT, 1)] + opts,
+                         launches=3)
+        for out in early:
+            assert np.array_equal(out, plain[0])
+        assert g.err_norm(plain[0], g.matmul_fp64(A, B)) <= TIGHT_3X
+    assert g.err_norm(ref, g.matmul_fp64(A, B)) <= TIGHT_3X
+    dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    dC = torch.full((M, N), float("nan"), device="cuda")
+    flags = torch.zeros(4, dtype=torch.int32, device="cuda")
+    plan = _lib.GemmPlan(_lib.find_tile(256, 256, 2), M, N, K, mode=3)
+    plan.set_option(_lib.OPT_TMA_STORE, 1)
+    plan.set_option(_lib.OPT_EARLY_EXIT, 1)
+    plan.run_synced_ptr(dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), arrive_ptr=flags.data_ptr(),
+                        arrive_value=7)
+    torch.cuda.synchronize()
+    plan.check_status()
+    assert int(flags[0].item()) == 7 and np.array_equal(dC.cpu().numpy(), ref)
+    plan.destroy()
