@@ -561,7 +561,10 @@ def strong_scaling(torch, dist, rank, world, steps, warmup, budget_s=240.0, all_
     by an NCCL gather of C to rank 0 ("gather"), with the exchange of C running underneath the
     computation through the copy engines to rank 0 ("banded_root") and to every rank
     ("banded_all"), and fused into the kernel ("fused_root": the kernel's TMA unit stores the
-    tiles straight into rank 0's C, progressive schedule, closed by flags). After timing, each
+    tiles straight into rank 0's C, progressive schedule, closed by flags; for M13 also
+    "fused_root_r4" with four equal rounds and "fused_root_pipelined", the steady-state time per
+    job with two C buffers on rank 0, which is a throughput and not counted as a delivery
+    latency). After timing, each
     path runs once more into a NaN-filled C and the delivered matrix is compared with fp64 on
     sampled rows. Returns a list of compact records (identical on all ranks); times are the max
     over ranks, errors the max over the ranks that hold a result. Jobs that would start after
