@@ -347,9 +347,12 @@ class ShapeCase:
         self.rotation = None
 
 
-def measure_pcie(torch, mib: int = 512):
+def measure_pcie(torch, mib: int = 512, only_duplex: bool = False, before=None):
     """Pinned-memory copy rates of this box, GB/s: (host->device alone, device->host alone,
-    each way with both directions busy). They bound the end-to-end figure."""
+    each way with both directions busy). They bound the end-to-end figure. With `only_duplex`
+    just the last one is measured (returned alone), after calling `before` -- a barrier, when
+    every rank of a node measures at the same moment to see what the host sustains for all
+    GPUs together."""
     n = mib * 1024 * 1024 // 4
     h_up = torch.empty(n, dtype=torch.float32).pin_memory()
     h_dn = torch.empty(n, dtype=torch.float32).pin_memory()
@@ -377,6 +380,10 @@ def measure_pcie(torch, mib: int = 512):
         return n * 4.0 * reps / e0.elapsed_time(e1) / 1e6
 
     timed(True, True, 1)
+    if only_duplex:
+        if before is not None:
+            before()
+        return timed(True, True, 4)
     return timed(True, False), timed(False, True), timed(True, True)
 
 
@@ -908,6 +915,14 @@ def run_gpu_arm(args) -> None:
                                 budget_s=args.strong_budget_s, all_jobs="alljobs" in parts,
                                 fused_shapes=[tuple(int(v) for v in s.split(":"))
                                               for s in args.fused_shapes.split(",") if s])
+    # what the host sustains when every GPU of the node copies both ways at once (the slowest
+    # rank's rate): the end-to-end step of N ranks cannot beat it
+    duplex_all_gbs = None
+    if dist is not None:
+        mine = measure_pcie(torch, mib=256, only_duplex=True, before=dist.barrier)
+        t = torch.tensor([mine], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        duplex_all_gbs = float(t.item())
     progress("measurements done on all ranks")
 
     if rank != 0:
@@ -921,6 +936,13 @@ def run_gpu_arm(args) -> None:
     up_gbs, down_gbs, duplex_gbs = measure_pcie(torch)
     t_down = d2h / (duplex_gbs * 1e6)
     e2e_bound_ms = t_down + max(h2d - t_down * duplex_gbs * 1e6, 0.0) / (up_gbs * 1e6)
+    pcie = {"h2d": up_gbs, "d2h": down_gbs, "each_way_duplex": duplex_gbs}
+    if duplex_all_gbs is not None:
+        # with all ranks copying: the same estimate with the duplex rate the host then sustains
+        pcie["each_way_duplex_all_ranks_at_once"] = duplex_all_gbs
+        t_down = d2h / (duplex_all_gbs * 1e6)
+        e2e_bound_ms = max(e2e_bound_ms,
+                           t_down + max(h2d - t_down * duplex_all_gbs * 1e6, 0.0) / (up_gbs * 1e6))
 
     # ---- roofline of the dominant kernel (the tcgen05 GEMM): algorithmic tensor flops (3 TF32
     # products per fp32 product) of one step over the step's duration. The denominator is a
@@ -1027,7 +1049,7 @@ def run_gpu_arm(args) -> None:
                 "path": ("roller_b200_gemm_host_async per shape, three streams" if world == 1 else
                          "mgpu.HostStagedGemm per shape: own rows of A and 1/world of B uploaded "
                          "per rank, B's shares exchanged over NVLink (bytes are per rank)"),
-                "pcie_gbs": {"h2d": up_gbs, "d2h": down_gbs, "each_way_duplex": duplex_gbs},
+                "pcie_gbs": pcie,
                 "pcie_bound_ms": e2e_bound_ms},
         "gpu_launches": len(README_SHAPES) * args.steps,
         # the same sweep with bf16 operands (fp32 accumulate and C); rank 0's own GPU only
