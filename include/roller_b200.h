@@ -90,7 +90,9 @@ typedef enum roller_status {
                                           finished tiles leave the kernel at a steady rate from
                                           early on rather than together at the end (at most 16,
                                           and at most one per tile). -1 = the library picks n;
-                                          0 = off */
+                                          0 = off. With equal rounds of fewer tiles than CTAs
+                                          (or CTA pairs) the grid shrinks by up to a sixth to a
+                                          count that the tiles of a round divide */
 #define ROLLER_OPT_ROUND_RATIO 7        /* size of each round of the progressive schedule relative
                                           to the one before it, in percent (25 .. 400; default
                                           100 = equal rounds). When C leaves over a link while
